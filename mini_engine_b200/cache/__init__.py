@@ -1,0 +1,13 @@
+"""The cache manager (host bookkeeping) and the device memory it describes."""
+
+from mini_engine_b200.cache.manager import (
+    NULL_PAGE,
+    CacheManager,
+    GroupSpec,
+    PagePool,
+    RequestCache,
+    SlotPool,
+    hash_page,
+)
+
+__all__ = ["NULL_PAGE", "CacheManager", "GroupSpec", "PagePool", "RequestCache", "SlotPool", "hash_page"]

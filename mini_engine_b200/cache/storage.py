@@ -1,0 +1,96 @@
+"""Device memory of the cache, laid out from what the model's mixers declare.
+
+Every execution entry whose mixer keeps keys and values gets two page arrays ``[pages + 1,
+kv_heads, block_size, head_dim]``: one page of one head is ``block_size * head_dim``
+contiguous elements (4 KB at 16 x 128 bfloat16), which is what the attention kernels stream.
+The reference keeps ``[kv_heads, pages + 1, block_size, head_dim]`` per layer
+(src/mini_engine/engine.py:72-79 of YuvGev00/mini-engine) because its gather wants heads in
+front; here nothing is gathered.  The last page is a spare that no request owns: padding
+rows of a captured decode graph write to it and read from it.  Entries with equal needs
+share a group, hence a page pool and block tables.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from mini_engine_b200.cache.manager import GroupSpec
+from mini_engine_b200.parts.base import LayerCache, PagedCacheSpec, StateSpec
+
+
+@dataclass
+class CacheLayout:
+    groups: list[GroupSpec]
+    group_specs: list[PagedCacheSpec]
+    views: list[LayerCache]  # one per execution entry
+    arrays: list[torch.Tensor]  # per group [entries, 2, pages + 1, kv_heads, block_size, head_dim]
+    has_state: bool
+    bytes_per_token: int
+
+
+def plan_groups(needs) -> tuple[list[PagedCacheSpec], list[int | None]]:
+    """Group the execution entries by equal per-token need.  Returns the distinct needs and,
+    per entry, its group index (``None`` for an entry without per-token cache)."""
+    specs: list[PagedCacheSpec] = []
+    group_of: list[int | None] = []
+    for paged, _state, cache_of in needs:
+        if paged is None:
+            group_of.append(None)
+            continue
+        if cache_of is not None:
+            owner = needs[cache_of][0]
+            if owner != paged:
+                raise ValueError(f"an entry reads a cache of {owner} but its mixer expects {paged}")
+            group_of.append(group_of[cache_of])
+            continue
+        if paged not in specs:
+            specs.append(paged)
+        group_of.append(specs.index(paged))
+    return specs, group_of
+
+
+def group_names(specs: list[PagedCacheSpec]) -> list[GroupSpec]:
+    return [
+        GroupSpec(f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f":w{s.window}" if s.window else ""), s.window)
+        for i, s in enumerate(specs)
+    ]
+
+
+def allocate_cache(
+    needs: list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]],
+    num_blocks: int,
+    block_size: int,
+    max_num_seqs: int,
+    dtype: torch.dtype,
+    device: str | torch.device = "cuda",
+) -> CacheLayout:
+    specs, group_of = plan_groups(needs)
+    owners: list[list[int]] = [[] for _ in specs]
+    for entry, (paged, _state, cache_of) in enumerate(needs):
+        if paged is not None and cache_of is None:
+            owners[group_of[entry]].append(entry)
+    element = torch.empty((), dtype=dtype).element_size()
+    arrays = [
+        torch.zeros(
+            (len(entries), 2, num_blocks + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device
+        )
+        for s, entries in zip(specs, owners)
+    ]
+    views: list[LayerCache] = []
+    has_state = False
+    for entry, (paged, state, cache_of) in enumerate(needs):
+        view = LayerCache()
+        if paged is not None:
+            g = group_of[entry]
+            owner = entry if cache_of is None else cache_of
+            index = owners[g].index(owner)
+            view.group, view.k, view.v = g, arrays[g][index, 0], arrays[g][index, 1]
+            view.writes = cache_of is None
+        if state is not None:
+            has_state = True
+            view.state = torch.zeros((max_num_seqs + 1, *state.shape), dtype=state.dtype, device=device)
+        views.append(view)
+    per_token = sum(2 * len(e) * s.kv_heads * s.head_dim * element for s, e in zip(specs, owners))
+    return CacheLayout(group_names(specs), specs, views, arrays, has_state, per_token)

@@ -1,0 +1,280 @@
+// Memory-bound kernels between the matrix products: embedding lookup, residual sum fused
+// with RMSNorm, the SwiGLU gate on partial sums, and per-head q/k norm + rotary + cache
+// write.  Statistics, angles and sums are 32-bit; outputs are rounded once.
+//
+// Formulas restate YuvGev00/mini-engine: src/mini_engine/model.py:59-69 (RMSNorm),
+// :72-90 (rotary, rotate-half), :113-116 (norm before rotation, v untouched), :130 (SwiGLU),
+// src/mini_engine/attention.py:118-121 (new K/V go to their slots before attention reads).
+#include "common.cuh"
+
+#include <algorithm>
+
+// ------------------------------------------------------------------------------ embedding
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int hidden, int vocab) {
+    const int token = blockIdx.x;
+    const int id = ids[token];
+    float* row_out = out + static_cast<size_t>(token) * hidden;
+    if (id < 0 || id >= vocab) {  // the host validates ids; never read outside the table
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = 0.0f;
+        return;
+    }
+    const T* row = table + static_cast<size_t>(id) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = to_float(row[i]);
+}
+
+ME_EXPORT int me_embedding(const void* table, int table_type, const int* ids, float* out, int tokens,
+                           int hidden, int vocab, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_type == ME_BF16)
+        embedding_kernel<<<tokens, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(table), ids, out,
+                                                         hidden, vocab);
+    else
+        embedding_kernel<<<tokens, threads, 0, stream>>>(static_cast<const float*>(table), ids, out, hidden,
+                                                         vocab);
+    return launch_status();
+}
+
+// --------------------------------------------------------------- residual sum + RMSNorm
+
+constexpr int NORM_THREADS = 256;
+
+// One block per output row.  x_row = x[src] + sum_s pending[s][src] (ascending s); when
+// `rows` is null the sum is written back to x (the residual stream advances), otherwise only
+// the listed rows are read and x is left alone.  out = weight * x_row * rsqrt(mean(x_row^2) + eps).
+template <typename OutT>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
+                   const float* __restrict__ weight, float eps, OutT* __restrict__ out,
+                   const int* __restrict__ rows, int hidden) {
+    extern __shared__ float row_cache[];  // [hidden]
+    __shared__ float warp_partial[NORM_THREADS / 32];
+    const int out_row = blockIdx.x;
+    const int src = rows ? rows[out_row] : out_row;
+    float* x_row = x + static_cast<size_t>(src) * hidden;
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
+        float v = x_row[i];
+        for (int s = 0; s < splits; ++s) v += pending[s * split_stride + static_cast<size_t>(src) * hidden + i];
+        row_cache[i] = v;
+        if (!rows && splits > 0) x_row[i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    sum_sq = warp_sum(sum_sq);
+    if ((threadIdx.x & 31) == 0) warp_partial[threadIdx.x >> 5] = sum_sq;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NORM_THREADS / 32; ++w) total += warp_partial[w];
+    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+    OutT* out_ptr = out + static_cast<size_t>(out_row) * hidden;
+    for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
+        out_ptr[i] = from_float<OutT>(weight[i] * (row_cache[i] * inv));
+}
+
+ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long long split_stride,
+                             const float* weight, float eps, void* out, int out_type, const int* rows,
+                             int count, int hidden, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    if (out_type == ME_BF16) {
+        auto kernel = add_rmsnorm_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, (size_t)split_stride, weight, eps,
+                                                      static_cast<__nv_bfloat16*>(out), rows, hidden);
+    } else {
+        auto kernel = add_rmsnorm_kernel<float>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, (size_t)split_stride, weight, eps,
+                                                      static_cast<float*>(out), rows, hidden);
+    }
+    return launch_status();
+}
+
+// --------------------------------------------------------------------------------- SwiGLU
+
+// partial[s][t][0..inter) are gate sums, [inter..2*inter) up sums.  out = silu(gate) * up.
+template <typename OutT>
+__global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
+                              OutT* __restrict__ out, int tokens, int inter) {
+    const size_t total = static_cast<size_t>(tokens) * inter;
+    for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t t = idx / inter;
+        const size_t i = idx - t * inter;
+        const float* base = partial + t * 2 * inter;
+        float gate = 0.0f, up = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            gate += base[s * split_stride + i];
+            up += base[s * split_stride + inter + i];
+        }
+        const float activated = gate / (1.0f + expf(-gate));
+        out[idx] = from_float<OutT>(activated * up);
+    }
+}
+
+ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride, void* out, int out_type,
+                        int tokens, int inter, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const size_t total = static_cast<size_t>(tokens) * inter;
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+    if (out_type == ME_BF16)
+        swiglu_kernel<<<blocks, threads, 0, stream>>>(partial, splits, (size_t)split_stride,
+                                                      static_cast<__nv_bfloat16*>(out), tokens, inter);
+    else
+        swiglu_kernel<<<blocks, threads, 0, stream>>>(partial, splits, (size_t)split_stride,
+                                                      static_cast<float*>(out), tokens, inter);
+    return launch_status();
+}
+
+// ------------------------------------------------- per-head norm + rotary + cache write
+
+// One warp per (token, head) over the columns of qkv = [q heads | k heads | v heads].
+//   q heads: optional RMSNorm over head_dim, optional rotation, written to q_out[t][h][:].
+//   k heads: the same, written to the token's slot of k_pages (or to k_dense[t][h][:]).
+//   v heads: copied to the slot of v_pages (or v_dense).
+// Pages are [page][kv_head][slot in page][head_dim]; slot_mapping[t] = page * page_size + slot,
+// negative for a token whose keys are not to be stored.
+struct QkvArgs {
+    const float* qkv;     // [splits][tokens][(heads + 2 kv_heads) * head_dim]
+    int splits;
+    size_t split_stride;
+    const float* q_weight;  // [head_dim] or null: no norm
+    const float* k_weight;
+    float eps;
+    const float* inv_freq;  // [head_dim / 2] or null: no rotation
+    const int* positions;
+    const int* slot_mapping;  // null: dense outputs
+    void* q_out;
+    void* k_pages;
+    void* v_pages;
+    void* k_dense;
+    void* v_dense;
+    int tokens, heads, kv_heads, head_dim, page_size;
+};
+
+constexpr int QKV_WARPS = 4;
+constexpr int MAX_HEAD_DIM = 512;
+
+template <typename OutT>
+__global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvArgs a) {
+    extern __shared__ float staged[];  // [QKV_WARPS][head_dim]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = a.heads + 2 * a.kv_heads;
+    const long long item = static_cast<long long>(blockIdx.x) * QKV_WARPS + warp;
+    if (item >= static_cast<long long>(a.tokens) * heads_total) return;
+    const int token = static_cast<int>(item / heads_total);
+    const int column_head = static_cast<int>(item % heads_total);
+    const int d = a.head_dim, half = d / 2;
+    float* vec = staged + warp * d;
+
+    const size_t row_width = static_cast<size_t>(heads_total) * d;
+    const float* src = a.qkv + static_cast<size_t>(token) * row_width + static_cast<size_t>(column_head) * d;
+    float sum_sq = 0.0f;
+    for (int i = lane; i < d; i += 32) {
+        float v = 0.0f;
+        for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        vec[i] = v;
+        sum_sq = fmaf(v, v, sum_sq);
+    }
+    const bool is_q = column_head < a.heads;
+    const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
+    const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+    float inv = 1.0f;
+    if (weight) {
+        sum_sq = warp_sum(sum_sq);
+        inv = rsqrtf(sum_sq / static_cast<float>(d) + a.eps);
+    }
+    __syncwarp();
+
+    OutT* dst;
+    if (is_q) {
+        dst = static_cast<OutT*>(a.q_out) + (static_cast<size_t>(token) * a.heads + column_head) * d;
+    } else {
+        const int kv_head = is_k ? column_head - a.heads : column_head - a.heads - a.kv_heads;
+        if (a.slot_mapping) {
+            const int slot = a.slot_mapping[token];
+            if (slot < 0) return;
+            const size_t page = slot / a.page_size, offset = slot % a.page_size;
+            OutT* pages = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages);
+            dst = pages + ((page * a.kv_heads + kv_head) * a.page_size + offset) * d;
+        } else {
+            OutT* dense = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense);
+            dst = dense + (static_cast<size_t>(token) * a.kv_heads + kv_head) * d;
+        }
+    }
+    const bool rotate = (is_q || is_k) && a.inv_freq != nullptr;
+    const float position = rotate ? static_cast<float>(a.positions[token]) : 0.0f;
+    for (int i = lane; i < d; i += 32) {
+        float value = weight ? weight[i] * (vec[i] * inv) : vec[i];
+        if (rotate) {
+            // rotate-half: out[i] = x[i] cos - x[i + half] sin (i < half); x[i] cos + x[i - half] sin.
+            const int j = i < half ? i + half : i - half;
+            const float other = weight ? weight[j] * (vec[j] * inv) : vec[j];
+            const float angle = position * a.inv_freq[i < half ? i : i - half];
+            float sine, cosine;
+            sincosf(angle, &sine, &cosine);
+            value = i < half ? value * cosine - other * sine : value * cosine + other * sine;
+        }
+        dst[i] = from_float<OutT>(value);
+    }
+}
+
+ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long split_stride, const float* q_weight,
+                                    const float* k_weight, float eps, const float* inv_freq,
+                                    const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
+                                    void* v_pages, void* k_dense, void* v_dense, int out_type, int tokens,
+                                    int heads, int kv_heads, int head_dim, int page_size, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim > MAX_HEAD_DIM || head_dim % 2) return ME_ERR_UNSUPPORTED;
+    QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, inv_freq, positions, slot_mapping,
+              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size};
+    const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
+    const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
+    const size_t smem = static_cast<size_t>(QKV_WARPS) * head_dim * sizeof(float);
+    if (out_type == ME_BF16)
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+    else
+        qk_norm_rope_store_kernel<float><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+    return launch_status();
+}
+
+// Dense [tokens][kv_heads][head_dim] keys and values into their slots of the pages.
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ k_dense, const T* __restrict__ v_dense,
+                                const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
+                                T* __restrict__ v_pages, int kv_heads, int head_dim, int page_size) {
+    const int token = blockIdx.x;
+    const int slot = slot_mapping[token];
+    if (slot < 0) return;
+    const size_t page = slot / page_size, offset = slot % page_size;
+    const int width = kv_heads * head_dim;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const int head = i / head_dim, e = i % head_dim;
+        const size_t dst = ((page * kv_heads + head) * page_size + offset) * head_dim + e;
+        k_pages[dst] = k_dense[static_cast<size_t>(token) * width + i];
+        v_pages[dst] = v_dense[static_cast<size_t>(token) * width + i];
+    }
+}
+
+ME_EXPORT int me_kv_store(const void* k_dense, const void* v_dense, const int* slot_mapping, void* k_pages,
+                          void* v_pages, int type, int tokens, int kv_heads, int head_dim, int page_size,
+                          cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (type == ME_BF16)
+        kv_store_kernel<<<tokens, 128, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(k_dense), static_cast<const __nv_bfloat16*>(v_dense), slot_mapping,
+            static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), kv_heads, head_dim,
+            page_size);
+    else
+        kv_store_kernel<<<tokens, 128, 0, stream>>>(static_cast<const float*>(k_dense),
+                                                    static_cast<const float*>(v_dense), slot_mapping,
+                                                    static_cast<float*>(k_pages), static_cast<float*>(v_pages),
+                                                    kv_heads, head_dim, page_size);
+    return launch_status();
+}

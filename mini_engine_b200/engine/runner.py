@@ -1,0 +1,209 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.execute`` takes entries that may be whole prompts, portions of prompts cut
+anywhere, and single decoded tokens, side by side.  It runs only the tokens it is given, as
+one flat batch, reading everything earlier from the cache, writes the new tokens' keys and
+values into their pages, and returns the logits at the wanted places.  It changes no host
+state: counting computed tokens, hashing pages and freeing belong to the caller (the
+scheduler's ``postprocess``, or the replay program), which is what lets a trace drive it
+directly.
+
+The reference's counterpart is ``LLMEngine._prepare`` plus the model call
+(src/mini_engine/engine.py:200-226, src/mini_engine/attention.py:56-101 of
+YuvGev00/mini-engine): there the batch becomes about ten small int64 tensors built token by
+token; here it is one int32 block in pinned memory and one host-to-device copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence as Seq
+
+import numpy as np
+import torch
+
+from mini_engine_b200.cache.manager import NULL_PAGE, RequestCache
+from mini_engine_b200.cache.storage import CacheLayout, allocate_cache
+from mini_engine_b200.engine.workspace import Workspace
+from mini_engine_b200.parts.base import StepContext
+from mini_engine_b200.parts.model import DecoderModel
+
+
+@dataclass
+class StepEntry:
+    """Tokens ``[start, start + len(token_ids))`` of one request."""
+
+    cache: RequestCache
+    start: int
+    token_ids: Seq[int]
+    want: Seq[int] = field(default_factory=tuple)  # places among these tokens whose logits are returned
+
+
+class ModelRunner:
+    def __init__(
+        self,
+        model: DecoderModel,
+        *,
+        dtype: torch.dtype,
+        num_blocks: int,
+        block_size: int,
+        max_num_seqs: int,
+        max_num_batched_tokens: int,
+        max_model_len: int,
+        device: str = "cuda",
+    ):
+        if not torch.cuda.is_available():
+            raise RuntimeError("mini_engine_b200 runs on a CUDA device only; none is available")
+        self.model = model
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.block_size = block_size
+        self.num_blocks = num_blocks
+        self.max_entries = max_num_seqs
+        self.max_tokens = max_num_batched_tokens
+        self.table_width = -(-max_model_len // block_size)
+        self.vocab_size = model.spec.vocab_size
+        self.layout: CacheLayout = allocate_cache(
+            model.cache_needs(), num_blocks, block_size, max_num_seqs, dtype, self.device
+        )
+        self.num_groups = len(self.layout.groups)
+        self.workspace = Workspace(max_num_batched_tokens, self.device)
+        self.spare_page = num_blocks  # owned by no request: padding rows write and read here
+        self.spare_slot = max_num_seqs
+        # One int32 block holds every index array of a step; two pinned copies alternate so a
+        # step never overwrites what an earlier copy may still be reading.
+        g, t, b = self.num_groups, self.max_tokens, self.max_entries
+        self._capacity = (3 + g) * t + (4 * b + 1) + t + g * b * self.table_width
+        self._host = [torch.empty(self._capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._host_np = [h.numpy() for h in self._host]
+        self._device = torch.zeros(self._capacity, dtype=torch.int32, device=self.device)
+        self._flip = 0
+
+    # ------------------------------------------------------------------ packing
+
+    def pack(self, entries: Seq[StepEntry], pad_entries_to: int | None = None) -> tuple[StepContext, torch.Tensor]:
+        """Lay the batch out as int32 arrays on the device.  With ``pad_entries_to`` the batch
+        is filled up with one-token dummy entries on the spare page (for a captured graph of
+        that size).  Returns the context and the int32 row numbers of the wanted logits."""
+        real = len(entries)
+        total_entries = max(real, pad_entries_to or 0)
+        counts = [len(e.token_ids) for e in entries]
+        if real == 0 or min(counts) < 1:
+            raise ValueError("a step needs at least one entry and every entry at least one token")
+        real_tokens = sum(counts)
+        tokens = real_tokens + (total_entries - real)
+        if tokens > self.max_tokens or total_entries > self.max_entries:
+            raise ValueError(
+                f"step of {tokens} tokens / {total_entries} entries exceeds the capacity "
+                f"({self.max_tokens} tokens, {self.max_entries} entries)"
+            )
+        g, bs, width = self.num_groups, self.block_size, self.table_width
+        self._flip ^= 1
+        host = self._host_np[self._flip]
+        offset = 0
+
+        def take(n: int) -> tuple[np.ndarray, int]:
+            nonlocal offset
+            view, start = host[offset : offset + n], offset
+            offset += n
+            return view, start
+
+        ids, o_ids = take(tokens)
+        pos, o_pos = take(tokens)
+        ent, o_ent = take(tokens)
+        slots = [take(tokens) for _ in range(g)]
+        cu, o_cu = take(total_entries + 1)
+        ctx_len, o_ctx = take(total_entries)
+        state, o_state = take(total_entries)
+        fresh, o_fresh = take(total_entries)
+        tables = [take(total_entries * width) for _ in range(g)]
+        wanted_rows: list[int] = []
+
+        cursor = 0
+        cu[0] = 0
+        max_q = max_ctx = 1
+        for b, entry in enumerate(entries):
+            n = counts[b]
+            end = entry.start + n
+            if end > width * bs:
+                raise ValueError(f"request of {end} tokens exceeds max_model_len {width * bs}")
+            ids[cursor : cursor + n] = entry.token_ids
+            span = np.arange(entry.start, end, dtype=np.int32)
+            pos[cursor : cursor + n] = span
+            ent[cursor : cursor + n] = b
+            for gi in range(g):
+                table = np.asarray(entry.cache.block_tables[gi], dtype=np.int32)
+                if table.shape[0] * bs < end:
+                    raise ValueError(f"entry {b}: block table covers {table.shape[0] * bs} tokens, {end} needed")
+                pages = table[span // bs]
+                if (pages == NULL_PAGE).any():
+                    raise ValueError(f"entry {b}: a new token falls on a page that was given back")
+                slots[gi][0][cursor : cursor + n] = pages * bs + span % bs
+                row = tables[gi][0][b * width : (b + 1) * width]
+                row[: table.shape[0]] = table
+                row[table.shape[0] :] = NULL_PAGE
+            cu[b + 1] = cursor + n
+            ctx_len[b] = end
+            state[b] = entry.cache.state_slot if entry.cache.state_slot >= 0 else self.spare_slot
+            fresh[b] = 1 if entry.start == 0 else 0
+            for place in entry.want:
+                if not 0 <= place < n:
+                    raise ValueError(f"entry {b}: wanted place {place} is outside its {n} tokens")
+                wanted_rows.append(cursor + place)
+            max_q, max_ctx = max(max_q, n), max(max_ctx, end)
+            cursor += n
+        if ids[:real_tokens].min() < 0 or ids[:real_tokens].max() >= self.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        for b in range(real, total_entries):  # padding: one token at position 0 of the spare page
+            ids[cursor], pos[cursor], ent[cursor] = 0, 0, b
+            for gi in range(g):
+                slots[gi][0][cursor] = self.spare_page * bs
+                row = tables[gi][0][b * width : (b + 1) * width]
+                row[:] = self.spare_page
+            cu[b + 1] = cursor + 1
+            ctx_len[b], state[b], fresh[b] = 1, self.spare_slot, 1
+            cursor += 1
+        rows_view, o_rows = take(len(wanted_rows))
+        rows_view[:] = wanted_rows
+
+        used = offset
+        self._device[:used].copy_(self._host[self._flip][:used], non_blocking=True)
+        dev = self._device
+
+        def at(start: int, n: int) -> torch.Tensor:
+            return dev[start : start + n]
+
+        ctx = StepContext(
+            dtype=self.dtype,
+            num_tokens=tokens,
+            num_entries=total_entries,
+            max_query_len=max_q,
+            max_context_len=max_ctx,
+            token_ids=at(o_ids, tokens),
+            positions=at(o_pos, tokens),
+            entry_of_token=at(o_ent, tokens),
+            cu_tokens=at(o_cu, total_entries + 1),
+            context_lens=at(o_ctx, total_entries),
+            state_slots=at(o_state, total_entries),
+            fresh=at(o_fresh, total_entries),
+            slot_mapping=[at(s[1], tokens) for s in slots],
+            block_tables=[at(t[1], total_entries * width).view(total_entries, width) for t in tables],
+            page_size=bs,
+            workspace=self.workspace,
+            all_decode=max_q == 1,
+            host={
+                "counts": counts + [1] * (total_entries - real),
+                "starts": [e.start for e in entries] + [0] * (total_entries - real),
+            },
+        )
+        return ctx, at(o_rows, len(wanted_rows))
+
+    # --------------------------------------------------------------------- step
+
+    @torch.inference_mode()
+    def execute(self, entries: Seq[StepEntry]) -> torch.Tensor:
+        """Float32 logits ``[wanted, vocab]`` on the device, in the order of the entries and
+        of each entry's ``want``.  The tensor is a view of a buffer that the next step
+        overwrites."""
+        ctx, rows = self.pack(entries)
+        return self.model.forward(ctx, self.layout.views, rows)

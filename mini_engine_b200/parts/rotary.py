@@ -1,0 +1,45 @@
+"""Rotary position encoding (rotate-half) as a part.
+
+``inv_freq[i] = 1 / theta**(2i/d)`` is formed in float32 on the host exactly as the
+reference does (src/mini_engine/model.py:75 of YuvGev00/mini-engine); the angle
+``position * inv_freq`` and its cosine and sine are evaluated in 32-bit inside the
+attention mixer's fused kernel (:79-90).  Unlike the reference, whose frequency buffer is
+cast to bfloat16 together with the module (src/mini_engine/engine.py:63), the table stays
+float32 in every mode.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from mini_engine_b200.parts.base import PositionEncoding, register
+
+
+@register("position_encoding", "rope")
+class RotaryEncoding(PositionEncoding):
+    def __init__(self, prefix: str, hidden_size: int, *, head_dim: int, theta: float):
+        if head_dim % 2:
+            raise ValueError(f"rotate-half RoPE needs an even head_dim, got {head_dim}")
+        self.head_dim = head_dim
+        self.theta = float(theta)
+        self._table: torch.Tensor | None = None
+
+    def inv_freq(self) -> torch.Tensor:
+        exponents = torch.arange(0, self.head_dim, 2, dtype=torch.float32) / self.head_dim
+        return 1.0 / (self.theta**exponents)
+
+    def fused_rotary_table(self) -> torch.Tensor:
+        if self._table is None:
+            self._table = self.inv_freq().to("cuda")
+        return self._table
+
+
+@register("position_encoding", "none")
+class NoEncoding(PositionEncoding):
+    """Queries and keys are used as projected (and normalised)."""
+
+    def __init__(self, prefix: str, hidden_size: int):
+        pass
+
+    def apply(self, q, k, positions) -> None:
+        return None

@@ -1,0 +1,57 @@
+"""The two tiny Qwen3-dense configurations that the tests run, and seeded inputs.
+
+They differ in every size and option: layers, width, head count and group size, head size,
+feed-forward width (no power of two in B), vocabulary, rope theta, the norms' eps, tied or
+untied head, and the page size they are run with.
+"""
+
+from __future__ import annotations
+
+import json
+import random
+from pathlib import Path
+
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 64,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "head_dim": 16,
+    "intermediate_size": 128,
+    "vocab_size": 256,
+    "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 512,
+    "hidden_act": "silu",
+}
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 3,
+    "hidden_size": 96,
+    "num_attention_heads": 8,
+    "num_key_value_heads": 2,
+    "head_dim": 32,
+    "intermediate_size": 160,
+    "vocab_size": 384,
+    "rope_parameters": {"rope_type": "default", "rope_theta": 1000000.0},
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 1024,
+    "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8}
+CONFIGS = {"A": TINY_A, "B": TINY_B}
+
+
+def random_ids(seed: int, count: int, vocab: int) -> list[int]:
+    rng = random.Random(seed)
+    return [rng.randrange(vocab) for _ in range(count)]
+
+
+def write_config(folder: Path, raw: dict) -> None:
+    folder.mkdir(parents=True, exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(raw, indent=2))
