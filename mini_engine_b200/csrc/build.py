@@ -54,8 +54,20 @@ def _nvcc() -> str:
     return found
 
 
+_build_dir_cached: Path | None = None
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> Path:
     """``_build`` beside the sources if writable, else a folder under the temp directory."""
+    global _build_dir_cached
+    with _dir_lock:
+        if _build_dir_cached is None:
+            _build_dir_cached = _find_build_dir()
+        return _build_dir_cached
+
+
+def _find_build_dir() -> Path:
     override = os.environ.get("MINI_ENGINE_B200_BUILD_DIR")
     candidates = [Path(override)] if override else []
     candidates.append(SOURCE_DIR / "_build")

@@ -25,6 +25,77 @@ PAGE_SIZE = 16  # tokens per page; --max-tokens counts requests rounded up to 64
 MAX_LIVE = 4
 
 
+class Replayer:
+    """The model, its step function and a cache manager whose pool holds ``max_tokens``."""
+
+    def __init__(
+        self,
+        model_dir: str | Path,
+        dtype: torch.dtype,
+        max_tokens: int,
+        block_size: int = PAGE_SIZE,
+        max_step_tokens: int | None = None,
+    ):
+        from mini_engine_b200.cache.manager import CacheManager
+        from mini_engine_b200.engine.loading import load_model
+        from mini_engine_b200.engine.runner import ModelRunner
+
+        self.block_size = block_size
+        self.num_blocks = max(-(-max_tokens // block_size), 1)
+        _arch, self.config, model = load_model(model_dir, dtype)
+        self.runner = ModelRunner(
+            model,
+            dtype=dtype,
+            num_blocks=self.num_blocks,
+            block_size=block_size,
+            max_num_seqs=MAX_LIVE * 2,
+            max_num_batched_tokens=max_step_tokens or max(max_tokens, 64),
+            max_model_len=self.num_blocks * block_size,
+        )
+        self.manager = CacheManager(
+            self.runner.layout.groups,
+            self.num_blocks,
+            block_size,
+            max_num_seqs=MAX_LIVE * 2,
+            enable_prefix_caching=False,
+            has_state=self.runner.layout.has_state,
+        )
+        self.live: dict[str, list] = {}  # id -> [RequestCache, tokens held]
+
+    def step(self, record: dict) -> torch.Tensor | None:
+        """Run one step record; return the wanted logits ``[wanted, vocab]`` on the host, or
+        ``None`` when nothing was wanted."""
+        from mini_engine_b200.engine.runner import StepEntry
+
+        entries = []
+        for item in record.get("entries", []):
+            name = item["id"]
+            if name not in self.live:
+                self.live[name] = [self.manager.new_request(), 0]
+            cache, held = self.live[name]
+            tokens = [int(t) for t in item["tokens"]]
+            if not self.manager.try_allocate(cache, held + len(tokens)):
+                raise MemoryError(
+                    f"step {record.get('step')}: request {name!r} needs {held + len(tokens)} tokens but the "
+                    f"pool of {self.num_blocks * self.block_size} tokens (--max-tokens) is exhausted"
+                )
+            entries.append(StepEntry(cache, held, tokens, tuple(item.get("want", ()))))
+            self.live[name][1] = held + len(tokens)
+        result = None
+        if entries:
+            logits = self.runner.execute(entries)
+            if logits.shape[0]:
+                result = logits.to("cpu")
+            else:
+                torch.cuda.synchronize()
+            for entry in entries:
+                self.manager.release_behind_window(entry.cache, entry.start + len(entry.token_ids))
+        for name in record.get("end", []):
+            if name in self.live:
+                self.manager.free(self.live.pop(name)[0])
+        return result
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -35,70 +106,23 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-step-tokens", type=int, default=None, help="most tokens in one step")
     args = parser.parse_args(argv)
 
-    from mini_engine_b200.cache.manager import CacheManager
-    from mini_engine_b200.engine.loading import load_model
-    from mini_engine_b200.engine.runner import ModelRunner, StepEntry
-
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
-    block_size = args.block_size
-    num_blocks = max(-(-args.max_tokens // block_size), 1)
-    step_tokens = args.max_step_tokens or max(args.max_tokens, 64)
-    _arch, _config, model = load_model(args.model, dtype)
-    runner = ModelRunner(
-        model,
-        dtype=dtype,
-        num_blocks=num_blocks,
-        block_size=block_size,
-        max_num_seqs=MAX_LIVE * 2,
-        max_num_batched_tokens=step_tokens,
-        max_model_len=num_blocks * block_size,
-    )
-    manager = CacheManager(
-        runner.layout.groups,
-        num_blocks,
-        block_size,
-        max_num_seqs=MAX_LIVE * 2,
-        enable_prefix_caching=False,
-        has_state=runner.layout.has_state,
-    )
-    live: dict[str, tuple] = {}  # id -> (RequestCache, tokens so far)
-
+    replayer = Replayer(args.model, dtype, args.max_tokens, args.block_size, args.max_step_tokens)
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         record = json.loads(line)
-        step = record["step"]
-        entries = []
-        for item in record.get("entries", []):
-            name = item["id"]
-            if name not in live:
-                live[name] = (manager.new_request(), 0)
-            cache, held = live[name]
-            tokens = [int(t) for t in item["tokens"]]
-            if not manager.try_allocate(cache, held + len(tokens)):
-                print(
-                    f"error: step {step}: request {name!r} needs {held + len(tokens)} tokens but the pool of "
-                    f"{num_blocks * block_size} (--max-tokens) is exhausted",
-                    file=sys.stderr,
-                )
-                return 2
-            entries.append(StepEntry(cache, held, tokens, tuple(item.get("want", ()))))
-            live[name] = (cache, held + len(tokens))
-        if entries:
-            logits = runner.execute(entries)
-            if logits.shape[0]:
-                logits.to("cpu").contiguous().numpy().astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
-            else:
-                torch.cuda.synchronize()
-            for entry in entries:
-                manager.release_behind_window(entry.cache, entry.start + len(entry.token_ids))
-        for name in record.get("end", []):
-            if name in live:
-                manager.free(live.pop(name)[0])
-        print(f"done {step}", flush=True)
+        try:
+            logits = replayer.step(record)
+        except MemoryError as error:
+            print(f"error: {error}", file=sys.stderr)
+            return 2
+        if logits is not None:
+            logits.contiguous().numpy().astype("<f4", copy=False).tofile(out_dir / f"{record['step']}.f32")
+        print(f"done {record['step']}", flush=True)
     return 0
 
 
