@@ -1,0 +1,372 @@
+// y = x W^T in bfloat16 on the 5th-generation tensor cores of sm_100a: TMA loads into
+// 128-byte-swizzled shared memory, tcgen05.mma with the accumulator in tensor memory,
+// tcgen05.ld for the epilogue.
+//
+// Orientation.  The weight W [out, in] (the checkpoint's layout, src/mini_engine/model.py:97-100
+// of YuvGev00/mini-engine) is the 128-row A operand; the tokens x [T, in] are the B operand
+// with N = BLOCK_T in {16, ..., 256}.  The accumulator D[out row][token] therefore has one
+// output feature per TMEM lane and one token per column, and the same kernel serves a
+// 2,048-token prompt (BLOCK_T = 256) and a single decoded token (BLOCK_T = 16), where it
+// streams the weight through shared memory at the rate of HBM.
+//
+// Work split.  grid = (out tiles, token tiles, k splits).  With few tokens there are too few
+// output tiles to occupy 148 SMs, so the reduction axis is cut into `splits` ranges of 64-wide
+// k blocks; split s writes its partial sum to out[s][T][out] and the consumer kernel adds the
+// partials in ascending s.  Nothing is added atomically: results are reproducible.
+//
+// Roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and issues the
+// MMAs, warps 2-5 read the accumulator (each warp its own 32 lanes) and store.  Stages are
+// handed over with mbarriers: full[s] (TMA bytes arrived), empty[s] (tcgen05.commit: the MMAs
+// that read stage s retired), accum (all MMAs retired).
+//
+// DUAL mode computes silu(x Wg^T) * (x Wu^T) (src/mini_engine/model.py:130): Wg and Wu tiles
+// of the same 128 output features are loaded side by side, accumulate into two column ranges
+// of tensor memory, and the epilogue applies the gate lane by lane, so the [T, 2 * inter]
+// intermediate never exists.
+//
+// Every wait is bounded: after a limit of polls and of time a role records an error code in a device
+// flag that the host reads, stops, and the CTA still frees its tensor memory and exits.
+#include <cuda.h>
+
+#include "common.cuh"
+
+constexpr int BLOCK_N = 128;  // output features per CTA = UMMA M
+constexpr int BLOCK_K = 64;   // one 128-byte swizzle row of bfloat16
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;           // polls
+constexpr long long WAIT_CYCLES = 3000000000ll;      // and about 1.5 s of SM clock, whichever ends first
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+__device__ int g_gemm_error = 0;  // 0 ok; else (role << 8) | detail of the first failure seen
+
+// ------------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const long long started = clock64();
+    for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && clock64() - started > WAIT_CYCLES) break;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int inner, int row, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(inner), "r"(row), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_alloc(uint32_t* holder, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major bfloat16 tile whose rows are 128 bytes
+// (BLOCK_K = 64) in the 128-byte swizzle that TMA wrote: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t address) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((address & 0x3FFFF) >> 4);  // start address, bits [0,14)
+    desc |= static_cast<uint64_t>(1) << 16;                     // leading byte offset (unused for swizzled K-major)
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset, bits [32,46)
+    desc |= static_cast<uint64_t>(1) << 46;                     // descriptor version of sm_100
+    desc |= static_cast<uint64_t>(2) << 61;                     // SWIZZLE_128B
+    return desc;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(BLOCK_N >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------ kernel
+
+template <int BLOCK_T, bool DUAL>
+struct Config {
+    static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2 * (DUAL ? 2 : 1);
+    static constexpr int B_BYTES = BLOCK_T * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+    static constexpr int ACC_COLUMNS = BLOCK_T * (DUAL ? 2 : 1);
+    static constexpr int TMEM_COLUMNS = ACC_COLUMNS < 32 ? 32 : ACC_COLUMNS;  // powers of two here
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+struct GemmParams {
+    void* out;            // float [splits][tokens][outs], or bfloat16 [tokens][outs] in DUAL mode
+    int tokens, outs, k_blocks, k_blocks_per_split;
+    int dual_row_offset;  // row of W where the second (up) half starts
+};
+
+template <int BLOCK_T, bool DUAL>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    using C = Config<BLOCK_T, DUAL>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* accum = empty + C::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * BLOCK_T, split = blockIdx.z;
+    const int kb_begin = split * p.k_blocks_per_split;
+    const int kb_end = min(kb_begin + p.k_blocks_per_split, p.k_blocks);
+    const int iterations = kb_end - kb_begin;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(tmem_holder, C::TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < iterations; ++i, ++issued) {
+                const int stage = i % C::STAGES;
+                const uint32_t parity = (i / C::STAGES) & 1;
+                if (!mbar_wait(&empty[stage], parity ^ 1)) { atomicCAS(&g_gemm_error, 0, (1 << 8) | stage); break; }
+                uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
+                uint8_t* b_tile = a_tile + C::A_BYTES;
+                mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(a_tile, &map_w, k, n0, &full[stage]);
+                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d(b_tile, &map_x, k, t0, &full[stage]);
+            }
+            // Copies still in flight must land before the CTA's shared memory is released.  On
+            // the normal path the MMA warp has waited for every one of them already.
+            if (issued < iterations || g_gemm_error != 0) {
+                for (int i = max(issued - C::STAGES, 0); i < issued; ++i)
+                    mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BLOCK_T);
+            bool ok = true;
+            for (int i = 0; i < iterations && ok; ++i) {
+                const int stage = i % C::STAGES;
+                const uint32_t parity = (i / C::STAGES) & 1;
+                if (!mbar_wait(&full[stage], parity)) { atomicCAS(&g_gemm_error, 0, (2 << 8) | stage); ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + C::A_BYTES;
+                const uint64_t a_desc = smem_desc_sw128(a_addr);
+                const uint64_t b_desc = smem_desc_sw128(b_addr);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t step = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);  // 32 bytes per k step
+                    const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+                    tcgen05_mma_bf16(tmem_base, a_desc + step, b_desc + step, idesc, accumulate);
+                    if (DUAL) {
+                        const uint64_t a2_desc = smem_desc_sw128(a_addr + BLOCK_N * BLOCK_K * 2);
+                        tcgen05_mma_bf16(tmem_base + BLOCK_T, a2_desc + step, b_desc + step, idesc, accumulate);
+                    }
+                }
+                tcgen05_commit(&empty[stage]);  // arrives when the MMAs above no longer read the stage
+            }
+            tcgen05_commit(accum);
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;  // a warp may read TMEM lanes [32 * (warp % 4), +32)
+        const int n = n0 + quarter * 32 + lane;
+        bool ok = mbar_wait(accum, 0);
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (3 << 8));
+        ok = __all_sync(0xffffffffu, ok) && g_gemm_error == 0;
+        tcgen05_fence_after();
+        if (ok && iterations > 0) {
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            if (!DUAL) {
+                float* out = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.tokens * p.outs;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_T; c0 += 16) {
+                    if (t0 + c0 >= p.tokens) break;  // uniform: the rest of the tile is padding
+                    float v[16];
+                    tcgen05_ld16(lane_base + c0, v);
+                    if (n < p.outs) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = t0 + c0 + c;
+                            if (t < p.tokens) out[static_cast<size_t>(t) * p.outs + n] = v[c];
+                        }
+                    }
+                }
+            } else {
+                __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_T; c0 += 16) {
+                    if (t0 + c0 >= p.tokens) break;
+                    float gate[16], up[16];
+                    tcgen05_ld16(lane_base + c0, gate);
+                    tcgen05_ld16(lane_base + BLOCK_T + c0, up);
+                    if (n < p.outs) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = t0 + c0 + c;
+                            if (t < p.tokens) {
+                                const float activated = gate[c] / (1.0f + expf(-gate[c]));
+                                out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem_base, C::TMEM_COLUMNS);
+}
+
+// -------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(entry);
+    }
+    return fn;
+}
+
+// A [rows][inner] bfloat16 matrix, tiles of box_rows x 64 in the 128-byte swizzle.  `out` is
+// 128 bytes.  Elements outside the matrix read as zero.
+ME_EXPORT int me_make_tensor_map(void* out, const void* base, unsigned long long rows, unsigned long long inner,
+                                 unsigned int box_rows) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return ME_ERR_UNSUPPORTED;
+    if (inner % 8 != 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0 || box_rows > 256) return ME_ERR_ARGUMENT;
+    alignas(64) CUtensorMap map;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {inner * 2};
+    const cuuint32_t box[2] = {BLOCK_K, box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult result = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                   element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS) return ME_ERR_ARGUMENT;
+    memcpy(out, &map, sizeof(map));
+    return 0;
+}
+
+template <int BLOCK_T, bool DUAL>
+static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, int splits, cudaStream_t stream) {
+    using C = Config<BLOCK_T, DUAL>;
+    auto kernel = gemm_tcgen05_kernel<BLOCK_T, DUAL>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid((p.outs + BLOCK_N - 1) / BLOCK_N, (p.tokens + BLOCK_T - 1) / BLOCK_T, splits);
+    kernel<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(map_w, map_x, p);
+    return launch_status();
+}
+
+// out[s][t][n] (float32) = sum over the k blocks of split s of x[t][k] * w[n][k].
+ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, int tokens, int outs, int inner,
+                              int block_t, int splits, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0};
+    if (splits < 1 || splits > p.k_blocks) return ME_ERR_ARGUMENT;
+    p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
+    if ((splits - 1) * p.k_blocks_per_split >= p.k_blocks) return ME_ERR_ARGUMENT;  // an empty split
+    switch (block_t) {
+        case 16: return launch<16, false>(w, x, p, splits, stream);
+        case 32: return launch<32, false>(w, x, p, splits, stream);
+        case 64: return launch<64, false>(w, x, p, splits, stream);
+        case 128: return launch<128, false>(w, x, p, splits, stream);
+        case 256: return launch<256, false>(w, x, p, splits, stream);
+        default: return ME_ERR_ARGUMENT;
+    }
+}
+
+// act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.
+ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,
+                                     int dual_row_offset, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset};
+    p.k_blocks_per_split = p.k_blocks;
+    return launch<128, true>(w, x, p, 1, stream);
+}
+
+// The first failure a kernel of this library recorded since the last call (0: none); clears it.
+ME_EXPORT int me_gemm_take_error(int* code) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(code, g_gemm_error, sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (*code != 0) e = cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    return static_cast<int>(e);
+}

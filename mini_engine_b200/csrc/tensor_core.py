@@ -1,11 +1,149 @@
-"""Host side of the TMA + tcgen05 matrix product (placeholder until the kernel is bound)."""
+"""Host side of the TMA + tcgen05 matrix product: tensor maps, tile and split choice, launch.
+
+A :class:`GemmPlan` is made once per weight and holds its TMA descriptor.  Descriptors of
+activations are cached by (address, rows, width, tile), which is stable because activations
+live in the engine's persistent workspace.
+"""
 
 from __future__ import annotations
 
+import ctypes
+from ctypes import c_int, c_uint, c_ulonglong, c_void_p
+
+import torch
+
+from mini_engine_b200.csrc.build import load_library
+
+NUM_SMS = 148
+BLOCK_N = 128
+BLOCK_K = 64
+TOKEN_TILES = (16, 32, 64, 128, 256)
+SPLIT_MAX_TOKENS = 64  # products of more tokens have enough tiles without splitting
+MIN_K_BLOCKS_PER_SPLIT = 4
+
+_lib = None
+
+
+def _library():
+    global _lib
+    if _lib is None:
+        lib = load_library("gemm_tcgen05")
+        lib.me_make_tensor_map.argtypes = [c_void_p, c_void_p, c_ulonglong, c_ulonglong, c_uint]
+        lib.me_make_tensor_map.restype = c_int
+        lib.me_gemm_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05.restype = c_int
+        lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_swiglu.restype = c_int
+        lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
+        lib.me_gemm_take_error.restype = c_int
+        _lib = lib
+    return _lib
+
 
 def supports(outs: int, inner: int) -> bool:
-    return False
+    """TMA wants a 16-byte row pitch: ``inner`` a multiple of 8 bfloat16 values."""
+    return inner % 8 == 0 and inner >= 8 and outs >= 1
+
+
+def token_tile(tokens: int) -> int:
+    for tile in TOKEN_TILES:
+        if tokens <= tile:
+            return tile
+    return TOKEN_TILES[-1]
 
 
 def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> int:
-    return 1
+    """How many ranges the reduction axis is cut into.  It depends on the sizes only (for a
+    given number of tokens the same split is always chosen), and no split is empty."""
+    if tokens > SPLIT_MAX_TOKENS:
+        return 1
+    tiles = -(-outs // BLOCK_N) * -(-tokens // token_tile(tokens))
+    k_blocks = -(-inner // BLOCK_K)
+    wanted = min(max_splits, max(1, (2 * NUM_SMS) // tiles), max(1, k_blocks // MIN_K_BLOCKS_PER_SPLIT))
+    per_split = -(-k_blocks // wanted)
+    return -(-k_blocks // per_split)
+
+
+def _make_map(tensor: torch.Tensor, box_rows: int) -> ctypes.Array:
+    rows, inner = tensor.shape
+    holder = (ctypes.c_ubyte * 128)()
+    code = _library().me_make_tensor_map(holder, tensor.data_ptr(), rows, inner, box_rows)
+    if code != 0:
+        raise RuntimeError(f"could not make a TMA descriptor for a {rows} x {inner} matrix (code {code})")
+    return holder
+
+
+class GemmPlan:
+    def __init__(self, weight: torch.Tensor, dual_rows: int | None = None):
+        if weight.dtype != torch.bfloat16 or not weight.is_contiguous() or not weight.is_cuda:
+            raise RuntimeError("the tensor-core product takes a contiguous bfloat16 CUDA weight")
+        self.weight = weight
+        self.rows, self.inner = weight.shape
+        self.dual_rows = dual_rows  # gate rows [0, dual_rows), up rows [dual_rows, 2 * dual_rows)
+        self.map = _make_map(weight, BLOCK_N)
+
+
+_activation_maps: dict[tuple[int, int, int, int], ctypes.Array] = {}
+
+
+def _activation_map(x: torch.Tensor, tile: int) -> ctypes.Array:
+    key = (x.data_ptr(), x.shape[0], x.shape[1], tile)
+    held = _activation_maps.get(key)
+    if held is None:
+        if len(_activation_maps) > 8192:
+            _activation_maps.clear()
+        held = _make_map(x, tile)
+        _activation_maps[key] = held
+    return held
+
+
+def _check_x(plan: GemmPlan, x: torch.Tensor) -> None:
+    if x.dtype != torch.bfloat16 or not x.is_contiguous() or x.dim() != 2 or x.shape[1] != plan.inner:
+        raise RuntimeError(f"activation {tuple(x.shape)} {x.dtype} does not fit a weight of width {plan.inner}")
+    if x.data_ptr() % 16:
+        raise RuntimeError("activation must be 16-byte aligned for TMA")
+
+
+def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
+    """``out[s] = x @ weight^T`` restricted to the k range of split ``s``; float32
+    ``[splits, T, rows]``."""
+    _check_x(plan, x)
+    tokens = x.shape[0]
+    if out.dtype != torch.float32 or tuple(out.shape) != (splits, tokens, plan.rows) or not out.is_contiguous():
+        raise RuntimeError(f"output {tuple(out.shape)} does not fit [{splits}, {tokens}, {plan.rows}] float32")
+    tile = token_tile(tokens)
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = _library().me_gemm_tcgen05(
+        plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream
+    )
+    if code != 0:
+        raise RuntimeError(f"tensor-core product failed to launch (code {code})")
+
+
+def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
+    """``act = silu(x @ gate^T) * (x @ up^T)`` in bfloat16, gate/up being the halves of the
+    plan's weight."""
+    _check_x(plan, x)
+    tokens = x.shape[0]
+    if plan.dual_rows is None:
+        raise RuntimeError("this plan was not made for a gated product")
+    if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
+        raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = _library().me_gemm_tcgen05_swiglu(
+        plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
+    )
+    if code != 0:
+        raise RuntimeError(f"gated tensor-core product failed to launch (code {code})")
+
+
+def take_error() -> int:
+    """The first failure that a tensor-core kernel recorded on the device since the last call
+    (a wait that ran into its limit), or 0.  Synchronises the device."""
+    if _lib is None:
+        return 0
+    code = c_int(0)
+    status = _lib.me_gemm_take_error(ctypes.byref(code))
+    if status != 0:
+        raise RuntimeError(f"could not read the kernels' error flag (CUDA error {status})")
+    return code.value

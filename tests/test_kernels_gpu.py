@@ -1,0 +1,356 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same operation,
+at sizes other than the engine's."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def ops():
+    from mini_engine_b200.csrc import ops as module
+
+    return module
+
+
+def rel_error(got: torch.Tensor, want: torch.Tensor) -> float:
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+
+
+# ------------------------------------------------------------------------------- GEMMs
+
+
+@pytest.mark.parametrize("tokens,outs,inner", [(1, 5, 3), (7, 96, 100), (65, 130, 257), (300, 70, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_simt(tokens, outs, inner, dtype):
+    torch.manual_seed(0)
+    x = torch.randn(tokens, inner, device="cuda").to(dtype)
+    w = torch.randn(outs, inner, device="cuda").to(dtype)
+    out = torch.empty(tokens, outs, device="cuda")
+    ops().gemm_simt(x, w, out)
+    want = x.double() @ w.double().T
+    assert rel_error(out, want) < 2e-6 * math.sqrt(inner)
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    torch.manual_seed(1)
+    x = torch.randn(200, 333, device="cuda")
+    w = torch.randn(77, 333, device="cuda")
+    full = torch.empty(200, 77, device="cuda")
+    ops().gemm_simt(x, w, full)
+    for rows in ([0], [5, 6, 7], list(range(63, 130))):
+        part = torch.empty(len(rows), 77, device="cuda")
+        ops().gemm_simt(x[rows].contiguous(), w, part)
+        assert torch.equal(part, full[rows])
+
+
+TC_SHAPES = [
+    (1, 128, 64),  # one token, one tile, one k block
+    (8, 384, 4096),  # decode-like, split over k
+    (13, 200, 96),  # ragged outputs and a partial k block
+    (64, 1000, 520),  # partial k block, several splits
+    (100, 256, 256),
+    (300, 520, 1160),  # token tile 256 with a ragged second tile
+    (700, 130, 72),
+]
+
+
+@pytest.mark.parametrize("tokens,outs,inner", TC_SHAPES)
+def test_gemm_tensor_core(tokens, outs, inner):
+    from mini_engine_b200.csrc import tensor_core
+
+    torch.manual_seed(2)
+    x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
+    w = torch.randn(outs, inner, device="cuda").to(torch.bfloat16)
+    plan = tensor_core.GemmPlan(w)
+    want = x.double() @ w.double().T
+    for splits in sorted({1, tensor_core.choose_splits(tokens, outs, inner)}):
+        out = torch.full((splits, tokens, outs), float("nan"), device="cuda")
+        tensor_core.gemm(plan, x, out, splits)
+        assert tensor_core.take_error() == 0
+        assert rel_error(out.sum(0), want) < 1e-5, f"splits={splits}"
+
+
+def test_gemm_tensor_core_finds_one_large_product():
+    """A single large x[t][k] * w[n][k] among small terms must land in exactly out[t][n]:
+    a wrong swizzle, k step or lane mapping would put it elsewhere or drop it."""
+    from mini_engine_b200.csrc import tensor_core
+
+    tokens, outs, inner = 40, 300, 200
+    for t, n, k in [(0, 0, 0), (39, 299, 199), (17, 131, 77), (5, 128, 64), (33, 127, 63)]:
+        x = torch.full((tokens, inner), 0.001, device="cuda").to(torch.bfloat16)
+        w = torch.full((outs, inner), 0.001, device="cuda").to(torch.bfloat16)
+        x[t, k], w[n, k] = 64.0, 32.0
+        out = torch.empty(1, tokens, outs, device="cuda")
+        tensor_core.gemm(tensor_core.GemmPlan(w), x, out, 1)
+        want = x.double() @ w.double().T
+        assert rel_error(out[0], want) < 1e-5
+        assert int(out[0].argmax()) == t * outs + n
+
+
+@pytest.mark.parametrize("tokens,inter,inner", [(65, 160, 96), (128, 128, 64), (300, 300, 264)])
+def test_gemm_tensor_core_swiglu(tokens, inter, inner):
+    from mini_engine_b200.csrc import tensor_core
+
+    torch.manual_seed(3)
+    x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * inter, inner, device="cuda") * 0.2).to(torch.bfloat16)
+    act = torch.empty(tokens, inter, device="cuda", dtype=torch.bfloat16)
+    tensor_core.gemm_swiglu(tensor_core.GemmPlan(w, dual_rows=inter), x, act)
+    assert tensor_core.take_error() == 0
+    both = x.double() @ w.double().T
+    gate, up = both[:, :inter], both[:, inter:]
+    want = gate * torch.sigmoid(gate) * up
+    assert rel_error(act, want) < 6e-3  # one rounding to bfloat16
+
+
+# -------------------------------------------------------------------------- elementwise
+
+
+@pytest.mark.parametrize("hidden", [24, 100, 4096])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(hidden, out_dtype):
+    torch.manual_seed(4)
+    tokens, eps = 9, 3e-5
+    x = torch.randn(tokens, hidden, device="cuda")
+    pending = torch.randn(3, tokens, hidden, device="cuda")
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    summed = x.double() + pending.double().sum(0)
+    want = weight.double() * summed * torch.rsqrt(summed.pow(2).mean(-1, keepdim=True) + eps)
+    out = torch.empty(tokens, hidden, device="cuda", dtype=out_dtype)
+    x_run = x.clone()
+    ops().add_rmsnorm(x_run, pending, weight, eps, out)
+    assert rel_error(x_run, summed) < 1e-6
+    assert rel_error(out, want) < (1e-5 if out_dtype == torch.float32 else 5e-3)
+    rows = torch.tensor([7, 0, 7], device="cuda", dtype=torch.int32)
+    picked = torch.empty(3, hidden, device="cuda", dtype=out_dtype)
+    x_keep = x.clone()
+    ops().add_rmsnorm(x_keep, pending, weight, eps, picked, rows)
+    assert torch.equal(x_keep, x)
+    assert rel_error(picked, want[rows.long()]) < (1e-5 if out_dtype == torch.float32 else 5e-3)
+    plain = torch.empty(tokens, hidden, device="cuda", dtype=out_dtype)
+    ops().add_rmsnorm(x.clone(), None, weight, eps, plain)
+    want_plain = weight.double() * x.double() * torch.rsqrt(x.double().pow(2).mean(-1, keepdim=True) + eps)
+    assert rel_error(plain, want_plain) < (1e-5 if out_dtype == torch.float32 else 5e-3)
+
+
+def test_embedding():
+    table = torch.randn(50, 24, device="cuda").to(torch.bfloat16)
+    ids = torch.tensor([3, 49, 0, 3], device="cuda", dtype=torch.int32)
+    out = torch.empty(4, 24, device="cuda")
+    ops().embedding(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(out_dtype):
+    torch.manual_seed(5)
+    partials = torch.randn(2, 5, 2 * 37, device="cuda")
+    both = partials.double().sum(0)
+    gate, up = both[:, :37], both[:, 37:]
+    out = torch.empty(5, 37, device="cuda", dtype=out_dtype)
+    ops().swiglu(partials, out)
+    assert rel_error(out, gate * torch.sigmoid(gate) * up) < (1e-6 if out_dtype == torch.float32 else 5e-3)
+
+
+def rope_reference(x, positions, theta):
+    d = x.shape[-1]
+    inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    angles = positions.float()[:, None] * inv_freq[None, :]
+    angles = torch.cat((angles, angles), -1).double()
+    half = d // 2
+    rotated = torch.cat((-x[..., half:], x[..., :half]), -1)
+    return x * angles.cos()[:, None, :] + rotated * angles.sin()[:, None, :]
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page", [(3, 1, 16, 4), (6, 3, 48, 8), (4, 2, 128, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_qk_norm_rope_store(heads, kv_heads, head_dim, page, dtype):
+    torch.manual_seed(6)
+    tokens, pages, eps, theta = 11, 9, 2e-5, 5000.0
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(2, tokens, width, device="cuda")
+    qw = 1 + 0.1 * torch.randn(head_dim, device="cuda")
+    kw = 1 + 0.1 * torch.randn(head_dim, device="cuda")
+    positions = torch.randint(0, 3000, (tokens,), dtype=torch.int32)
+    slots = torch.randperm(pages * page)[:tokens].to(torch.int32)
+    slots[4] = -1  # not stored
+    inv_freq = (1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+    q_out = torch.empty(tokens, heads * head_dim, device="cuda", dtype=dtype)
+    k_pages = torch.zeros(pages, kv_heads, page, head_dim, device="cuda", dtype=dtype)
+    v_pages = torch.zeros_like(k_pages)
+    ops().qk_norm_rope_store(
+        qkv=qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim, q_weight=qw, k_weight=kw, eps=eps,
+        inv_freq=inv_freq, positions=positions.cuda(), q_out=q_out, page_size=page, slot_mapping=slots.cuda(),
+        k_pages=k_pages, v_pages=v_pages,
+    )  # fmt: skip
+    total = qkv.double().sum(0).cpu()
+    q, k, v = total.split([heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], dim=-1)
+
+    def normed(t, w, n):
+        t = t.view(tokens, n, head_dim)
+        return w.double().cpu() * t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+
+    q_want = rope_reference(normed(q, qw, heads), positions, theta)
+    k_want = rope_reference(normed(k, kw, kv_heads), positions, theta)
+    tol = 2e-5 if dtype == torch.float32 else 6e-3
+    assert rel_error(q_out.cpu().view(tokens, heads, head_dim), q_want) < tol
+    for t in range(tokens):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        assert rel_error(k_pages[s // page, :, s % page].cpu(), k_want[t]) < tol
+        assert rel_error(v_pages[s // page, :, s % page].cpu(), v.view(tokens, kv_heads, head_dim)[t]) < tol
+    written = {int(s) for s in slots if s >= 0}
+    for s in range(pages * page):
+        if s not in written:
+            assert float(k_pages[s // page, :, s % page].abs().max()) == 0.0
+
+
+# ---------------------------------------------------------------------------- attention
+
+
+def attention_reference(q, k, v, scale, window=None):
+    """q [T, heads, d], k/v [T, kv, d] (float64) of one whole sequence -> [T, heads, d]."""
+    t, heads, d = q.shape
+    group = heads // k.shape[1]
+    pos = torch.arange(t)
+    allowed = pos[None, :] <= pos[:, None]
+    if window:
+        allowed &= pos[None, :] > pos[:, None] - window
+    out = torch.empty_like(q)
+    for h in range(heads):
+        s = (q[:, h] @ k[:, h // group].T) * scale
+        s = s.masked_fill(~allowed, float("-inf"))
+        out[:, h] = torch.softmax(s, -1) @ v[:, h // group]
+    return out
+
+
+def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None):
+    """Sequences of the given lengths in scattered pages; the last ``new_counts[i]`` tokens of
+    each are the batch's queries.  Returns kernel inputs and the expected output rows."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    width = max(-(-n // page) for n in lengths) + 1
+    k_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(dtype)  # stale data everywhere
+    v_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(dtype)
+    table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    q_rows, want_rows, entry_of, positions = [], [], [], []
+    for b, (n, new) in enumerate(zip(lengths, new_counts)):
+        q = torch.randn(n, heads, head_dim, generator=g).to(dtype)
+        k = torch.randn(n, kv_heads, head_dim, generator=g).to(dtype)
+        v = torch.randn(n, kv_heads, head_dim, generator=g).to(dtype)
+        if spike is not None and n > spike[1]:
+            # one far key answers one late query loudly: it must be found among hundreds
+            query_pos, key_pos = n - 1, spike[1]
+            k[key_pos] = 0
+            q[query_pos] = 0
+            k[key_pos, :, 0] = 30.0
+            q[query_pos, :, 0] = 30.0
+            v[key_pos] = 5.0
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+        for p in range(n):
+            k_pages[table[b, p // page], :, p % page] = k[p]
+            v_pages[table[b, p // page], :, p % page] = v[p]
+        want = attention_reference(q.double(), k.double(), v.double(), head_dim**-0.5)
+        q_rows.append(q[n - new :])
+        want_rows.append(want[n - new :])
+        entry_of += [b] * new
+        positions += list(range(n - new, n))
+    return dict(
+        q=torch.cat(q_rows).reshape(-1, heads * head_dim).contiguous().cuda(),
+        k_pages=k_pages.cuda(), v_pages=v_pages.cuda(), table=table.cuda(),
+        entry_of=torch.tensor(entry_of, dtype=torch.int32).cuda(),
+        positions=torch.tensor(positions, dtype=torch.int32).cuda(),
+        want=torch.cat(want_rows).reshape(-1, heads * head_dim),
+        lengths=lengths, new_counts=new_counts,
+    )  # fmt: skip
+
+
+ATTENTION_CASES = [
+    # lengths, new tokens of each, heads, kv heads, head_dim, page
+    ([1, 16, 17, 33, 100, 255], [1, 1, 1, 1, 1, 1], 4, 2, 16, 16),  # decode at the reference's lengths
+    ([7, 9, 13], [7, 1, 5], 4, 2, 32, 4),  # fresh prompt, decode, continuation
+    ([300, 64, 2], [300, 33, 2], 6, 1, 48, 8),
+    ([513, 40], [2, 40], 8, 8, 80, 16),
+]
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_paged_attention_generic(case, dtype):
+    lengths, news, heads, kv_heads, head_dim, page = case
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, dtype, seed=7, spike=(0, 3))
+    out = torch.empty_like(data["q"])
+    ops().paged_attention_generic(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], data["entry_of"], data["positions"], out,
+        heads, kv_heads, head_dim, head_dim**-0.5, 0,
+    )  # fmt: skip
+    assert rel_error(out.cpu(), data["want"]) < (2e-5 if dtype == torch.float32 else 1e-2)
+
+
+def test_paged_attention_generic_window():
+    heads, kv_heads, head_dim, page, window = 4, 2, 16, 4, 10
+    data = paged_case([50, 9], [50, 3], heads, kv_heads, head_dim, page, torch.float32, seed=8)
+    out = torch.empty_like(data["q"])
+    ops().paged_attention_generic(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], data["entry_of"], data["positions"], out,
+        heads, kv_heads, head_dim, head_dim**-0.5, window,
+    )  # fmt: skip
+    # reference with the window: rebuild from the pages
+    wants = []
+    for b, (n, new) in enumerate(zip(data["lengths"], data["new_counts"])):
+        table = data["table"][b].cpu()
+        k = torch.stack([data["k_pages"][table[p // page], :, p % page].cpu() for p in range(n)]).double()
+        v = torch.stack([data["v_pages"][table[p // page], :, p % page].cpu() for p in range(n)]).double()
+        rows = data["entry_of"].cpu() == b
+        q_new = data["q"].cpu()[rows].view(new, heads, head_dim).double()
+        q = torch.zeros(n, heads, head_dim, dtype=torch.float64)
+        q[n - new :] = q_new
+        wants.append(attention_reference(q, k, v, head_dim**-0.5, window)[n - new :])
+    want = torch.cat(wants).reshape(-1, heads * head_dim)
+    assert rel_error(out.cpu(), want) < 2e-5
+
+
+# ----------------------------------------------------------------------------- sampling
+
+
+def test_sample_greedy_and_temperature():
+    torch.manual_seed(9)
+    rows, vocab = 6, 5003
+    logits = torch.randn(rows, vocab, device="cuda") * 3
+    logits[1, 77] = logits[1, 4000] = 50.0  # equal maxima: the lowest index wins
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops().sample(logits, None, None, out)
+    want = logits.argmax(-1)
+    want[1] = 77
+    assert out.tolist() == want.tolist()
+    temps = torch.tensor([0.0, 0.0, 0.8, 1.0, 1.5, 0.3], device="cuda")
+    uniforms = torch.tensor([0.5, 0.5, 0.0, 0.37, 0.93, 0.999999], device="cuda")
+    ops().sample(logits, temps, uniforms, out)
+    got = out.tolist()
+    assert got[:2] == want.tolist()[:2]
+    for r in range(2, rows):
+        probs = torch.softmax(logits[r].double() / float(temps[r]), -1).cpu()
+        cdf = torch.cumsum(probs, -1)
+        target = float(uniforms[r])
+        below = float(cdf[got[r] - 1]) if got[r] > 0 else 0.0
+        assert below - 1e-4 <= target <= float(cdf[got[r]]) + 1e-4, f"row {r}: token {got[r]} does not hold u={target}"
+
+
+def test_sample_distribution():
+    vocab, draws = 7, 4000
+    logits = torch.tensor([[2.0, 0.0, 1.0, -1.0, 0.5, 0.0, -3.0]], device="cuda").repeat(draws, 1)
+    temps = torch.full((draws,), 0.7, device="cuda")
+    uniforms = torch.rand(draws, device="cuda", generator=torch.Generator("cuda").manual_seed(0))
+    out = torch.empty(draws, dtype=torch.int32, device="cuda")
+    ops().sample(logits, temps, uniforms, out)
+    freq = torch.bincount(out.long().cpu(), minlength=vocab).double() / draws
+    want = torch.softmax(logits[0].double().cpu() / 0.7, -1)
+    assert float((freq - want).abs().max()) < 0.03
