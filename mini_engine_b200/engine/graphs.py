@@ -1,0 +1,79 @@
+"""CUDA graphs for decode-only steps: the whole forward pass of a batch of single tokens is
+captured once per batch-size bucket and replayed with one launch.
+
+As in the reference (src/mini_engine/cuda_graphs.py:28-138 of YuvGev00/mini-engine): buckets
+1, 2, 4, 8, then multiples of 16 up to the request cap; a batch is padded up to its bucket
+with dummy rows that write to and read from a spare cache page that no request owns; every
+buffer that a graph reads lives as long as the graph (here: the runner's index block and
+workspace, whose addresses never change).
+"""
+
+from __future__ import annotations
+
+from typing import Sequence as Seq
+
+import torch
+
+from mini_engine_b200.cache.manager import RequestCache
+from mini_engine_b200.engine.runner import ModelRunner, StepEntry
+
+
+def batch_buckets(max_batch: int) -> list[int]:
+    small = [b for b in (1, 2, 4, 8) if b < max_batch]
+    return small + list(range(16, max_batch, 16)) + [max_batch]
+
+
+class DecodeGraphs:
+    def __init__(self, runner: ModelRunner, max_batch: int):
+        self.runner = runner
+        self.buckets = batch_buckets(max_batch)
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.logits: dict[int, torch.Tensor] = {}
+        self._capture_all()
+
+    @property
+    def max_batch(self) -> int:
+        return self.buckets[-1]
+
+    def _dummy_entries(self, count: int) -> list[StepEntry]:
+        caches = [
+            RequestCache(block_tables=[[self.runner.spare_page] for _ in range(self.runner.num_groups)])
+            for _ in range(count)
+        ]
+        return [StepEntry(c, 0, [0], (0,)) for c in caches]
+
+    @torch.inference_mode()
+    def _capture_all(self) -> None:
+        runner = self.runner
+        pool = None
+        for bucket in reversed(self.buckets):  # largest first: smaller graphs reuse its memory pool
+            entries = self._dummy_entries(bucket)
+            ctx, rows = runner.pack(entries)
+            # A captured launch must cover any context that a later replay may bring.
+            ctx.max_context_len = runner.table_width * runner.block_size
+            runner.model.forward(ctx, runner.layout.views, rows)  # warm-up: builds, descriptors, buffers
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            runner.workspace.frozen = True
+            try:
+                with torch.cuda.graph(graph, pool=pool):
+                    self.logits[bucket] = runner.model.forward(ctx, runner.layout.views, rows)
+            finally:
+                runner.workspace.frozen = False
+            pool = graph.pool()
+            self.graphs[bucket] = graph
+        torch.cuda.synchronize()
+
+    def bucket_for(self, batch: int) -> int | None:
+        for bucket in self.buckets:
+            if bucket >= batch:
+                return bucket
+        return None
+
+    def run(self, entries: Seq[StepEntry]) -> torch.Tensor:
+        """Logits ``[len(entries), vocab]``: one decoded token per entry, the logits of each."""
+        real = len(entries)
+        bucket = self.bucket_for(real)
+        self.runner.pack(entries, pad_entries_to=bucket, want_every_entry=True)
+        self.graphs[bucket].replay()
+        return self.logits[bucket][:real]

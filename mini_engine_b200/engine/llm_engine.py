@@ -1,0 +1,157 @@
+"""The engine loop: schedule -> pack -> forward -> sample -> postprocess.
+
+Names and meanings follow ``LLMEngine`` of YuvGev00/mini-engine
+(src/mini_engine/engine.py:59-299): ``from_pretrained``, ``add_request``, ``generate``,
+``step``, ``stats``, ``scheduler``, ``block_manager``.  Token ids go in and come out;
+tokenisation is the caller's business.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Iterable
+
+import torch
+
+from mini_engine_b200.cache.manager import CacheManager
+from mini_engine_b200.config.engine_config import EngineConfig
+from mini_engine_b200.engine.graphs import DecodeGraphs
+from mini_engine_b200.engine.loading import load_model, random_model
+from mini_engine_b200.engine.runner import ModelRunner, StepEntry
+from mini_engine_b200.engine.scheduler import ScheduledSeq, Scheduler, SchedulerConfig
+from mini_engine_b200.engine.sequence import Sequence
+from mini_engine_b200.parts.model import DecoderModel
+from mini_engine_b200.sampling.params import SamplingParams
+from mini_engine_b200.sampling.sampler import Sampler
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prompt_tokens: int = 0  # hits of the prefix cache are counted in scheduler.num_cached_tokens
+    computed_tokens: int = 0  # tokens actually run through the model
+    generated_tokens: int = 0
+    graph_steps: int = 0  # steps that replayed a captured graph
+    step_batch_sizes: list[int] = field(default_factory=list)
+
+
+def kv_cache_bytes_per_token(runner: ModelRunner) -> int:
+    """Bytes of keys and values that one token occupies over all layers
+    (src/mini_engine/engine.py:54-56)."""
+    return runner.layout.bytes_per_token
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderModel, config: EngineConfig, eos_token_ids: Iterable[int] = ()):
+        self.config = config
+        self.model = model
+        self.runner = ModelRunner(
+            model,
+            dtype=config.dtype,
+            num_blocks=config.num_blocks,
+            block_size=config.block_size,
+            max_num_seqs=config.max_num_seqs,
+            max_num_batched_tokens=config.max_num_batched_tokens,
+            max_model_len=config.max_model_len,
+        )
+        self.block_manager = CacheManager(
+            self.runner.layout.groups,
+            config.num_blocks,
+            config.block_size,
+            config.max_num_seqs,
+            config.enable_prefix_caching,
+            has_state=self.runner.layout.has_state,
+        )
+        self.scheduler = Scheduler(
+            SchedulerConfig(config.max_num_seqs, config.max_num_batched_tokens, config.max_model_len),
+            self.block_manager,
+            set(eos_token_ids),
+        )
+        self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
+        self.stats = EngineStats()
+        self.decode_graphs: DecodeGraphs | None = None
+        if config.cuda_graphs:
+            self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
+
+    # ----------------------------------------------------------------- loading
+
+    @classmethod
+    def from_pretrained(cls, model_path: str | Path, config: EngineConfig | None = None) -> "LLMEngine":
+        """Load a checkpoint from a local folder with ``config.json`` and safetensors files
+        (and ``generation_config.json`` for the end-of-sequence ids, if present)."""
+        config = config or EngineConfig()
+        _arch, model_config, model = load_model(model_path, config.dtype)
+        return cls(model, config, getattr(model_config, "eos_token_ids", ()))
+
+    @classmethod
+    def from_random(cls, model_config: Any, seed: int = 0, config: EngineConfig | None = None, scale: float = 1.0) -> "LLMEngine":
+        """An engine on seeded random weights of the given typed configuration."""
+        config = config or EngineConfig()
+        model = random_model(model_config, seed, config.dtype, scale=scale)
+        return cls(model, config, getattr(model_config, "eos_token_ids", ()))
+
+    # -------------------------------------------------------------------- API
+
+    def add_request(self, prompt_token_ids: list[int], params: SamplingParams | None = None) -> Sequence:
+        seq = Sequence(prompt_token_ids, params or SamplingParams())
+        vocab = self.runner.vocab_size
+        if min(seq.token_ids) < 0 or max(seq.token_ids) >= vocab:
+            raise ValueError(f"prompt token ids must lie in [0, {vocab})")
+        self.scheduler.add(seq)
+        self.stats.prompt_tokens += len(seq)
+        return seq
+
+    def generate(self, prompts: list[list[int]], params: SamplingParams | None = None) -> list[list[int]]:
+        """Run all prompts to completion as one continuously batched workload; returns the
+        generated ids of each."""
+        seqs = [self.add_request(p, params) for p in prompts]
+        while self.scheduler.has_unfinished():
+            self.step()
+        return [s.output_token_ids for s in seqs]
+
+    @torch.inference_mode()
+    def step(self) -> list[Sequence]:
+        """One iteration; returns the requests that finished in it."""
+        batch = self.scheduler.schedule()
+        if not batch:
+            raise RuntimeError("scheduler produced an empty batch with work pending")
+        entries = [self._entry(item) for item in batch]
+        sampling = [item for item in batch if item.samples]
+        if self._graph_fits(batch):
+            logits = self.decode_graphs.run(entries)
+            self.stats.graph_steps += 1
+        else:
+            logits = self.runner.execute(entries)
+        sampled = self.sampler.sample(
+            logits,
+            [item.seq.params.temperature for item in sampling],
+            [item.seq.seq_id for item in sampling],
+            [item.seq.num_output_tokens for item in sampling],
+        )
+        tokens = iter(sampled)
+        next_tokens = [next(tokens) if item.samples else None for item in batch]
+        self._update_stats(batch)
+        return self.scheduler.postprocess(batch, next_tokens)
+
+    # ---------------------------------------------------------------- private
+
+    @staticmethod
+    def _entry(item: ScheduledSeq) -> StepEntry:
+        seq, start = item.seq, item.seq.num_computed_tokens
+        want = (item.num_tokens - 1,) if item.samples else ()
+        return StepEntry(seq.cache, start, seq.token_ids[start : start + item.num_tokens], want)
+
+    def _graph_fits(self, batch: list[ScheduledSeq]) -> bool:
+        graphs = self.decode_graphs
+        if graphs is None or len(batch) > graphs.max_batch:
+            return False
+        return all(item.num_tokens == 1 and item.samples for item in batch)
+
+    def _update_stats(self, batch: list[ScheduledSeq]) -> None:
+        stats = self.stats
+        stats.steps += 1
+        stats.step_batch_sizes.append(len(batch))
+        for item in batch:
+            stats.computed_tokens += item.num_tokens
+            stats.generated_tokens += int(item.samples)

@@ -81,10 +81,14 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ packing
 
-    def pack(self, entries: Seq[StepEntry], pad_entries_to: int | None = None) -> tuple[StepContext, torch.Tensor]:
+    def pack(
+        self, entries: Seq[StepEntry], pad_entries_to: int | None = None, want_every_entry: bool = False
+    ) -> tuple[StepContext, torch.Tensor]:
         """Lay the batch out as int32 arrays on the device.  With ``pad_entries_to`` the batch
         is filled up with one-token dummy entries on the spare page (for a captured graph of
-        that size).  Returns the context and the int32 row numbers of the wanted logits."""
+        that size); with ``want_every_entry`` the wanted rows are the last token of every entry,
+        padding included, whatever the entries ask for.  Returns the context and the int32 row
+        numbers of the wanted logits."""
         real = len(entries)
         total_entries = max(real, pad_entries_to or 0)
         counts = [len(e.token_ids) for e in entries]
@@ -163,6 +167,8 @@ class ModelRunner:
             cu[b + 1] = cursor + 1
             ctx_len[b], state[b], fresh[b] = 1, self.spare_slot, 1
             cursor += 1
+        if want_every_entry:
+            wanted_rows = [int(cu[b + 1]) - 1 for b in range(total_entries)]
         rows_view, o_rows = take(len(wanted_rows))
         rows_view[:] = wanted_rows
 
