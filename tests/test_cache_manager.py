@@ -1,0 +1,179 @@
+"""The cache manager: pages, prefix hashes, windows, state slots (no GPU)."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from mini_engine_b200.cache import NULL_PAGE, CacheManager, GroupSpec, hash_page
+
+FULL = [GroupSpec("full")]
+
+
+def computed(mgr, req, tokens, count):
+    mgr.register_computed(req, tokens, count)
+
+
+def test_hashes_chain():
+    a = hash_page(b"", [1, 2, 3, 4])
+    assert a == hash_page(b"", [1, 2, 3, 4]) and len(a) == 16
+    assert hash_page(a, [5, 6, 7, 8]) != hash_page(b"", [5, 6, 7, 8])
+
+
+def test_allocate_free_round_trip_and_all_or_nothing():
+    mgr = CacheManager(FULL, num_blocks=4, block_size=4, max_num_seqs=2)
+    a, b = mgr.new_request(), mgr.new_request()
+    assert mgr.try_allocate(a, 9) and len(a.block_tables[0]) == 3 and a.state_slot >= 0
+    assert not mgr.try_allocate(b, 8)  # two pages wanted, one free: nothing changes
+    assert b.block_tables == [[]] and b.state_slot == -1 and mgr.num_free_blocks == 1
+    mgr.check_invariants([a, b])
+    mgr.free(a)
+    assert mgr.num_free_blocks == 4 and a.holds_nothing()
+    mgr.check_invariants([])
+    with pytest.raises(AssertionError):
+        mgr.pools[0].release(0)  # freed twice
+
+
+def test_prefix_sharing_counts_references_and_always_leaves_a_token():
+    mgr = CacheManager(FULL, num_blocks=8, block_size=4, max_num_seqs=4)
+    tokens = list(range(12))
+    a = mgr.new_request()
+    assert mgr.try_allocate(a, 12)
+    computed(mgr, a, tokens, 12)
+    hits = mgr.match_prefix(tokens)  # 12 tokens: only the first two pages are eligible
+    assert hits == [a.block_tables[0][:2]]
+    b = mgr.new_request()
+    assert mgr.try_allocate(b, 12, hits)
+    assert b.block_tables[0][:2] == a.block_tables[0][:2] and b.block_tables[0][2] != a.block_tables[0][2]
+    assert [mgr.pools[0].ref_counts[p] for p in hits[0]] == [2, 2]
+    mgr.check_invariants([a, b])
+    mgr.free(a)
+    mgr.free(b)
+    mgr.check_invariants([])
+    assert mgr.match_prefix(tokens + [99]) != [[]]  # freed pages stay cached
+
+
+def test_eviction_takes_unhashed_pages_first_then_least_recently_freed():
+    mgr = CacheManager(FULL, num_blocks=4, block_size=2, max_num_seqs=4)
+    a, b = mgr.new_request(), mgr.new_request()
+    assert mgr.try_allocate(a, 4) and mgr.try_allocate(b, 3)
+    computed(mgr, a, [1, 2, 3, 4], 4)
+    computed(mgr, b, [5, 6, 7], 3)  # b's second page is not full: unhashed
+    b_tail = b.block_tables[0][1]
+    a_pages = list(a.block_tables[0])
+    mgr.free(a)
+    mgr.free(b)
+    c = mgr.new_request()
+    assert mgr.try_allocate(c, 2) and c.block_tables[0] == [b_tail] and mgr.num_evictions == 0
+    d = mgr.new_request()
+    assert mgr.try_allocate(d, 2)
+    assert d.block_tables[0] == [a_pages[1]] and mgr.num_evictions == 1  # a's tail before a's head
+    mgr.check_invariants([c, d])
+
+
+def test_reviving_cached_pages_counts_against_capacity():
+    mgr = CacheManager(FULL, num_blocks=3, block_size=2, max_num_seqs=4)
+    a = mgr.new_request()
+    tokens = [1, 2, 3, 4, 5]
+    assert mgr.try_allocate(a, 5)
+    computed(mgr, a, tokens, 5)
+    mgr.free(a)
+    b = mgr.new_request()
+    assert mgr.try_allocate(b, 2)  # takes the unhashed third page
+    c = mgr.new_request()
+    hits = mgr.match_prefix(tokens)
+    assert len(hits[0]) == 2
+    assert not mgr.try_allocate(c, 6, hits)  # 2 revived + 1 fresh > 2 free
+    assert mgr.try_allocate(c, 4, hits)
+    mgr.check_invariants([b, c])
+
+
+def test_duplicate_content_is_not_registered_twice_and_reset():
+    mgr = CacheManager(FULL, num_blocks=4, block_size=2, max_num_seqs=4)
+    a, b = mgr.new_request(), mgr.new_request()
+    assert mgr.try_allocate(a, 2) and mgr.try_allocate(b, 2)
+    computed(mgr, a, [1, 2], 2)
+    computed(mgr, b, [1, 2], 2)
+    assert mgr.pools[0].page_hash[b.block_tables[0][0]] is None
+    mgr.check_invariants([a, b])
+    mgr.reset_prefix_cache()
+    assert mgr.match_prefix([1, 2, 3]) == [[]]
+
+
+def test_prefix_caching_disabled_or_unsound():
+    off = CacheManager(FULL, 4, 2, 2, enable_prefix_caching=False)
+    a = off.new_request()
+    assert off.try_allocate(a, 4)
+    computed(off, a, [1, 2, 3, 4], 4)
+    assert off.match_prefix([1, 2, 3, 4, 5]) == [[]] and a.page_hashes == []
+    assert not CacheManager([GroupSpec("w", window=8)], 4, 2, 2).enable_prefix_caching
+    assert not CacheManager(FULL, 4, 2, 2, has_state=True).enable_prefix_caching
+
+
+def test_window_group_gives_pages_back_while_the_request_runs():
+    groups = [GroupSpec("full"), GroupSpec("win", window=6)]
+    mgr = CacheManager(groups, num_blocks=8, block_size=4, max_num_seqs=2)
+    req = mgr.new_request()
+    assert mgr.try_allocate(req, 16)
+    assert mgr.release_behind_window(req, 16) == 2  # next query at 16 reads keys > 10: pages 0 and 1 are passed
+    assert req.block_tables[1][:2] == [NULL_PAGE, NULL_PAGE] and NULL_PAGE not in req.block_tables[0]
+    assert mgr.pools[1].num_free == 6 and mgr.pools[0].num_free == 4
+    assert mgr.release_behind_window(req, 16) == 0
+    mgr.check_invariants([req])
+    assert mgr.try_allocate(req, 20) and len(req.block_tables[1]) == 5
+    mgr.free(req)
+    mgr.check_invariants([])
+    assert mgr.pools[1].num_free == 8
+
+
+def test_state_slots_run_out_and_come_back():
+    mgr = CacheManager(FULL, num_blocks=16, block_size=4, max_num_seqs=2, has_state=True)
+    reqs = [mgr.new_request() for _ in range(3)]
+    assert mgr.try_allocate(reqs[0], 1) and mgr.try_allocate(reqs[1], 1)
+    assert not mgr.try_allocate(reqs[2], 1) and reqs[2].holds_nothing()
+    assert reqs[0].state_slot != reqs[1].state_slot
+    mgr.free(reqs[0])
+    assert mgr.try_allocate(reqs[2], 1)
+    mgr.check_invariants(reqs[1:])
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_lose_no_page(seed):
+    """Requests arrive, grow, share prefixes, pass windows and end in random order; after every
+    operation no page is lost, held twice without a count, or free while held."""
+    rng = random.Random(seed)
+    groups = [GroupSpec("full")] if seed % 2 == 0 else [GroupSpec("full"), GroupSpec("win", window=5)]
+    mgr = CacheManager(groups, num_blocks=12, block_size=4, max_num_seqs=5)
+    live: list[dict] = []
+    prefixes = [[rng.randrange(50) for _ in range(8)] for _ in range(2)]
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.35 and len(live) < 6:
+            tokens = list(rng.choice(prefixes)) + [rng.randrange(50) for _ in range(rng.randrange(1, 20))]
+            req = mgr.new_request()
+            hits = mgr.match_prefix(tokens)
+            cached = len(hits[0]) * 4
+            take = rng.randrange(1, len(tokens) - cached + 1)
+            if mgr.try_allocate(req, cached + take, hits):
+                live.append({"req": req, "tokens": tokens, "done": cached, "alloc": cached + take})
+            else:
+                assert req.holds_nothing()
+        elif action < 0.8 and live:
+            item = rng.choice(live)
+            item["done"] = item["alloc"]
+            mgr.register_computed(item["req"], item["tokens"], item["done"])
+            mgr.release_behind_window(item["req"], item["done"])
+            if item["done"] == len(item["tokens"]):
+                item["tokens"].append(rng.randrange(50))
+            grow = min(len(item["tokens"]), item["done"] + rng.randrange(1, 6))
+            if mgr.try_allocate(item["req"], grow):
+                item["alloc"] = grow
+        elif live:
+            item = live.pop(rng.randrange(len(live)))
+            mgr.free(item["req"])
+        mgr.check_invariants([i["req"] for i in live])
+    for item in live:
+        mgr.free(item["req"])
+    mgr.check_invariants([])
+    assert all(pool.num_free == 12 for pool in mgr.pools)
