@@ -1,0 +1,342 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+The default run builds the Qwen3-8B layer sizes with seeded random bfloat16 weights, fills the
+cache of 8 requests with 2,048-token contexts, and times K decode steps (one token for every
+request per step) as captured CUDA graphs, with CUDA events on the launching stream.  It
+prints ONE JSON line: ``value`` is decoded tokens per second on the device; ``e2e`` is the
+same through ``LLMEngine.step`` (host token ids in, sampled ids out, scheduler and copies
+included); ``prefill`` times one 2,048-token prompt; ``roofline`` is the bytes a decode step
+must read (every weight once plus the live requests' cache) over its time, against the
+measured copy bandwidth; ``points`` adds decode at batch 1 and 64.
+
+Every step reads about 15 GB of weights, far more than the 126 MB L2, so no flush is needed
+between timed iterations (``config.l2`` says so).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: Qwen3-8B layer sizes.
+QWEN3_8B = dict(
+    vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
+    max_position_embeddings=40960, tie_word_embeddings=False,
+)  # fmt: skip
+CONTEXT = 2048  # tokens each request holds when decode is timed
+PREFILL_TOKENS = 2048
+MAX_MODEL_LEN = 4096  # benchmark context length of the configuration
+BLOCK_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            peaks = {
+                "hbm_gbs": float(raw["hbm_gbs"]),
+                "bf16_tflops": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
+                "source": "measured",
+            }
+            return peaks
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5,
+                ).stdout.strip()  # fmt: skip
+                if out:
+                    self.samples.append([f.strip() for f in out.splitlines()[0].split(",")])
+            except (OSError, subprocess.SubprocessError):
+                return
+            self._stop.wait(0.2)
+
+    def __enter__(self) -> "ClockSampler":
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        maxima = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        reasons = sorted(
+            {name for s in self.samples for name, flag in zip(self.NAMES, s[2:]) if flag.lower().startswith("active")}
+        )
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "reasons": reasons,
+            "samples": len(clocks),
+        }
+
+
+def decode_bytes(cfg, layers: int, batch: int, context: int) -> float:
+    """Bytes one decode step has to read: every weight it uses once (the embedding table is
+    only touched at ``batch`` rows) and the keys and values of the live requests."""
+    d, h, inter = cfg.head_dim, cfg.hidden_size, cfg.intermediate_size
+    per_layer = ((cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d * h + cfg.num_attention_heads * d * h + 3 * h * inter) * 2
+    head = cfg.vocab_size * h * 2
+    kv = 2 * layers * cfg.num_key_value_heads * d * 2 * context * batch
+    return per_layer * layers + head + kv
+
+
+def prefill_flops(cfg, layers: int, tokens: int) -> float:
+    d, h, inter = cfg.head_dim, cfg.hidden_size, cfg.intermediate_size
+    gemm = 2.0 * tokens * ((cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d * h + cfg.num_attention_heads * d * h + 3 * h * inter)
+    attention = 2.0 * 2.0 * cfg.num_attention_heads * d * tokens * (tokens + 1) / 2  # causal QK^T and PV
+    return layers * (gemm + attention) + 2.0 * cfg.vocab_size * h  # one row of logits
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.config import Qwen3Config
+    from mini_engine_b200.csrc import ops, tensor_core
+    from mini_engine_b200.engine.runner import StepEntry
+
+    sizes = dict(QWEN3_8B)
+    full_layers = sizes["num_hidden_layers"]
+    if args.layers:
+        sizes["num_hidden_layers"] = args.layers
+    cfg = Qwen3Config(**sizes)
+    layers = cfg.num_hidden_layers
+    peaks = load_peaks()
+    max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
+    steps_total = args.steps + args.warmup + 8
+    pages_per_request = -(-(CONTEXT + steps_total + 1) // BLOCK_SIZE)
+    engine_config = EngineConfig(
+        block_size=BLOCK_SIZE, num_blocks=max_batch * pages_per_request + 8, max_num_seqs=max_batch,
+        max_num_batched_tokens=max(PREFILL_TOKENS, max_batch), max_model_len=MAX_MODEL_LEN,
+        enable_prefix_caching=False, dtype=torch.bfloat16, seed=0, cuda_graphs=True,
+    )  # fmt: skip
+    torch.manual_seed(0)
+    engine = LLMEngine.from_random(cfg, seed=0, config=engine_config)
+    runner, graphs = engine.runner, engine.decode_graphs
+    generator = torch.Generator().manual_seed(1)
+    sampled = torch.empty(max_batch, dtype=torch.int32, device="cuda")
+
+    def random_prompt(n: int) -> list[int]:
+        return torch.randint(0, cfg.vocab_size, (n,), generator=generator).tolist()
+
+    # ---------------------------------------------------------------- prefill, device timed
+    def time_prefill() -> float:
+        cache = engine.block_manager.new_request()
+        assert engine.block_manager.try_allocate(cache, PREFILL_TOKENS)
+        entry = StepEntry(cache, 0, random_prompt(PREFILL_TOKENS), (PREFILL_TOKENS - 1,))
+        times = []
+        for i in range(3 + 3):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.execute([entry])
+            end.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(start.elapsed_time(end))
+        engine.block_manager.free(cache)
+        return statistics.median(times)
+
+    prefill_ms = time_prefill()
+
+    # ------------------------------------------------------------ decode, device timed
+    def fill_contexts(batch: int) -> list:
+        caches = []
+        for _ in range(batch):
+            cache = engine.block_manager.new_request()
+            assert engine.block_manager.try_allocate(cache, CONTEXT + steps_total + 1)
+            runner.execute([StepEntry(cache, 0, random_prompt(CONTEXT), ())])
+            caches.append(cache)
+        torch.cuda.synchronize()
+        return caches
+
+    def time_decode(batch: int, steps: int, warmup: int) -> tuple[float, int]:
+        caches = fill_contexts(batch)
+        tokens = random_prompt(batch)
+        position = CONTEXT
+        launches_before = 0
+
+        def one_step() -> None:
+            nonlocal position
+            entries = [StepEntry(c, position, [tokens[i]], (0,)) for i, c in enumerate(caches)]
+            logits = graphs.run(entries)
+            ops.sample(logits, None, None, sampled[:batch])
+            position += 1
+
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        launches_before = ops.launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            one_step()
+        end.record()
+        torch.cuda.synchronize()
+        eager_launches = ops.launch_count() - launches_before
+        in_graph = graphs.launches[graphs.bucket_for(batch)] * steps
+        for cache in caches:
+            engine.block_manager.free(cache)
+        return start.elapsed_time(end) / steps, eager_launches + in_graph
+
+    with ClockSampler() as clocks:
+        ms_per_step, launches = time_decode(args.batch, args.steps, args.warmup)
+    clock_summary = clocks.summary()
+    value = args.batch / (ms_per_step / 1e3)
+
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            ms, _ = time_decode(batch, max(args.steps // 2, 5), args.warmup)
+            points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 1)
+            points[f"decode_b{batch}_ms"] = round(ms, 4)
+
+    # ------------------------------------------------- decode through the Python entry point
+    def time_e2e(batch: int, steps: int, warmup: int) -> tuple[float, int, int]:
+        params = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+        seqs = [engine.add_request(random_prompt(CONTEXT), params) for _ in range(batch)]
+        while any(s.num_computed_tokens < s.num_prompt_tokens for s in seqs):
+            engine.step()  # prompts, in portions under the token budget
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        began = time.perf_counter()
+        for _ in range(steps):
+            engine.step()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - began
+        while engine.scheduler.has_unfinished():
+            engine.step()
+        return batch * steps / elapsed, runner.last_h2d_bytes, 4 * batch
+
+    e2e_value, h2d_bytes, d2h_bytes = time_e2e(args.batch, args.steps, args.warmup)
+    device_error = tensor_core.take_error()
+
+    achieved_gbs = decode_bytes(cfg, layers, args.batch, CONTEXT + args.warmup + args.steps // 2) / (ms_per_step / 1e3) / 1e9
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    return {
+        "metric": "decode tok/s at batch 8, 2,048-token contexts (Qwen3-8B layer sizes)",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B layer sizes",
+            "layers": layers,
+            "layers_of_configuration": full_layers,
+            "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads,
+            "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size,
+            "global_batch": args.batch,
+            "seq_len": CONTEXT,
+            "max_model_len": MAX_MODEL_LEN,
+            "kv_block_size": BLOCK_SIZE,
+            "parallelism": "single GPU",
+            "decode": "captured CUDA graph per step + sampling kernel",
+            "l2": "inputs larger than L2: each step reads all weights",
+            "peaks": peaks["source"],
+        },
+        "e2e": {
+            "value": round(e2e_value, 1),
+            "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d_bytes,
+            "d2h_bytes_per_step": d2h_bytes,
+        },
+        "gpu_launches": launches,
+        "prefill": {
+            "value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1),
+            "tokens": PREFILL_TOKENS,
+            "ms": round(prefill_ms, 3),
+            "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+        },
+        "roofline": {
+            "bound": "hbm",
+            "achieved": round(achieved_gbs, 1),
+            "peak": peaks["hbm_gbs"],
+            "unit": "GB/s",
+            "frac": round(achieved_gbs / peaks["hbm_gbs"], 4),
+        },
+        "points": points,
+        "clocks": clock_summary,
+        "device_error": device_error,
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--skip-points", action="store_true", help="do not time batch 1 and 64")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "YuvGev00/mini-engine does not install offline: its build backend uv_build is not in "
+                           "the image or the wheelhouse (pip install --no-index --no-build-isolation fails)",
+        }))  # fmt: skip
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

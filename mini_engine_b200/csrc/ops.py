@@ -40,7 +40,18 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _Counter:
+    """Kernel launches issued through this package's bindings since import."""
+
+    launches = 0
+
+
+def launch_count() -> int:
+    return _Counter.launches
+
+
 def _check(code: int, what: str) -> None:
+    _Counter.launches += 1
     if code == 0:
         return
     if code in _ERRORS:

@@ -116,6 +116,7 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
     code = _library().me_gemm_tcgen05(
         plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream
     )
+    _count_launch()
     if code != 0:
         raise RuntimeError(f"tensor-core product failed to launch (code {code})")
 
@@ -133,8 +134,15 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     code = _library().me_gemm_tcgen05_swiglu(
         plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
     )
+    _count_launch()
     if code != 0:
         raise RuntimeError(f"gated tensor-core product failed to launch (code {code})")
+
+
+def _count_launch() -> None:
+    from mini_engine_b200.csrc import ops
+
+    ops._Counter.launches += 1
 
 
 def take_error() -> int:

@@ -15,6 +15,7 @@ from typing import Sequence as Seq
 import torch
 
 from mini_engine_b200.cache.manager import RequestCache
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.engine.runner import ModelRunner, StepEntry
 
 
@@ -29,6 +30,7 @@ class DecodeGraphs:
         self.buckets = batch_buckets(max_batch)
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.logits: dict[int, torch.Tensor] = {}
+        self.launches: dict[int, int] = {}  # kernels inside each bucket's graph
         self._capture_all()
 
     @property
@@ -55,11 +57,13 @@ class DecodeGraphs:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             runner.workspace.frozen = True
+            before = ops.launch_count()
             try:
                 with torch.cuda.graph(graph, pool=pool):
                     self.logits[bucket] = runner.model.forward(ctx, runner.layout.views, rows)
             finally:
                 runner.workspace.frozen = False
+            self.launches[bucket] = ops.launch_count() - before
             pool = graph.pool()
             self.graphs[bucket] = graph
         torch.cuda.synchronize()

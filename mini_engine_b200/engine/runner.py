@@ -77,7 +77,9 @@ class ModelRunner:
         self._host = [torch.empty(self._capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._host_np = [h.numpy() for h in self._host]
         self._device = torch.zeros(self._capacity, dtype=torch.int32, device=self.device)
+        self._copied = [torch.cuda.Event(), torch.cuda.Event()]  # the copy out of each pinned block
         self._flip = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ packing
 
@@ -103,6 +105,7 @@ class ModelRunner:
             )
         g, bs, width = self.num_groups, self.block_size, self.table_width
         self._flip ^= 1
+        self._copied[self._flip].synchronize()  # the host may run ahead of the device by many steps
         host = self._host_np[self._flip]
         offset = 0
 
@@ -174,6 +177,8 @@ class ModelRunner:
 
         used = offset
         self._device[:used].copy_(self._host[self._flip][:used], non_blocking=True)
+        self._copied[self._flip].record()
+        self.last_h2d_bytes = used * 4
         dev = self._device
 
         def at(start: int, n: int) -> torch.Tensor:
