@@ -1,0 +1,493 @@
+// Causal grouped-query attention over the paged cache in bfloat16 with tensor-core products
+// and a 32-bit online softmax, for head sizes 64 and 128.
+//
+// Two kernels share the tile code:
+//   * portions (any number of new tokens per request): one CTA per (request, query head,
+//     64 consecutive new tokens); it walks the request's keys in tiles of 64 that start at
+//     multiples of 64 in absolute position, double-buffered through shared memory.
+//   * decode (one new token per request): one CTA per (request, KV head, 256 keys); all query
+//     heads of the group share the keys that are read; each of its four warps takes 64 keys;
+//     the CTA writes one partial (max, sum, unnormalised output) per head to scratch memory,
+//     and a second kernel merges a request's partials in ascending key order.  The split
+//     depends on positions only, never on the batch.
+//
+// Formula (YuvGev00/mini-engine: src/mini_engine/attention.py:84-86,160-175, the online softmax
+// of src/mini_engine/triton_attention.py:56-82): query head h reads KV head h / group;
+// s = (q . k) * scale; a query at position p sees keys at positions <= p (and > p - window);
+// out = softmax(s) V.  Scores, maxima, sums and the output accumulate in float32; the
+// probabilities are rounded to bfloat16 for the second product, as the reference's
+// `p.to(v.dtype)` does.
+//
+// Pages are [page][kv_head][slot][head_dim]; a key's address comes from the request's block
+// table, so any page size works.  Keys outside the visible range are zero-filled in shared
+// memory (never read from the cache), so stale contents of reused pages cannot leak.
+#include "common.cuh"
+
+constexpr int BLOCK_M = 64;   // query rows per CTA (portions)
+constexpr int BLOCK_KEYS = 64;  // keys per tile
+constexpr int ATTN_THREADS = 128;
+constexpr int DECODE_CHUNK = 256;  // keys per decode CTA: 4 warps x 64
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+    const __nv_bfloat16* q;        // [tokens][heads][D]
+    const __nv_bfloat16* k_pages;  // [pages][kv_heads][page_size][D]
+    const __nv_bfloat16* v_pages;
+    const int* block_table;   // [entries][table_width]
+    const int* cu_tokens;     // [entries + 1]
+    const int* context_lens;  // [entries]
+    __nv_bfloat16* out;       // [tokens][heads][D]
+    float* partials;          // decode: [entries][heads][max_splits][D + 2]
+    float scale_log2;         // scale * log2(e)
+    int heads, kv_heads, page_size, table_width, window, max_splits;
+};
+
+// ------------------------------------------------------------------------ small helpers
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16-byte chunks of a row are permuted by the row's low bits so that the eight rows an
+// ldmatrix reads fall into different banks.
+template <int D>
+__device__ __forceinline__ int swizzled(int row, int chunk) {
+    return row * (D / 8) + (chunk ^ (row & 7));
+}
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;  // 0: the destination is filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies `rows` key (or value) rows starting at absolute position `first_key` of one KV head
+// into a swizzled [rows][D] tile.  Rows outside [lowest, last_key] are zero-filled.
+template <int D, int THREADS>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* pages, const int* table,
+                                             int first_key, int rows, int lowest, int last_key, int kv_head,
+                                             const AttnParams& p, int thread) {
+    constexpr int CHUNKS = D / 8;
+    for (int idx = thread; idx < rows * CHUNKS; idx += THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const int key = first_key + row;
+        bool valid = key >= lowest && key <= last_key;
+        const __nv_bfloat16* src = pages;
+        if (valid) {
+            const int page = table[key / p.page_size];
+            valid = page >= 0;
+            if (valid)
+                src = pages + ((static_cast<size_t>(page) * p.kv_heads + kv_head) * p.page_size + key % p.page_size) * D + chunk * 8;
+        }
+        cp_async_16(tile + swizzled<D>(row, chunk) * 8, src, valid);
+    }
+}
+
+// One warp: scores of its 16 query rows against 64 keys.  `q_frag` holds the rows' A fragments.
+template <int D>
+__device__ __forceinline__ void scores_16x64(float (&s)[8][4], const uint32_t (&q_frag)[D / 16][4],
+                                             const __nv_bfloat16* k_tile, int lane) {
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[n][i] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int pair = 0; pair < 4; ++pair) {  // two 8-key tiles per ldmatrix.x4
+            uint32_t b[4];
+            const int key = pair * 16 + (lane & 7) + (lane >> 4) * 8;
+            const int chunk = kk * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, k_tile + swizzled<D>(key, chunk) * 8);
+            mma_bf16(s[pair * 2], q_frag[kk], b[0], b[1]);
+            mma_bf16(s[pair * 2 + 1], q_frag[kk], b[2], b[3]);
+        }
+    }
+}
+
+// One warp: acc[16 x D] += P[16 x 64] V[64 x D], P taken from the score registers.
+template <int D>
+__device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const float (&s)[8][4],
+                                              const __nv_bfloat16* v_tile, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int pair = 0; pair < D / 16; ++pair) {  // two 8-dim tiles per ldmatrix.x4.trans
+            uint32_t b[4];
+            const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int chunk = pair * 2 + (lane >> 4);
+            ldmatrix_x4_trans(b, v_tile + swizzled<D>(key, chunk) * 8);
+            mma_bf16(acc[pair * 2], a, b[0], b[1]);
+            mma_bf16(acc[pair * 2 + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// Masks the scores of one tile, updates the running maximum and sum of the thread's two rows
+// (row `g` and row `g + 8` of the warp's 16) and turns the scores into probabilities.
+// `row_pos[i]` is the absolute position of row i's query; keys are visible in
+// [row_pos - window + 1, row_pos] (window <= 0: from 0).
+template <int D>
+__device__ __forceinline__ void softmax_step(float (&s)[8][4], float (&acc)[D / 8][4], float (&row_max)[2],
+                                             float (&row_sum)[2], const int (&row_pos)[2], int first_key,
+                                             int window, float scale_log2, int lane) {
+    const int col0 = first_key + 2 * (lane & 3);
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = col0 + n * 8 + (i & 1);
+            const int r = i >> 1;
+            const bool visible = key <= row_pos[r] && (window <= 0 || key > row_pos[r] - window);
+            s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
+            tile_max[r] = fmaxf(tile_max[r], s[n][i]);
+        }
+    float rescale[2], base[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float new_max = fmaxf(row_max[r], tile_max[r]);
+        base[r] = new_max == -INFINITY ? 0.0f : new_max;  // a row that has seen nothing yet
+        rescale[r] = exp2f(row_max[r] - base[r]);         // 0 while row_max is -inf
+        row_max[r] = new_max;
+        row_sum[r] *= rescale[r];
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float prob = exp2f(s[n][i] - base[i >> 1]);
+            s[n][i] = prob;
+            row_sum[i >> 1] += prob;
+        }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] *= rescale[i >> 1];
+}
+
+// --------------------------------------------------------------------- portions kernel
+
+template <int D>
+__global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [64][D]
+    __nv_bfloat16* kv_tiles = q_tile + BLOCK_M * D;                  // [2 stages][K | V][64][D]
+
+    const int entry = blockIdx.z, head = blockIdx.y, q_block = blockIdx.x;
+    const int token0 = p.cu_tokens[entry];
+    const int new_tokens = p.cu_tokens[entry + 1] - token0;
+    if (q_block * BLOCK_M >= new_tokens) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows_valid = min(BLOCK_M, new_tokens - q_block * BLOCK_M);
+    const int pos0 = p.context_lens[entry] - new_tokens + q_block * BLOCK_M;  // position of row 0
+    const int last_key = pos0 + rows_valid - 1;
+    const int lowest = p.window > 0 ? max(pos0 - p.window + 1, 0) : 0;
+    const int kv_head = head / (p.heads / p.kv_heads);
+    const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+
+    // Queries of this block -> shared memory (rows past the end are zero).
+    {
+        constexpr int CHUNKS = D / 8;
+        const __nv_bfloat16* q_src = p.q + (static_cast<size_t>(token0 + q_block * BLOCK_M) * p.heads + head) * D;
+        for (int idx = threadIdx.x; idx < BLOCK_M * CHUNKS; idx += ATTN_THREADS) {
+            const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+            const bool valid = row < rows_valid;
+            cp_async_16(q_tile + swizzled<D>(row, chunk) * 8,
+                        valid ? q_src + static_cast<size_t>(row) * p.heads * D + chunk * 8 : p.q, valid);
+        }
+    }
+    const int first_tile = lowest / BLOCK_KEYS, last_tile = last_key / BLOCK_KEYS;
+    auto stage_k = [&](int s) { return kv_tiles + s * 2 * BLOCK_KEYS * D; };
+    auto stage_v = [&](int s) { return kv_tiles + (s * 2 + 1) * BLOCK_KEYS * D; };
+    auto prefetch = [&](int tile, int s) {
+        load_kv_tile<D, ATTN_THREADS>(stage_k(s), p.k_pages, table, tile * BLOCK_KEYS, BLOCK_KEYS, lowest, last_key,
+                                      kv_head, p, threadIdx.x);
+        load_kv_tile<D, ATTN_THREADS>(stage_v(s), p.v_pages, table, tile * BLOCK_KEYS, BLOCK_KEYS, lowest, last_key,
+                                      kv_head, p, threadIdx.x);
+    };
+    prefetch(first_tile, 0);
+    cp_async_commit();
+
+    uint32_t q_frag[D / 16][4];
+    float acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    const int row_pos[2] = {pos0 + warp * 16 + (lane >> 2), pos0 + warp * 16 + (lane >> 2) + 8};
+
+    for (int tile = first_tile; tile <= last_tile; ++tile) {
+        const int s = (tile - first_tile) & 1;
+        if (tile < last_tile) {
+            prefetch(tile + 1, s ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (tile == first_tile) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
+            }
+        }
+        float scores[8][4];
+        scores_16x64<D>(scores, q_frag, stage_k(s), lane);
+        softmax_step<D>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane);
+        accumulate_pv<D>(acc, scores, stage_v(s), lane);
+        __syncthreads();  // the next iteration's prefetch overwrites the other stage's reader
+    }
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= rows_valid) continue;
+        const float inv = 1.0f / row_sum[r];
+        __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * BLOCK_M + row) * p.heads + head) * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const int col = n * 8 + 2 * (lane & 3);
+            *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(acc[n][r * 2] * inv, acc[n][r * 2 + 1] * inv);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------- decode kernels
+
+// grid (splits, kv_heads, entries).  Rows of the score tile are the query heads of the group
+// (at most 16; the rest of the 16 rows are zero).
+template <int D>
+__global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
+    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][64][D]
+
+    const int entry = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
+    const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
+    const int chunk_start = split * DECODE_CHUNK;
+    if (chunk_start > position || chunk_start + DECODE_CHUNK <= lowest) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = p.heads / p.kv_heads;
+    const int token = p.cu_tokens[entry];
+    const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+    constexpr int CHUNKS = D / 8;
+
+    for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += ATTN_THREADS) {
+        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+        const bool valid = row < group;
+        const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.heads + kv_head * group + row) * D + chunk * 8;
+        cp_async_16(q_tile + swizzled<D>(row, chunk) * 8, valid ? src : p.q, valid);
+    }
+    const int first_key = chunk_start + warp * BLOCK_KEYS;
+    const bool active = first_key <= position && first_key + BLOCK_KEYS > lowest;
+    __nv_bfloat16* k_tile = kv_tiles + warp * 2 * BLOCK_KEYS * D;
+    __nv_bfloat16* v_tile = k_tile + BLOCK_KEYS * D;
+    if (active) load_kv_tile<D, 32>(k_tile, p.k_pages, table, first_key, BLOCK_KEYS, lowest, position, kv_head, p, lane);
+    cp_async_commit();
+    if (active) load_kv_tile<D, 32>(v_tile, p.v_pages, table, first_key, BLOCK_KEYS, lowest, position, kv_head, p, lane);
+    cp_async_commit();
+
+    float acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+
+    cp_async_wait<1>();
+    __syncthreads();  // the queries (loaded by all threads) and this warp's keys have landed
+    if (active) {
+        uint32_t q_frag[D / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
+        }
+        float scores[8][4];
+        scores_16x64<D>(scores, q_frag, k_tile, lane);
+        const int row_pos[2] = {position, position};
+        softmax_step<D>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane);
+        cp_async_wait<0>();
+        __syncwarp();
+        accumulate_pv<D>(acc, scores, v_tile, lane);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+        }
+    } else {
+        cp_async_wait<0>();
+    }
+    __syncthreads();  // every warp is done with its key tile: reuse it for the warp's partial
+
+    // Per-warp partial [16][D + 2] float32 in the warp's own K tile (8.3 KB of its 16 KB at D = 128).
+    float* mine = reinterpret_cast<float*>(k_tile);
+    constexpr int STRIDE = D + 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+            const int col = n * 8 + 2 * (lane & 3);
+            mine[row * STRIDE + col] = acc[n][r * 2];
+            mine[row * STRIDE + col + 1] = acc[n][r * 2 + 1];
+        }
+        if ((lane & 3) == 0) {
+            mine[row * STRIDE + D] = row_max[r];
+            mine[row * STRIDE + D + 1] = row_sum[r];
+        }
+    }
+    __syncthreads();
+
+    // Merge the four warps in ascending key order and write the CTA's partial.
+    for (int idx = threadIdx.x; idx < group * STRIDE; idx += ATTN_THREADS) {
+        const int row = idx / STRIDE, col = idx % STRIDE;
+        float warp_max[4], total_max = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            warp_max[w] = reinterpret_cast<const float*>(kv_tiles + w * 2 * BLOCK_KEYS * D)[row * STRIDE + D];
+            total_max = fmaxf(total_max, warp_max[w]);
+        }
+        float value = 0.0f;
+        if (col == D) {
+            value = total_max;
+        } else {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                if (warp_max[w] == -INFINITY) continue;
+                const float* part = reinterpret_cast<const float*>(kv_tiles + w * 2 * BLOCK_KEYS * D);
+                value += part[row * STRIDE + col] * exp2f(warp_max[w] - total_max);
+            }
+        }
+        const int head = kv_head * group + row;
+        p.partials[((static_cast<size_t>(entry) * p.heads + head) * p.max_splits + split) * STRIDE + col] = value;
+    }
+}
+
+// One block per (entry, head): merges the splits that the decode kernel wrote, in ascending order.
+template <int D>
+__global__ void __launch_bounds__(D) attention_decode_merge_kernel(AttnParams p) {
+    const int entry = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+    const int position = p.context_lens[entry] - 1;
+    const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
+    const int first = lowest / DECODE_CHUNK, last = position / DECODE_CHUNK;
+    constexpr int STRIDE = D + 2;
+    const float* base = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
+    float total_max = -INFINITY;
+    for (int s = first; s <= last; ++s) total_max = fmaxf(total_max, base[s * STRIDE + D]);
+    float value = 0.0f, denom = 0.0f;
+    for (int s = first; s <= last; ++s) {
+        const float m = base[s * STRIDE + D];
+        if (m == -INFINITY) continue;
+        const float weight = exp2f(m - total_max);
+        value += base[s * STRIDE + threadIdx.x] * weight;
+        denom += base[s * STRIDE + D + 1] * weight;
+    }
+    const int token = p.cu_tokens[entry];
+    p.out[(static_cast<size_t>(token) * p.heads + head) * D + threadIdx.x] = __float2bfloat16_rn(value / denom);
+}
+
+// -------------------------------------------------------------------------------- host
+
+template <int D>
+static int launch_portions(const AttnParams& p, int entries, int max_new_tokens, cudaStream_t stream) {
+    constexpr int SMEM = (BLOCK_M * D + 4 * BLOCK_KEYS * D) * 2;
+    auto kernel = attention_portions_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid((max_new_tokens + BLOCK_M - 1) / BLOCK_M, p.heads, entries);
+    kernel<<<grid, ATTN_THREADS, SMEM, stream>>>(p);
+    return launch_status();
+}
+
+template <int D>
+static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) {
+    constexpr int SMEM = (16 * D + 8 * BLOCK_KEYS * D) * 2;
+    auto kernel = attention_decode_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid(p.max_splits, p.kv_heads, entries);
+    kernel<<<grid, ATTN_THREADS, SMEM, stream>>>(p);
+    int status = launch_status();
+    if (status != 0) return status;
+    attention_decode_merge_kernel<D><<<entries * p.heads, D, 0, stream>>>(p);
+    return launch_status();
+}
+
+static bool sizes_ok(int head_dim, int heads, int kv_heads) {
+    return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0;
+}
+
+// Any mix of portions and single tokens.  grid.x covers the longest portion.
+ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                         const int* cu_tokens, const int* context_lens, void* out, float scale,
+                                         int entries, int max_new_tokens, int heads, int kv_heads, int head_dim,
+                                         int page_size, int table_width, int window, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
+    AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
+                 static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
+                 static_cast<__nv_bfloat16*>(out), nullptr, scale * LOG2E, heads, kv_heads, page_size, table_width,
+                 window, 0};
+    return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
+                           : launch_portions<64>(p, entries, max_new_tokens, stream);
+}
+
+// Every entry brings exactly one token.  `partials` is scratch of
+// entries * heads * max_splits * (head_dim + 2) floats; max_splits covers the longest context
+// that this launch may meet (ceil(max_context / 256)).
+ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                       const int* cu_tokens, const int* context_lens, void* out, float* partials,
+                                       float scale, int entries, int max_splits, int heads, int kv_heads, int head_dim,
+                                       int page_size, int table_width, int window, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
+    AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
+                 static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
+                 static_cast<__nv_bfloat16*>(out), partials, scale * LOG2E, heads, kv_heads, page_size, table_width,
+                 window, max_splits};
+    return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
+}

@@ -1,7 +1,69 @@
-"""Host side of the bfloat16 tensor-core attention kernels (placeholder until bound)."""
+"""Host side of the bfloat16 tensor-core attention kernels: which kernel a batch takes.
+
+* every entry brings one token and the group has at most 16 query heads: the split decode
+  kernel (scratch for the partial results comes from the workspace);
+* otherwise: the portions kernel, for any mix of portion lengths.
+
+Head sizes 64 and 128 are taken; other sizes use the generic kernel.
+"""
 
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from mini_engine_b200.csrc.build import load_library
+
+DECODE_CHUNK = 256
+_lib = None
+
+
+def _library():
+    global _lib
+    if _lib is None:
+        lib = load_library("attention_bf16")
+        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p]
+        lib.me_attention_portions_bf16.restype = c_int
+        lib.me_attention_decode_bf16.argtypes = [c_void_p] * 8 + [c_float] + [c_int] * 8 + [c_void_p]
+        lib.me_attention_decode_bf16.restype = c_int
+        _lib = lib
+    return _lib
+
 
 def supports(head_dim: int, heads: int, kv_heads: int) -> bool:
-    return False
+    return head_dim in (64, 128) and kv_heads > 0 and heads % kv_heads == 0
+
+
+def decode_splits(max_context_len: int) -> int:
+    return max(1, -(-max_context_len // DECODE_CHUNK))
+
+
+def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window) -> None:
+    from mini_engine_b200.csrc import ops
+
+    for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ops.KernelError(f"{name} must be contiguous bfloat16")
+    if block_table.dtype != torch.int32 or not block_table.is_contiguous():
+        raise ops.KernelError("block_table must be contiguous int32")
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    page_size, width = k_pages.shape[2], block_table.shape[1]
+    entries = ctx.num_entries
+    if ctx.all_decode and heads // kv_heads <= 16:
+        splits = decode_splits(ctx.max_context_len)
+        partials = ctx.workspace.growing("attn.partials", (entries, heads, splits, head_dim + 2), torch.float32)
+        code = _library().me_attention_decode_bf16(
+            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
+            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), scale, entries, splits, heads,
+            kv_heads, head_dim, page_size, width, window, stream,
+        )  # fmt: skip
+        ops._Counter.launches += 1  # the merge kernel; _check counts the first
+        ops._check(code, "attention_decode_bf16")
+        return
+    code = _library().me_attention_portions_bf16(
+        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
+        ctx.context_lens.data_ptr(), out.data_ptr(), scale, entries, ctx.max_query_len, heads, kv_heads, head_dim,
+        page_size, width, window, stream,
+    )  # fmt: skip
+    ops._check(code, "attention_portions_bf16")

@@ -33,6 +33,7 @@ LIBRARIES = {
     "gemm_simt": "gemm_simt.cu",
     "attention_generic": "attention_generic.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
+    "attention_bf16": "attention_bf16.cu",
     "sampling": "sampling.cu",
 }
 

@@ -318,6 +318,71 @@ def test_paged_attention_generic_window():
     assert rel_error(out.cpu(), want) < 2e-5
 
 
+BF16_ATTENTION_CASES = [
+    # lengths, new tokens of each, heads, kv heads, head_dim, page
+    ([1, 16, 17, 33, 100, 255, 256, 257, 600], [1] * 9, 8, 2, 128, 16),  # decode, group 4
+    ([64, 65, 300], [1, 1, 1], 4, 4, 64, 4),  # decode, group 1, small pages
+    ([700, 3], [1, 1], 16, 1, 64, 16),  # decode, group 16
+    ([7, 9, 13], [7, 1, 5], 4, 2, 64, 4),  # fresh prompt, decode, continuation
+    ([300, 64, 2, 129], [300, 33, 2, 65], 6, 2, 128, 8),
+    ([513, 40], [2, 40], 8, 8, 64, 16),
+    ([1000], [1000], 2, 1, 128, 16),
+]
+
+
+def fake_context(data):
+    """What the attention binding reads of a step context."""
+    from types import SimpleNamespace
+
+    from mini_engine_b200.engine.workspace import Workspace
+
+    news, lengths = data["new_counts"], data["lengths"]
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    return SimpleNamespace(
+        num_entries=len(news), all_decode=max(news) == 1, max_query_len=max(news), max_context_len=max(lengths),
+        cu_tokens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
+        context_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"),
+        entry_of_token=data["entry_of"], positions=data["positions"], workspace=Workspace(64),
+    )  # fmt: skip
+
+
+@pytest.mark.parametrize("case", BF16_ATTENTION_CASES)
+def test_paged_attention_bf16_tensor_core(case):
+    from mini_engine_b200.csrc import attention_bf16
+
+    lengths, news, heads, kv_heads, head_dim, page = case
+    assert attention_bf16.supports(head_dim, heads, kv_heads)
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=11, spike=(0, 3))
+    out = torch.full_like(data["q"], float("nan"))
+    attention_bf16.paged_attention(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
+        head_dim, head_dim**-0.5, 0,
+    )  # fmt: skip
+    assert rel_error(out.cpu(), data["want"]) < 1e-2
+
+
+@pytest.mark.parametrize("news", [[1, 1], [90, 5]])
+def test_paged_attention_bf16_window(news):
+    from mini_engine_b200.csrc import attention_bf16
+
+    heads, kv_heads, head_dim, page, window = 4, 2, 64, 8, 70
+    lengths = [400, 90]
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=12)
+    out = torch.full_like(data["q"], float("nan"))
+    attention_bf16.paged_attention(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
+        head_dim, head_dim**-0.5, window,
+    )  # fmt: skip
+    generic = torch.empty_like(out)
+    ops().paged_attention_generic(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], data["entry_of"], data["positions"], generic,
+        heads, kv_heads, head_dim, head_dim**-0.5, window,
+    )  # fmt: skip
+    assert rel_error(out, generic) < 1e-2
+
+
 # ----------------------------------------------------------------------------- sampling
 
 

@@ -43,8 +43,26 @@ TINY_B = {
     "max_position_embeddings": 1024,
     "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 16, "B": 8}
-CONFIGS = {"A": TINY_A, "B": TINY_B}
+# A third size whose head_dim (64) the bfloat16 tensor-core attention kernels take, so that the
+# whole-model replays exercise them too (A and B, at 16 and 32, use the generic kernel).
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 136,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "intermediate_size": 200,
+    "vocab_size": 320,
+    "rope_theta": 500000.0,
+    "rms_norm_eps": 3e-6,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 2048,
+    "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
 
 def random_ids(seed: int, count: int, vocab: int) -> list[int]:
