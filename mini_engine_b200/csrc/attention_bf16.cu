@@ -491,3 +491,41 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                  window, max_splits};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
+
+// ------------------------------------------------- decode attention without allocation
+
+#include "attention_bf16_noalloc.h"
+
+// Scratch of the allocation-free entry point: partial results of the split decode kernel.
+// It lives in the library's image, so every GPU on which this library is loaded holds these
+// 8 MiB from the first use of the library until the process exits.
+static __device__ __align__(256) float g_noalloc_partials[ME_NOALLOC_MAX_PARTIAL_FLOATS];
+
+// In host code `g_noalloc_partials` names a host-side shadow of the device array, not device
+// memory, so it must never be handed to a kernel.  The device address is looked up once per
+// device, with that device current, and remembered here.
+static float* g_noalloc_address[ME_NOALLOC_MAX_DEVICES] = {};
+
+ME_EXPORT int me_attention_decode_bf16_noalloc(const void* q, const void* k_pages, const void* v_pages,
+                                               const int* block_table, const int* cu_tokens, const int* context_lens,
+                                               void* out, float scale, int entries, int max_splits, int heads,
+                                               int kv_heads, int head_dim, int page_size, int table_width, int window,
+                                               cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (max_splits < 1 || heads < 1) return ME_ERR_ARGUMENT;
+    const long long needed = static_cast<long long>(entries) * heads * max_splits * (head_dim + 2);
+    if (needed > ME_NOALLOC_MAX_PARTIAL_FLOATS) return ME_ERR_NOALLOC_TOO_LARGE;
+    int device = -1;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return static_cast<int>(status);
+    if (device < 0 || device >= ME_NOALLOC_MAX_DEVICES) return ME_ERR_ARGUMENT;
+    if (g_noalloc_address[device] == nullptr) {
+        void* address = nullptr;
+        status = cudaGetSymbolAddress(&address, g_noalloc_partials);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        g_noalloc_address[device] = static_cast<float*>(address);
+    }
+    return me_attention_decode_bf16(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out,
+                                    g_noalloc_address[device], scale, entries, max_splits, heads, kv_heads, head_dim,
+                                    page_size, table_width, window, stream);
+}

@@ -87,7 +87,7 @@ def _find_build_dir() -> Path:
 def _source_hash(source: Path) -> str:
     digest = hashlib.sha256()
     digest.update(source.read_bytes())
-    for header in sorted(SOURCE_DIR.glob("*.cuh")):
+    for header in sorted(list(SOURCE_DIR.glob("*.cuh")) + list(SOURCE_DIR.glob("*.h"))):
         digest.update(header.read_bytes())
     digest.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
     return digest.hexdigest()[:16]
