@@ -205,6 +205,7 @@ class ModelRunner:
             host={
                 "counts": counts + [1] * (total_entries - real),
                 "starts": [e.start for e in entries] + [0] * (total_entries - real),
+                "state_slots": [int(x) for x in state[:total_entries]],
             },
         )
         return ctx, at(o_rows, len(wanted_rows))

@@ -119,7 +119,14 @@ class GroupedQueryAttention(Mixer):
             k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, positions=ctx.positions, q_out=q,
             page_size=ctx.page_size,
         )  # fmt: skip
-        if table is not None or kv_in == 0:
+        if kv_in and not cache.writes:
+            # This execution reads another entry's cache: its own keys and values are not kept.
+            unused_k = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
+            unused_v = ctx.buffer("attn.v_new", (tokens, kv_in * d), ctx.dtype)
+            ops.qk_norm_rope_store(**args, inv_freq=table, k_dense=unused_k, v_dense=unused_v)
+            if table is None:
+                self.position.apply(q.view(tokens, self.heads, d), unused_k.view(tokens, kv_in, d), ctx.positions)
+        elif table is not None or kv_in == 0:
             ops.qk_norm_rope_store(
                 **args, inv_freq=table, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v
             )

@@ -154,3 +154,26 @@ def test_bfloat16_generation_runs_and_mostly_agrees(peaked_model_folders):
     got = engine_for(folder, "B", dtype=torch.bfloat16, max_num_batched_tokens=40).generate(prompts, params)
     agree = sum(a == b for x, y in zip(got, reference) for a, b in zip(x[:1], y[:1]))
     assert agree >= 2  # the first generated token of at least two of three requests
+
+
+def test_command_line(peaked_model_folders):
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    folder = peaked_model_folders["A"]
+    proc = subprocess.run(
+        [sys.executable, str(ROOT / "examples" / "generate.py"), "--model", str(folder), "--dtype", "fp32",
+         "--max-tokens", "5", "--block-size", "16", "--num-blocks", "32", "--max-model-len", "256"],
+        capture_output=True, text=True, timeout=600,
+    )  # fmt: skip
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.strip().splitlines()
+    assert len(lines) == 4 and lines[-1].startswith("15 tokens in")
+    assert "served from prefix cache 128" in lines[-1]  # two later requests reuse four pages each
+    refused = subprocess.run(
+        [sys.executable, str(ROOT / "examples" / "generate.py"), "--model", str(folder), "--device", "cpu"],
+        capture_output=True, text=True, timeout=600,
+    )  # fmt: skip
+    assert refused.returncode == 2 and "CUDA only" in refused.stderr

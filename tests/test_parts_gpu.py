@@ -1,0 +1,372 @@
+"""Each part of a layer alone against the plain implementation, at sizes of its own; models
+whose order repeats a layer, reads another entry's cache or uses a window; and a toy mixer
+with state of its own that is registered, built and stepped from here without touching the
+framework's files."""
+
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+# ------------------------------------------------------------------ a small harness
+
+
+def make_runner(spec, dtype=torch.float32, page=4, pages=64, seed=0, scale=5.0):
+    """A model of `spec` with seeded random weights, its runner and a cache manager."""
+    from mini_engine_b200.cache import CacheManager
+    from mini_engine_b200.engine.runner import ModelRunner
+    from mini_engine_b200.parts.model import DecoderModel
+    from mini_engine_b200.weights.loader import place_tensors
+    from mini_engine_b200.weights.random_init import random_tensors
+
+    model = DecoderModel(spec)
+    specs = model.weight_specs()
+    host = random_tensors(specs, seed, torch.float32, scale=scale)
+    model.load(place_tensors(dict(host), specs, dtype, "cuda"))
+    runner = ModelRunner(model, dtype=dtype, num_blocks=pages, block_size=page, max_num_seqs=4,
+                         max_num_batched_tokens=256, max_model_len=pages * page)  # fmt: skip
+    manager = CacheManager(runner.layout.groups, pages, page, 4, False, has_state=runner.layout.has_state)
+    return model, runner, manager, host
+
+
+def one_layer_spec(hidden, heads, kv_heads, head_dim, inter, vocab=50, window=None, theta=777.0, eps=2e-5, layers=1,
+                   order=None):
+    from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
+
+    rope = PartSpec("rope", {"head_dim": head_dim, "theta": theta})
+    layer_specs = tuple(
+        LayerSpec(
+            prefix=f"model.layers.{i}.",
+            block="prenorm",
+            mixer=PartSpec("gqa_attention", {
+                "num_heads": heads, "kv_heads": kv_heads, "head_dim": head_dim, "qk_norm_eps": eps,
+                "position_encoding": rope, "window": window,
+                "names": {k: f"self_attn.{k}_proj.weight" for k in "qkvo"} | {
+                    "q_norm": "self_attn.q_norm.weight", "k_norm": "self_attn.k_norm.weight"},
+            }),
+            feed_forward=PartSpec("gated_mlp", {"intermediate_size": inter, "names": {
+                "gate": "mlp.gate_proj.weight", "up": "mlp.up_proj.weight", "down": "mlp.down_proj.weight"}}),
+            mixer_norm=PartSpec("rmsnorm", {"name": "input_layernorm.weight", "eps": eps}),
+            feed_forward_norm=PartSpec("rmsnorm", {"name": "post_attention_layernorm.weight", "eps": eps}),
+        )
+        for i in range(layers)
+    )  # fmt: skip
+    return ModelSpec(
+        vocab_size=vocab, hidden_size=hidden,
+        embedding=PartSpec("token_embedding", {"weight": "model.embed_tokens.weight"}),
+        layers=layer_specs, order=tuple(order or [OrderEntry(i) for i in range(layers)]),
+        final_norm=PartSpec("rmsnorm", {"name": "model.norm.weight", "eps": eps}),
+        head=PartSpec("linear_head", {"weight": "lm_head.weight", "tied_to": None}),
+    )  # fmt: skip
+
+
+def plain_cfg(hidden, heads, kv_heads, head_dim, inter, vocab=50, window=None, theta=777.0, eps=2e-5, layers=1):
+    return {"vocab": vocab, "hidden": hidden, "inter": inter, "layers": layers, "heads": heads, "kv_heads": kv_heads,
+            "head_dim": head_dim, "eps": eps, "theta": theta, "tied": False, "window": window}  # fmt: skip
+
+
+def context_for(runner, manager, lengths):
+    from mini_engine_b200.engine.runner import StepEntry
+
+    entries = []
+    for n in lengths:
+        cache = manager.new_request()
+        assert manager.try_allocate(cache, n)
+        entries.append(StepEntry(cache, 0, [1] * n, ()))
+    ctx, _ = runner.pack(entries)
+    return ctx
+
+
+SIZES = dict(hidden=48, heads=6, kv_heads=2, head_dim=16, inter=72)
+
+
+# ----------------------------------------------------------------------- parts alone
+
+
+def test_rmsnorm_part_alone():
+    from mini_engine_b200.parts.base import Residual
+
+    model, runner, manager, host = make_runner(one_layer_spec(**SIZES))
+    norm = model.blocks[0].mixer_norm
+    ctx = context_for(runner, manager, [5, 3])
+    torch.manual_seed(0)
+    x, delta = torch.randn(8, 48, device="cuda"), torch.randn(2, 8, 48, device="cuda")
+    state = Residual(x.clone(), delta)
+    out = norm.forward(state, ctx, torch.float32)
+    summed = x + delta.sum(0)
+    want = plain.rms_norm(summed.cpu(), host["model.layers.0.input_layernorm.weight"], 2e-5)
+    assert state.pending is None and torch.allclose(state.x, summed, atol=1e-6)
+    assert torch.allclose(out.cpu(), want, atol=1e-5, rtol=1e-5)
+
+
+def test_rotary_part_alone():
+    from mini_engine_b200.parts.rotary import RotaryEncoding
+
+    part = RotaryEncoding("", 0, head_dim=48, theta=12345.0)
+    want = 1.0 / (12345.0 ** (torch.arange(0, 48, 2, dtype=torch.float32) / 48))
+    assert torch.equal(part.fused_rotary_table().cpu(), want)
+
+
+@pytest.mark.parametrize("window", [None, 5])
+def test_attention_mixer_alone(window):
+    model, runner, manager, host = make_runner(one_layer_spec(**SIZES, window=window))
+    mixer = model.blocks[0].mixer
+    lengths = [13, 1, 7]
+    ctx = context_for(runner, manager, lengths)
+    torch.manual_seed(1)
+    h = torch.randn(sum(lengths), 48, device="cuda")
+    out = mixer.forward(h, ctx, runner.layout.views[0]).sum(0).cpu()
+    cfg = plain_cfg(**SIZES, window=window)
+    start = 0
+    for n in lengths:
+        want = plain.attention_block(h[start : start + n].cpu(), host, "model.layers.0.self_attn.", cfg, torch.arange(n))
+        assert torch.allclose(out[start : start + n], want, atol=2e-5, rtol=1e-4)
+        start += n
+
+
+def test_feed_forward_alone():
+    model, runner, manager, host = make_runner(one_layer_spec(**SIZES))
+    ctx = context_for(runner, manager, [9])
+    torch.manual_seed(2)
+    h = torch.randn(9, 48, device="cuda")
+    out = model.blocks[0].feed_forward.forward(h, ctx).sum(0).cpu()
+    want = plain.swiglu_mlp(h.cpu(), host, "model.layers.0.mlp.")
+    assert torch.allclose(out, want, atol=2e-5, rtol=1e-4)
+
+
+def test_block_alone():
+    from mini_engine_b200.parts.base import Residual
+
+    model, runner, manager, host = make_runner(one_layer_spec(**SIZES))
+    ctx = context_for(runner, manager, [11])
+    torch.manual_seed(3)
+    x = torch.randn(11, 48, device="cuda")
+    state = Residual(x.clone())
+    model.blocks[0].forward(state, ctx, runner.layout.views[0])
+    got = (state.x + state.pending.sum(0)).cpu()
+    want = plain.decoder_layer(x.cpu(), host, 0, plain_cfg(**SIZES), torch.arange(11))
+    assert torch.allclose(got, want, atol=3e-5, rtol=1e-4)
+
+
+# ------------------------------------------------- order as data: repeats, shared caches
+
+
+def run_whole_and_cut(runner, manager, tokens):
+    """Logits of a request run whole and run in portions of 5, 1, 1, 4, ... tokens."""
+    from mini_engine_b200.engine.runner import StepEntry
+
+    cache = manager.new_request()
+    assert manager.try_allocate(cache, len(tokens))
+    whole = runner.execute([StepEntry(cache, 0, tokens, tuple(range(len(tokens))))]).cpu().clone()
+    manager.free(cache)
+    cache = manager.new_request()
+    rows, done = [], 0
+    for size in [5, 1, 1, 4, 2, 100]:
+        chunk = tokens[done : done + size]
+        if not chunk:
+            break
+        assert manager.try_allocate(cache, done + len(chunk))
+        rows.append(runner.execute([StepEntry(cache, done, chunk, tuple(range(len(chunk))))]).cpu().clone())
+        done += len(chunk)
+        manager.release_behind_window(cache, done)
+    manager.free(cache)
+    return whole, torch.cat(rows)
+
+
+def test_a_layer_twice_and_a_layer_reading_anothers_cache():
+    """order = [0, 1, 0 (reading entry 0's cache), 1]: weights of a layer are shared by its two
+    executions; the third entry attends over the keys that the first one wrote."""
+    from mini_engine_b200.config.model_spec import LayerSpec, OrderEntry, PartSpec
+
+    base = one_layer_spec(**SIZES, layers=2)
+    order = (OrderEntry(0), OrderEntry(1), OrderEntry(0, cache_of=0), OrderEntry(1))
+    spec = type(base)(**{**base.__dict__, "order": order})
+    model, runner, manager, host = make_runner(spec)
+    assert len(runner.layout.views) == 4 and runner.layout.views[2].k.data_ptr() == runner.layout.views[0].k.data_ptr()
+    assert runner.layout.views[3].k.data_ptr() != runner.layout.views[1].k.data_ptr()
+    tokens = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)  # float32: cutting changes nothing
+
+    # plain restatement of the same order
+    cfg = plain_cfg(**SIZES, layers=2)
+    w = host
+    ids, pos = torch.tensor(tokens), torch.arange(len(tokens))
+    x = w["model.embed_tokens.weight"][ids]
+
+    def attention(x_in, layer, keys_from=None):
+        p = f"model.layers.{layer}.self_attn."
+        t, d = x_in.shape[0], cfg["head_dim"]
+        source = x_in if keys_from is None else keys_from
+        q = plain.rms_norm((x_in @ w[p + "q_proj.weight"].T).view(t, cfg["heads"], d), w[p + "q_norm.weight"], cfg["eps"])
+        k = plain.rms_norm((source @ w[p + "k_proj.weight"].T).view(t, cfg["kv_heads"], d), w[p + "k_norm.weight"], cfg["eps"])
+        v = (source @ w[p + "v_proj.weight"].T).view(t, cfg["kv_heads"], d)
+        cos, sin = plain.rope_angles(pos, d, cfg["theta"], torch.float32)
+        out = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v)
+        return out.reshape(t, -1) @ w[p + "o_proj.weight"].T
+
+    normed_first = None
+    for position, entry in enumerate(order):
+        p = f"model.layers.{entry.layer}."
+        normed = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+        if position == 0:
+            normed_first = normed
+        # the entry that reads entry 0's cache sees the keys and values entry 0 computed
+        x = x + attention(normed, entry.layer, normed_first if entry.cache_of == 0 else None)
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+    want = plain.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
+
+
+def test_layers_with_and_without_a_window_get_groups_of_their_own():
+    from mini_engine_b200.config.model_spec import PartSpec
+
+    base = one_layer_spec(**SIZES, layers=2)
+    windowed = base.layers[1]
+    mixer = PartSpec(windowed.mixer.kind, {**windowed.mixer.params, "window": 6})
+    layers = (base.layers[0], type(windowed)(**{**windowed.__dict__, "mixer": mixer}))
+    spec = type(base)(**{**base.__dict__, "layers": layers})
+    model, runner, manager, host = make_runner(spec, page=4)
+    assert len(runner.layout.groups) == 2 and [g.window for g in runner.layout.groups] == [None, 6]
+    tokens = list(range(1, 30))
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+    manager.check_invariants([])
+    # plain: layer 0 full, layer 1 with the window
+    cfg0, cfg1 = plain_cfg(**SIZES, layers=2), plain_cfg(**SIZES, layers=2, window=6)
+    x = host["model.embed_tokens.weight"][torch.tensor(tokens)]
+    x = plain.decoder_layer(x, host, 0, cfg0, torch.arange(len(tokens)))
+    x = plain.decoder_layer(x, host, 1, cfg1, torch.arange(len(tokens)))
+    want = plain.rms_norm(x, host["model.norm.weight"], cfg0["eps"]) @ host["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
+
+
+# --------------------------------------------------- a toy mixer with state of its own
+
+
+def register_toy():
+    """A mixer that keeps a decaying sum of its inputs per request: s_t = a * s_{t-1} + h_t,
+    y_t = s_t W^T.  It owns no pages, only a state slot.  Everything is defined here."""
+    from mini_engine_b200.config import Architecture, register_architecture
+    from mini_engine_b200.config.model_spec import LayerSpec, ModelSpec, OrderEntry, PartSpec
+    from mini_engine_b200.parts.base import MIXERS, Mixer, StateSpec, register
+    from mini_engine_b200.weights.loader import WeightSpec
+
+    if "toy_decay" not in MIXERS:
+
+        @register("mixer", "toy_decay")
+        class ToyDecay(Mixer):
+            def __init__(self, prefix, hidden_size, *, decay):
+                self.name, self.hidden, self.decay = prefix + "toy.weight", hidden_size, decay
+                self.weight = None
+
+            def state(self):
+                return StateSpec((self.hidden,), torch.float32)
+
+            def weight_specs(self):
+                return [WeightSpec(self.name, (self.hidden, self.hidden))]
+
+            def load(self, tensors):
+                self.weight = tensors[self.name].float()
+
+            def forward(self, h, ctx, cache):
+                out = torch.empty(1, h.shape[0], self.hidden, device=h.device)
+                row = 0
+                for count, start, slot in zip(ctx.host["counts"], ctx.host["starts"], ctx.host["state_slots"]):
+                    state = cache.state[slot]
+                    if start == 0:
+                        state.zero_()
+                    for _ in range(count):
+                        state.mul_(self.decay).add_(h[row].float())
+                        out[0, row] = state @ self.weight.T
+                        row += 1
+                return out
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+        hidden_size: int
+        intermediate_size: int
+        decay: float
+        eps: float
+        architecture = "ToyDecayLM"
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+                    "intermediate_size": self.intermediate_size, "decay": self.decay, "eps": self.eps}  # fmt: skip
+
+        @classmethod
+        def from_folder(cls, folder):
+            raw = json.loads((Path(folder) / "config.json").read_text())
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["intermediate_size"], raw["decay"], raw["eps"])
+
+    def spec(cfg):
+        layer = LayerSpec(
+            prefix="layers.0.", block="prenorm", mixer=PartSpec("toy_decay", {"decay": cfg.decay}),
+            feed_forward=PartSpec("gated_mlp", {"intermediate_size": cfg.intermediate_size}),
+            mixer_norm=PartSpec("rmsnorm", {"name": "norm1.weight", "eps": cfg.eps}),
+            feed_forward_norm=PartSpec("rmsnorm", {"name": "norm2.weight", "eps": cfg.eps}),
+        )  # fmt: skip
+        return ModelSpec(
+            vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size,
+            embedding=PartSpec("token_embedding", {"weight": "embed.weight"}), layers=(layer,),
+            order=(OrderEntry(0), OrderEntry(0)),  # the same layer twice: two states
+            final_norm=PartSpec("rmsnorm", {"name": "final.weight", "eps": cfg.eps}),
+            head=PartSpec("linear_head", {"weight": "head.weight", "tied_to": "embed.weight"}),
+        )  # fmt: skip
+
+    register_architecture(Architecture("ToyDecayLM", ToyConfig.from_folder, spec, ToyConfig), replace=True)
+    return ToyConfig
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from safetensors.torch import load_file
+
+    from mini_engine_b200.engine.replay import Replayer
+    from mini_engine_b200.weights import write_random_model
+
+    ToyConfig = register_toy()
+    cfg = ToyConfig(vocab_size=40, hidden_size=24, intermediate_size=32, decay=0.7, eps=1e-5)
+    folder = write_random_model(tmp_path / "toy", cfg, seed=5, dtype=torch.float32, scale=8.0)
+    replayer = Replayer(folder, torch.float32, max_tokens=128, block_size=16)
+    assert replayer.runner.layout.has_state and replayer.runner.layout.groups == []
+    assert not replayer.manager.enable_prefix_caching  # state cannot be shared through page hashes
+
+    a, b = [3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], [8, 9, 7, 9, 3, 2]
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:4], "want": [0, 1, 2, 3]}]},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[4:5], "want": [0]}, {"id": "b", "tokens": b[:3], "want": [0, 1, 2]}]},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[3:], "want": [0, 1, 2]}, {"id": "a", "tokens": a[5:], "want": list(range(6))}], "end": ["a", "b"]},
+        {"step": 3, "entries": [{"id": "c", "tokens": b, "want": list(range(6))}], "end": ["c"]},  # reuses a slot
+    ]  # fmt: skip
+    got = {s["step"]: replayer.step(s) for s in steps}
+    replayer.manager.check_invariants([])
+
+    w = load_file(str(folder / "model.safetensors"))
+
+    def plain_toy(tokens):
+        x = w["embed.weight"][torch.tensor(tokens)]
+        for _ in range(2):
+            normed = plain.rms_norm(x, w["layers.0.norm1.weight"], cfg.eps)
+            state, rows = torch.zeros(cfg.hidden_size), []
+            for t in range(len(tokens)):
+                state = cfg.decay * state + normed[t]
+                rows.append(state @ w["layers.0.toy.weight"].T)
+            x = x + torch.stack(rows)
+            x = x + plain.swiglu_mlp(plain.rms_norm(x, w["layers.0.norm2.weight"], cfg.eps), w, "layers.0.")
+        return plain.rms_norm(x, w["final.weight"], cfg.eps) @ w["embed.weight"].T
+
+    want_a, want_b = plain_toy(a), plain_toy(b)
+    assert torch.allclose(got[0], want_a[:4], atol=1e-4, rtol=1e-4)
+    assert torch.allclose(got[1], torch.cat([want_a[4:5], want_b[:3]]), atol=1e-4, rtol=1e-4)
+    assert torch.allclose(got[2], torch.cat([want_b[3:], want_a[5:]]), atol=1e-4, rtol=1e-4)
+    assert torch.allclose(got[3], want_b, atol=1e-4, rtol=1e-4)
