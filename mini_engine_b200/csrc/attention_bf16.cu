@@ -5,8 +5,8 @@
 //   * portions (any number of new tokens per request): one CTA per (request, query head,
 //     64 consecutive new tokens); it walks the request's keys in tiles of 64 that start at
 //     multiples of 64 in absolute position, double-buffered through shared memory.
-//   * decode (one new token per request): one CTA per (request, KV head, 256 keys); all query
-//     heads of the group share the keys that are read; each of its four warps takes 64 keys;
+//   * decode (one new token per request): one CTA per (request, KV head, 128 keys); all query
+//     heads of the group share the keys that are read; each of its four warps takes 32 keys;
 //     the CTA writes one partial (max, sum, unnormalised output) per head to scratch memory,
 //     and a second kernel merges a request's partials in ascending key order.  The split
 //     depends on positions only, never on the batch.
@@ -26,7 +26,8 @@
 constexpr int BLOCK_M = 64;   // query rows per CTA (portions)
 constexpr int BLOCK_KEYS = 64;  // keys per tile
 constexpr int ATTN_THREADS = 128;
-constexpr int DECODE_CHUNK = 256;  // keys per decode CTA: 4 warps x 64
+constexpr int DECODE_WARP_KEYS = 32;
+constexpr int DECODE_CHUNK = 4 * DECODE_WARP_KEYS;  // keys per decode CTA
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
@@ -40,6 +41,7 @@ struct AttnParams {
     float* partials;          // decode: [entries][heads][max_splits][D + 2]
     float scale_log2;         // scale * log2(e)
     int heads, kv_heads, page_size, table_width, window, max_splits;
+    int page_shift;  // log2(page_size) when it is a power of two, else -1
 };
 
 // ------------------------------------------------------------------------ small helpers
@@ -79,40 +81,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copies `rows` key (or value) rows starting at absolute position `first_key` of one KV head
-// into a swizzled [rows][D] tile.  Rows outside [lowest, last_key] are zero-filled.
-template <int D, int THREADS>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* pages, const int* table,
-                                             int first_key, int rows, int lowest, int last_key, int kv_head,
-                                             const AttnParams& p, int thread) {
-    constexpr int CHUNKS = D / 8;
-    for (int idx = thread; idx < rows * CHUNKS; idx += THREADS) {
-        const int row = idx / CHUNKS, chunk = idx % CHUNKS;
-        const int key = first_key + row;
-        bool valid = key >= lowest && key <= last_key;
-        const __nv_bfloat16* src = pages;
-        if (valid) {
-            const int page = table[key / p.page_size];
-            valid = page >= 0;
-            if (valid)
-                src = pages + ((static_cast<size_t>(page) * p.kv_heads + kv_head) * p.page_size + key % p.page_size) * D + chunk * 8;
-        }
-        cp_async_16(tile + swizzled<D>(row, chunk) * 8, src, valid);
+// Element offset of a key's row inside the page arrays (the same for keys and values), or -1
+// when the key is outside [lowest, last_key] or its page was given back.
+__device__ __forceinline__ long long key_row_offset(const AttnParams& p, const int* table, int key, int lowest,
+                                                    int last_key, int kv_head, int head_dim) {
+    if (key < lowest || key > last_key) return -1;
+    int page_index, slot;
+    if (p.page_shift >= 0) {
+        page_index = key >> p.page_shift;
+        slot = key & (p.page_size - 1);
+    } else {
+        page_index = key / p.page_size;
+        slot = key - page_index * p.page_size;
     }
+    const int page = table[page_index];
+    if (page < 0) return -1;
+    return ((static_cast<long long>(page) * p.kv_heads + kv_head) * p.page_size + slot) * head_dim;
 }
 
-// One warp: scores of its 16 query rows against 64 keys.  `q_frag` holds the rows' A fragments.
-template <int D>
-__device__ __forceinline__ void scores_16x64(float (&s)[8][4], const uint32_t (&q_frag)[D / 16][4],
-                                             const __nv_bfloat16* k_tile, int lane) {
+// One warp: scores of its 16 query rows against KEYS keys.  `q_frag` holds the rows' A fragments.
+template <int D, int KEYS>
+__device__ __forceinline__ void scores_tile(float (&s)[KEYS / 8][4], const uint32_t (&q_frag)[D / 16][4],
+                                            const __nv_bfloat16* k_tile, int lane) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < KEYS / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[n][i] = 0.0f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-        for (int pair = 0; pair < 4; ++pair) {  // two 8-key tiles per ldmatrix.x4
+        for (int pair = 0; pair < KEYS / 16; ++pair) {  // two 8-key tiles per ldmatrix.x4
             uint32_t b[4];
             const int key = pair * 16 + (lane & 7) + (lane >> 4) * 8;
             const int chunk = kk * 2 + ((lane >> 3) & 1);
@@ -123,12 +121,12 @@ __device__ __forceinline__ void scores_16x64(float (&s)[8][4], const uint32_t (&
     }
 }
 
-// One warp: acc[16 x D] += P[16 x 64] V[64 x D], P taken from the score registers.
-template <int D>
-__device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const float (&s)[8][4],
+// One warp: acc[16 x D] += P[16 x KEYS] V[KEYS x D], P taken from the score registers.
+template <int D, int KEYS>
+__device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const float (&s)[KEYS / 8][4],
                                               const __nv_bfloat16* v_tile, int lane) {
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+    for (int kk = 0; kk < KEYS / 16; ++kk) {  // 16 keys per step
         uint32_t a[4];
         a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
         a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -150,14 +148,14 @@ __device__ __forceinline__ void accumulate_pv(float (&acc)[D / 8][4], const floa
 // (row `g` and row `g + 8` of the warp's 16) and turns the scores into probabilities.
 // `row_pos[i]` is the absolute position of row i's query; keys are visible in
 // [row_pos - window + 1, row_pos] (window <= 0: from 0).
-template <int D>
-__device__ __forceinline__ void softmax_step(float (&s)[8][4], float (&acc)[D / 8][4], float (&row_max)[2],
+template <int D, int KEYS>
+__device__ __forceinline__ void softmax_step(float (&s)[KEYS / 8][4], float (&acc)[D / 8][4], float (&row_max)[2],
                                              float (&row_sum)[2], const int (&row_pos)[2], int first_key,
                                              int window, float scale_log2, int lane) {
     const int col0 = first_key + 2 * (lane & 3);
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < KEYS / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = col0 + n * 8 + (i & 1);
@@ -178,7 +176,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[8][4], float (&acc)[D / 
         row_sum[r] *= rescale[r];
     }
 #pragma unroll
-    for (int n = 0; n < 8; ++n)
+    for (int n = 0; n < KEYS / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float prob = exp2f(s[n][i] - base[i >> 1]);
@@ -198,8 +196,12 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
     extern __shared__ __align__(128) uint8_t smem[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [64][D]
     __nv_bfloat16* kv_tiles = q_tile + BLOCK_M * D;                  // [2 stages][K | V][64][D]
+    constexpr int CHUNKS = D / 8;
+    constexpr int ROWS_PER_PASS = ATTN_THREADS / CHUNKS;
+    constexpr int PASSES = BLOCK_KEYS / ROWS_PER_PASS;
 
-    const int entry = blockIdx.z, head = blockIdx.y, q_block = blockIdx.x;
+    // Later blocks of a request see more keys: start them first so that the grid's tail is short.
+    const int entry = blockIdx.z, head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
     const int token0 = p.cu_tokens[entry];
     const int new_tokens = p.cu_tokens[entry + 1] - token0;
     if (q_block * BLOCK_M >= new_tokens) return;
@@ -210,26 +212,32 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
     const int lowest = p.window > 0 ? max(pos0 - p.window + 1, 0) : 0;
     const int kv_head = head / (p.heads / p.kv_heads);
     const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+    const int my_chunk = threadIdx.x % CHUNKS, my_row = threadIdx.x / CHUNKS;
 
     // Queries of this block -> shared memory (rows past the end are zero).
     {
-        constexpr int CHUNKS = D / 8;
         const __nv_bfloat16* q_src = p.q + (static_cast<size_t>(token0 + q_block * BLOCK_M) * p.heads + head) * D;
-        for (int idx = threadIdx.x; idx < BLOCK_M * CHUNKS; idx += ATTN_THREADS) {
-            const int row = idx / CHUNKS, chunk = idx % CHUNKS;
+#pragma unroll
+        for (int pass = 0; pass < BLOCK_M / ROWS_PER_PASS; ++pass) {
+            const int row = pass * ROWS_PER_PASS + my_row;
             const bool valid = row < rows_valid;
-            cp_async_16(q_tile + swizzled<D>(row, chunk) * 8,
-                        valid ? q_src + static_cast<size_t>(row) * p.heads * D + chunk * 8 : p.q, valid);
+            cp_async_16(q_tile + swizzled<D>(row, my_chunk) * 8,
+                        valid ? q_src + static_cast<size_t>(row) * p.heads * D + my_chunk * 8 : p.q, valid);
         }
     }
     const int first_tile = lowest / BLOCK_KEYS, last_tile = last_key / BLOCK_KEYS;
-    auto stage_k = [&](int s) { return kv_tiles + s * 2 * BLOCK_KEYS * D; };
-    auto stage_v = [&](int s) { return kv_tiles + (s * 2 + 1) * BLOCK_KEYS * D; };
     auto prefetch = [&](int tile, int s) {
-        load_kv_tile<D, ATTN_THREADS>(stage_k(s), p.k_pages, table, tile * BLOCK_KEYS, BLOCK_KEYS, lowest, last_key,
-                                      kv_head, p, threadIdx.x);
-        load_kv_tile<D, ATTN_THREADS>(stage_v(s), p.v_pages, table, tile * BLOCK_KEYS, BLOCK_KEYS, lowest, last_key,
-                                      kv_head, p, threadIdx.x);
+        __nv_bfloat16* k_tile = kv_tiles + s * 2 * BLOCK_KEYS * D;
+        __nv_bfloat16* v_tile = k_tile + BLOCK_KEYS * D;
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) {
+            const int row = pass * ROWS_PER_PASS + my_row;
+            const long long offset = key_row_offset(p, table, tile * BLOCK_KEYS + row, lowest, last_key, kv_head, D);
+            const bool valid = offset >= 0;
+            const long long at = valid ? offset + my_chunk * 8 : 0;
+            cp_async_16(k_tile + swizzled<D>(row, my_chunk) * 8, p.k_pages + at, valid);
+            cp_async_16(v_tile + swizzled<D>(row, my_chunk) * 8, p.v_pages + at, valid);
+        }
     };
     prefetch(first_tile, 0);
     cp_async_commit();
@@ -260,10 +268,11 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
                 ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
             }
         }
-        float scores[8][4];
-        scores_16x64<D>(scores, q_frag, stage_k(s), lane);
-        softmax_step<D>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane);
-        accumulate_pv<D>(acc, scores, stage_v(s), lane);
+        const __nv_bfloat16* k_tile = kv_tiles + s * 2 * BLOCK_KEYS * D;
+        float scores[BLOCK_KEYS / 8][4];
+        scores_tile<D, BLOCK_KEYS>(scores, q_frag, k_tile, lane);
+        softmax_step<D, BLOCK_KEYS>(scores, acc, row_max, row_sum, row_pos, tile * BLOCK_KEYS, p.window, p.scale_log2, lane);
+        accumulate_pv<D, BLOCK_KEYS>(acc, scores, k_tile + BLOCK_KEYS * D, lane);
         __syncthreads();  // the next iteration's prefetch overwrites the other stage's reader
     }
 
@@ -289,12 +298,16 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
 // ----------------------------------------------------------------------- decode kernels
 
 // grid (splits, kv_heads, entries).  Rows of the score tile are the query heads of the group
-// (at most 16; the rest of the 16 rows are zero).
+// (at most 16; the rest of the 16 rows are zero).  Three CTAs fit an SM, so one CTA's loads
+// overlap another's arithmetic.
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int KEYS = DECODE_WARP_KEYS;
+    constexpr int CHUNKS = D / 8;
+    constexpr int WARP_TILE = 2 * KEYS * D;  // elements of one warp's K and V tiles
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
-    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][64][D]
+    __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][KEYS][D]
 
     const int entry = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
     const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
@@ -305,7 +318,6 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     const int group = p.heads / p.kv_heads;
     const int token = p.cu_tokens[entry];
     const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
-    constexpr int CHUNKS = D / 8;
 
     for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += ATTN_THREADS) {
         const int row = idx / CHUNKS, chunk = idx % CHUNKS;
@@ -313,13 +325,28 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
         const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.heads + kv_head * group + row) * D + chunk * 8;
         cp_async_16(q_tile + swizzled<D>(row, chunk) * 8, valid ? src : p.q, valid);
     }
-    const int first_key = chunk_start + warp * BLOCK_KEYS;
-    const bool active = first_key <= position && first_key + BLOCK_KEYS > lowest;
-    __nv_bfloat16* k_tile = kv_tiles + warp * 2 * BLOCK_KEYS * D;
-    __nv_bfloat16* v_tile = k_tile + BLOCK_KEYS * D;
-    if (active) load_kv_tile<D, 32>(k_tile, p.k_pages, table, first_key, BLOCK_KEYS, lowest, position, kv_head, p, lane);
+    const int first_key = chunk_start + warp * KEYS;
+    const bool active = first_key <= position && first_key + KEYS > lowest;
+    __nv_bfloat16* k_tile = kv_tiles + warp * WARP_TILE;
+    __nv_bfloat16* v_tile = k_tile + KEYS * D;
+    // Lane r resolves key row r once; the copies below fetch the offsets by shuffle.
+    const long long my_offset = active ? key_row_offset(p, table, first_key + lane, lowest, position, kv_head, D) : -1;
+    constexpr int ROWS_PER_PASS = 32 / CHUNKS;
+#pragma unroll
+    for (int pass = 0; pass < KEYS / ROWS_PER_PASS; ++pass) {
+        const int row = pass * ROWS_PER_PASS + lane / CHUNKS;
+        const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
+        if (active) cp_async_16(k_tile + swizzled<D>(row, lane % CHUNKS) * 8,
+                                p.k_pages + (offset >= 0 ? offset + (lane % CHUNKS) * 8 : 0), offset >= 0);
+    }
     cp_async_commit();
-    if (active) load_kv_tile<D, 32>(v_tile, p.v_pages, table, first_key, BLOCK_KEYS, lowest, position, kv_head, p, lane);
+#pragma unroll
+    for (int pass = 0; pass < KEYS / ROWS_PER_PASS; ++pass) {
+        const int row = pass * ROWS_PER_PASS + lane / CHUNKS;
+        const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
+        if (active) cp_async_16(v_tile + swizzled<D>(row, lane % CHUNKS) * 8,
+                                p.v_pages + (offset >= 0 ? offset + (lane % CHUNKS) * 8 : 0), offset >= 0);
+    }
     cp_async_commit();
 
     float acc[D / 8][4];
@@ -338,13 +365,13 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
             const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
             ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
         }
-        float scores[8][4];
-        scores_16x64<D>(scores, q_frag, k_tile, lane);
+        float scores[KEYS / 8][4];
+        scores_tile<D, KEYS>(scores, q_frag, k_tile, lane);
         const int row_pos[2] = {position, position};
-        softmax_step<D>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane);
+        softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane);
         cp_async_wait<0>();
         __syncwarp();
-        accumulate_pv<D>(acc, scores, v_tile, lane);
+        accumulate_pv<D, KEYS>(acc, scores, v_tile, lane);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
@@ -353,11 +380,12 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     } else {
         cp_async_wait<0>();
     }
-    __syncthreads();  // every warp is done with its key tile: reuse it for the warp's partial
+    __syncwarp();  // every lane is done reading this warp's tiles: they now hold the warp's partial
 
-    // Per-warp partial [16][D + 2] float32 in the warp's own K tile (8.3 KB of its 16 KB at D = 128).
+    // Per-warp partial [16][D + 2] float32 over the warp's own K and V tiles.
     float* mine = reinterpret_cast<float*>(k_tile);
     constexpr int STRIDE = D + 2;
+    static_assert(16 * STRIDE * 4 <= WARP_TILE * 2, "the partial must fit the warp's tiles");
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + r * 8;
@@ -380,7 +408,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
         float warp_max[4], total_max = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            warp_max[w] = reinterpret_cast<const float*>(kv_tiles + w * 2 * BLOCK_KEYS * D)[row * STRIDE + D];
+            warp_max[w] = reinterpret_cast<const float*>(kv_tiles + w * WARP_TILE)[row * STRIDE + D];
             total_max = fmaxf(total_max, warp_max[w]);
         }
         float value = 0.0f;
@@ -390,7 +418,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
                 if (warp_max[w] == -INFINITY) continue;
-                const float* part = reinterpret_cast<const float*>(kv_tiles + w * 2 * BLOCK_KEYS * D);
+                const float* part = reinterpret_cast<const float*>(kv_tiles + w * WARP_TILE);
                 value += part[row * STRIDE + col] * exp2f(warp_max[w] - total_max);
             }
         }
@@ -441,7 +469,7 @@ static int launch_portions(const AttnParams& p, int entries, int max_new_tokens,
 
 template <int D>
 static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) {
-    constexpr int SMEM = (16 * D + 8 * BLOCK_KEYS * D) * 2;
+    constexpr int SMEM = (16 * D + 8 * DECODE_WARP_KEYS * D) * 2;
     auto kernel = attention_decode_kernel<D>;
     static bool configured = false;
     if (!configured) {
@@ -455,6 +483,12 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
     if (status != 0) return status;
     attention_decode_merge_kernel<D><<<entries * p.heads, D, 0, stream>>>(p);
     return launch_status();
+}
+
+static int shift_of(int page_size) {
+    for (int shift = 0; shift < 31; ++shift)
+        if ((1 << shift) == page_size) return shift;
+    return -1;
 }
 
 static bool sizes_ok(int head_dim, int heads, int kv_heads) {
@@ -471,14 +505,14 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), nullptr, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, 0};
+                 window, 0, shift_of(page_size)};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
 
 // Every entry brings exactly one token.  `partials` is scratch of
 // entries * heads * max_splits * (head_dim + 2) floats; max_splits covers the longest context
-// that this launch may meet (ceil(max_context / 256)).
+// that this launch may meet (ceil(max_context / 128)).
 ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                        const int* cu_tokens, const int* context_lens, void* out, float* partials,
                                        float scale, int entries, int max_splits, int heads, int kv_heads, int head_dim,
@@ -488,7 +522,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, max_splits};
+                 window, max_splits, shift_of(page_size)};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 

@@ -15,7 +15,7 @@ import torch
 
 from mini_engine_b200.csrc.build import load_library
 
-DECODE_CHUNK = 256
+DECODE_CHUNK = 128
 _lib = None
 
 

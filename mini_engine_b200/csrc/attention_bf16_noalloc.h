@@ -19,8 +19,9 @@
  * Limits and rules.
  *  - entries * heads * max_splits * (head_dim + 2) must not exceed
  *    ME_NOALLOC_MAX_PARTIAL_FLOATS (2,097,152 floats = 8 MiB); otherwise the call returns
- *    ME_ERR_NOALLOC_TOO_LARGE and launches nothing.  Example: 32 requests x 32 heads x
- *    15 splits (3,840 tokens of context) x head_dim 128.
+ *    ME_ERR_NOALLOC_TOO_LARGE and launches nothing.  max_splits must cover the longest
+ *    context of the call: ceil(context / 128).  Example: 16 requests x 32 heads x 30 splits
+ *    (3,840 tokens of context) x head_dim 128 = 1,996,800 floats.
  *  - Every GPU on which the library is loaded holds the 8 MiB until the process exits.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress,
  *    with that device current) and keeps it; make that first call before any stream capture.

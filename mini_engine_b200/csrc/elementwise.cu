@@ -41,11 +41,23 @@ ME_EXPORT int me_embedding(const void* table, int table_type, const int* ids, fl
 // --------------------------------------------------------------- residual sum + RMSNorm
 
 constexpr int NORM_THREADS = 256;
+constexpr int MAX_UNROLLED_SPLITS = 8;
+
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
 
 // One block per output row.  x_row = x[src] + sum_s pending[s][src] (ascending s); when
 // `rows` is null the sum is written back to x (the residual stream advances), otherwise only
 // the listed rows are read and x is left alone.  out = weight * x_row * rsqrt(mean(x_row^2) + eps).
-template <typename OutT>
+// VEC: hidden is a multiple of 4 and every pointer is 16-byte aligned; all loads of a thread are
+// then issued before any of them is used, which is what matters when only a few rows run.
+template <typename OutT, bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
                    const float* __restrict__ weight, float eps, OutT* __restrict__ out,
@@ -55,13 +67,34 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     const int out_row = blockIdx.x;
     const int src = rows ? rows[out_row] : out_row;
     float* x_row = x + static_cast<size_t>(src) * hidden;
+    const float* pending_row = pending + static_cast<size_t>(src) * hidden;
+    const bool write_back = !rows && splits > 0;
     float sum_sq = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
-        float v = x_row[i];
-        for (int s = 0; s < splits; ++s) v += pending[s * split_stride + static_cast<size_t>(src) * hidden + i];
-        row_cache[i] = v;
-        if (!rows && splits > 0) x_row[i] = v;
-        sum_sq = fmaf(v, v, sum_sq);
+    if (VEC && splits <= MAX_UNROLLED_SPLITS) {
+        for (int i = threadIdx.x * 4; i < hidden; i += NORM_THREADS * 4) {
+            float4 v = *reinterpret_cast<const float4*>(x_row + i);
+            float4 part[MAX_UNROLLED_SPLITS];
+#pragma unroll
+            for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+                if (s < splits) part[s] = *reinterpret_cast<const float4*>(pending_row + s * split_stride + i);
+#pragma unroll
+            for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+                if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+            *reinterpret_cast<float4*>(row_cache + i) = v;
+            if (write_back) *reinterpret_cast<float4*>(x_row + i) = v;
+            sum_sq = fmaf(v.x, v.x, sum_sq);
+            sum_sq = fmaf(v.y, v.y, sum_sq);
+            sum_sq = fmaf(v.z, v.z, sum_sq);
+            sum_sq = fmaf(v.w, v.w, sum_sq);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
+            float v = x_row[i];
+            for (int s = 0; s < splits; ++s) v += pending_row[s * split_stride + i];
+            row_cache[i] = v;
+            if (write_back) x_row[i] = v;
+            sum_sq = fmaf(v, v, sum_sq);
+        }
     }
     sum_sq = warp_sum(sum_sq);
     if ((threadIdx.x & 31) == 0) warp_partial[threadIdx.x >> 5] = sum_sq;
@@ -71,28 +104,48 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     for (int w = 0; w < NORM_THREADS / 32; ++w) total += warp_partial[w];
     const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
     OutT* out_ptr = out + static_cast<size_t>(out_row) * hidden;
-    for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
-        out_ptr[i] = from_float<OutT>(weight[i] * (row_cache[i] * inv));
+    if (VEC) {
+        for (int i = threadIdx.x * 4; i < hidden; i += NORM_THREADS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
+            const float4 w = *reinterpret_cast<const float4*>(weight + i);
+            store4(out_ptr + i, make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv)));
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
+            out_ptr[i] = from_float<OutT>(weight[i] * (row_cache[i] * inv));
+    }
 }
+
+template <typename OutT, bool VEC>
+static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
+                              float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
+    auto kernel = add_rmsnorm_kernel<OutT, VEC>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, split_stride, weight, eps, out, rows, hidden);
+    return launch_status();
+}
+
+static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 ME_EXPORT int me_add_rmsnorm(float* x, const float* pending, int splits, long long split_stride,
                              const float* weight, float eps, void* out, int out_type, const int* rows,
                              int count, int hidden, cudaStream_t stream) {
     if (count <= 0) return 0;
-    const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
-    if (smem > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    if (static_cast<size_t>(hidden) * sizeof(float) > 200 * 1024) return ME_ERR_UNSUPPORTED;
+    // Which path runs depends on the width and on the alignment of the engine's persistent
+    // buffers only, never on the batch, so a row's statistics are the same bits in every step.
+    const bool vec = hidden % 4 == 0 && aligned16(x) && aligned16(weight) && aligned16(out) &&
+                     (pending == nullptr || (aligned16(pending) && split_stride % 4 == 0));
+    const size_t stride = static_cast<size_t>(split_stride);
     if (out_type == ME_BF16) {
-        auto kernel = add_rmsnorm_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, (size_t)split_stride, weight, eps,
-                                                      static_cast<__nv_bfloat16*>(out), rows, hidden);
-    } else {
-        auto kernel = add_rmsnorm_kernel<float>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, (size_t)split_stride, weight, eps,
-                                                      static_cast<float*>(out), rows, hidden);
+        auto* o = static_cast<__nv_bfloat16*>(out);
+        return vec ? launch_add_rmsnorm<__nv_bfloat16, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream)
+                   : launch_add_rmsnorm<__nv_bfloat16, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream);
     }
-    return launch_status();
+    auto* o = static_cast<float*>(out);
+    return vec ? launch_add_rmsnorm<float, true>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream)
+               : launch_add_rmsnorm<float, false>(x, pending, splits, stride, weight, eps, o, rows, count, hidden, stream);
 }
 
 // --------------------------------------------------------------------------------- SwiGLU
@@ -225,6 +278,71 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     }
 }
 
+// The same for head_dim == 128: each lane owns four consecutive elements, all partial sums are
+// loaded before they are added, and the rotation partner (64 elements away) is 16 lanes away.
+template <typename OutT>
+__global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(QkvArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = a.heads + 2 * a.kv_heads;
+    const long long item = static_cast<long long>(blockIdx.x) * QKV_WARPS + warp;
+    if (item >= static_cast<long long>(a.tokens) * heads_total) return;
+    const int token = static_cast<int>(item / heads_total);
+    const int column_head = static_cast<int>(item % heads_total);
+    constexpr int D = 128;
+    const float* src = a.qkv + static_cast<size_t>(token) * heads_total * D + static_cast<size_t>(column_head) * D + lane * 4;
+    float4 part[MAX_UNROLLED_SPLITS];
+#pragma unroll
+    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+        if (s < a.splits) part[s] = *reinterpret_cast<const float4*>(src + s * a.split_stride);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+        if (s < a.splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+    const bool is_q = column_head < a.heads;
+    const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
+    const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+    if (weight) {
+        float sum_sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        sum_sq = warp_sum(sum_sq);
+        const float inv = rsqrtf(sum_sq / static_cast<float>(D) + a.eps);
+        const float4 w = *reinterpret_cast<const float4*>(weight + lane * 4);
+        v = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
+    }
+    if ((is_q || is_k) && a.inv_freq != nullptr) {
+        const float position = static_cast<float>(a.positions[token]);
+        const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
+                                         __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
+        const float4 freq = *reinterpret_cast<const float4*>(a.inv_freq + (lane & 15) * 4);
+        const float sign = lane < 16 ? -1.0f : 1.0f;  // first half: x cos - partner sin; second: x cos + partner sin
+        float sine, cosine;
+        sincosf(position * freq.x, &sine, &cosine);
+        v.x = v.x * cosine + sign * other.x * sine;
+        sincosf(position * freq.y, &sine, &cosine);
+        v.y = v.y * cosine + sign * other.y * sine;
+        sincosf(position * freq.z, &sine, &cosine);
+        v.z = v.z * cosine + sign * other.z * sine;
+        sincosf(position * freq.w, &sine, &cosine);
+        v.w = v.w * cosine + sign * other.w * sine;
+    }
+    OutT* dst;
+    if (is_q) {
+        dst = static_cast<OutT*>(a.q_out) + (static_cast<size_t>(token) * a.heads + column_head) * D;
+    } else {
+        const int kv_head = is_k ? column_head - a.heads : column_head - a.heads - a.kv_heads;
+        if (a.slot_mapping) {
+            const int slot = a.slot_mapping[token];
+            if (slot < 0) return;
+            const size_t page = slot / a.page_size, offset = slot % a.page_size;
+            OutT* pages = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages);
+            dst = pages + ((page * a.kv_heads + kv_head) * a.page_size + offset) * D;
+        } else {
+            OutT* dense = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense);
+            dst = dense + (static_cast<size_t>(token) * a.kv_heads + kv_head) * D;
+        }
+    }
+    store4(dst + lane * 4, v);
+}
+
 ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long split_stride, const float* q_weight,
                                     const float* k_weight, float eps, const float* inv_freq,
                                     const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
@@ -237,10 +355,17 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
     const size_t smem = static_cast<size_t>(QKV_WARPS) * head_dim * sizeof(float);
-    if (out_type == ME_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
-    else
-        qk_norm_rope_store_kernel<float><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+    // The choice depends on the model's sizes and the engine's buffers only, never on the batch.
+    const bool vec = head_dim == 128 && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
+                     aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
+                     aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(inv_freq);
+    if (out_type == ME_BF16) {
+        if (vec) qk_norm_rope_store_128_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, 0, stream>>>(a);
+        else qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+    } else {
+        if (vec) qk_norm_rope_store_128_kernel<float><<<blocks, QKV_WARPS * 32, 0, stream>>>(a);
+        else qk_norm_rope_store_kernel<float><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+    }
     return launch_status();
 }
 

@@ -352,14 +352,16 @@ ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, 
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.
 ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,
-                                     int dual_row_offset, cudaStream_t stream) {
+                                     int dual_row_offset, int block_t, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset};
     p.k_blocks_per_split = p.k_blocks;
-    return launch<128, true>(w, x, p, 1, stream);
+    if (block_t == 256) return launch<256, true>(w, x, p, 1, stream);  // both accumulators fill all 512 TMEM columns
+    if (block_t == 128) return launch<128, true>(w, x, p, 1, stream);
+    return ME_ERR_ARGUMENT;
 }
 
 // The first failure a kernel of this library recorded since the last call (0: none); clears it.

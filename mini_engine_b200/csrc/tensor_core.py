@@ -32,7 +32,7 @@ def _library():
         lib.me_make_tensor_map.restype = c_int
         lib.me_gemm_tcgen05.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05.restype = c_int
-        lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_swiglu.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_gemm_take_error.restype = c_int
@@ -131,8 +131,10 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    tile = 256 if tokens > 128 else 128
     code = _library().me_gemm_tcgen05_swiglu(
-        plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
+        plan.map, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, tile,
+        stream,
     )
     _count_launch()
     if code != 0:

@@ -70,16 +70,16 @@ def call_both(lib, case, heads, kv_heads, head_dim, page, splits):
 def test_no_alloc_entry_matches_the_ordinary_one_twice_in_a_row():
     lib = library()
     first = make_case(1, [600, 33, 256, 1], heads=8, kv_heads=2, head_dim=128, page=16)
-    ours, theirs = call_both(lib, first, 8, 2, 128, 16, splits=3)
+    ours, theirs = call_both(lib, first, 8, 2, 128, 16, splits=5)  # ceil(600 / 128)
     assert torch.isfinite(ours.float()).all()
     assert float((ours.float() - theirs.float()).abs().max()) <= 1e-2 * float(theirs.float().abs().max())
     # a second call of another shape, right behind the first, on the same scratch
     second = make_case(2, [90, 300], heads=4, kv_heads=4, head_dim=64, page=8)
-    ours2, theirs2 = call_both(lib, second, 4, 4, 64, 8, splits=2)
+    ours2, theirs2 = call_both(lib, second, 4, 4, 64, 8, splits=3)
     assert torch.isfinite(ours2.float()).all()
     assert float((ours2.float() - theirs2.float()).abs().max()) <= 1e-2 * float(theirs2.float().abs().max())
     # and the first again: the same bits as before (the kernels are deterministic)
-    ours3, _ = call_both(lib, first, 8, 2, 128, 16, splits=3)
+    ours3, _ = call_both(lib, first, 8, 2, 128, 16, splits=5)
     assert torch.equal(ours3, ours)
 
 
