@@ -202,6 +202,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
 
     // Later blocks of a request see more keys: start them first so that the grid's tail is short.
     const int entry = blockIdx.z, head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int token0 = p.cu_tokens[entry];
     const int new_tokens = p.cu_tokens[entry + 1] - token0;
     if (q_block * BLOCK_M >= new_tokens) return;
@@ -310,6 +312,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][KEYS][D]
 
     const int entry = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int chunk_start = split * DECODE_CHUNK;
@@ -431,6 +435,8 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
 template <int D>
 __global__ void __launch_bounds__(D) attention_decode_merge_kernel(AttnParams p) {
     const int entry = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+    pdl_trigger();
+    pdl_wait();
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int first = lowest / DECODE_CHUNK, last = position / DECODE_CHUNK;
@@ -463,8 +469,7 @@ static int launch_portions(const AttnParams& p, int entries, int max_new_tokens,
         configured = true;
     }
     dim3 grid((max_new_tokens + BLOCK_M - 1) / BLOCK_M, p.heads, entries);
-    kernel<<<grid, ATTN_THREADS, SMEM, stream>>>(p);
-    return launch_status();
+    return launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
 }
 
 template <int D>
@@ -478,11 +483,9 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
         configured = true;
     }
     dim3 grid(p.max_splits, p.kv_heads, entries);
-    kernel<<<grid, ATTN_THREADS, SMEM, stream>>>(p);
-    int status = launch_status();
+    const int status = launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
     if (status != 0) return status;
-    attention_decode_merge_kernel<D><<<entries * p.heads, D, 0, stream>>>(p);
-    return launch_status();
+    return launch_kernel(attention_decode_merge_kernel<D>, entries * p.heads, D, 0, stream, p);
 }
 
 static int shift_of(int page_size) {

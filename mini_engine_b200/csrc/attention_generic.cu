@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) paged_attention_generic_kerne
     if (item >= static_cast<long long>(a.tokens) * a.heads) return;
     const int token = static_cast<int>(item / a.heads), head = static_cast<int>(item % a.heads);
     const int d = a.head_dim;
+    pdl_trigger();
+    pdl_wait();
     const int kv_head = head / (a.heads / a.kv_heads);
     const int position = a.positions[token];
     const int* table = a.block_table + static_cast<size_t>(a.entry_of_token[token]) * a.table_width;
@@ -111,8 +113,6 @@ ME_EXPORT int me_paged_attention_generic(const void* q, const void* k_pages, con
     const int blocks = static_cast<int>((items + ATTN_WARPS - 1) / ATTN_WARPS);
     const size_t smem = static_cast<size_t>(ATTN_WARPS) * head_dim * sizeof(float);
     if (type == ME_BF16)
-        paged_attention_generic_kernel<__nv_bfloat16><<<blocks, ATTN_WARPS * 32, smem, stream>>>(a);
-    else
-        paged_attention_generic_kernel<float><<<blocks, ATTN_WARPS * 32, smem, stream>>>(a);
-    return launch_status();
+        return launch_kernel(paged_attention_generic_kernel<__nv_bfloat16>, blocks, ATTN_WARPS * 32, smem, stream, a);
+    return launch_kernel(paged_attention_generic_kernel<float>, blocks, ATTN_WARPS * 32, smem, stream, a);
 }

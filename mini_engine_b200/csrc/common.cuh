@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define ME_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -37,3 +38,38 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 static inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+// Programmatic dependent launch.  Every kernel of this package is launched with the attribute
+// that lets its CTAs become resident while the kernel before it in the stream is still running.
+// Such a CTA may only set itself up and read weights (which no kernel writes); before it reads
+// or writes anything that another kernel writes or reads it calls pdl_wait(), which returns once
+// the preceding kernel has completed and its memory is visible.  pdl_trigger() tells the
+// scheduler that the next kernel's CTAs may be made resident as far as this CTA is concerned.
+// Without the attribute (MINI_ENGINE_B200_PDL=0) both are no-ops and kernels run back to back.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* value = getenv("MINI_ENGINE_B200_PDL");
+        enabled = (value && value[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+template <typename... KernelArgs, typename... Args>
+static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
+}

@@ -15,6 +15,8 @@ template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
     const int token = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int id = ids[token];
     float* row_out = out + static_cast<size_t>(token) * hidden;
     if (id < 0 || id >= vocab) {  // the host validates ids; never read outside the table
@@ -30,12 +32,10 @@ ME_EXPORT int me_embedding(const void* table, int table_type, const int* ids, fl
     if (tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_type == ME_BF16)
-        embedding_kernel<<<tokens, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(table), ids, out,
-                                                         hidden, vocab);
-    else
-        embedding_kernel<<<tokens, threads, 0, stream>>>(static_cast<const float*>(table), ids, out, hidden,
-                                                         vocab);
-    return launch_status();
+        return launch_kernel(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
+                             static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab);
+    return launch_kernel(embedding_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out,
+                         hidden, vocab);
 }
 
 // --------------------------------------------------------------- residual sum + RMSNorm
@@ -65,6 +65,8 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     extern __shared__ float row_cache[];  // [hidden]
     __shared__ float warp_partial[NORM_THREADS / 32];
     const int out_row = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int src = rows ? rows[out_row] : out_row;
     float* x_row = x + static_cast<size_t>(src) * hidden;
     const float* pending_row = pending + static_cast<size_t>(src) * hidden;
@@ -122,8 +124,8 @@ static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
     auto kernel = add_rmsnorm_kernel<OutT, VEC>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kernel<<<count, NORM_THREADS, smem, stream>>>(x, pending, splits, split_stride, weight, eps, out, rows, hidden);
-    return launch_status();
+    return launch_kernel(kernel, count, NORM_THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
+                         rows, hidden);
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
@@ -155,6 +157,8 @@ template <typename OutT>
 __global__ void swiglu_kernel(const float* __restrict__ partial, int splits, size_t split_stride,
                               OutT* __restrict__ out, int tokens, int inter) {
     const size_t total = static_cast<size_t>(tokens) * inter;
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total;
          idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t t = idx / inter;
@@ -177,12 +181,10 @@ ME_EXPORT int me_swiglu(const float* partial, int splits, long long split_stride
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
     if (out_type == ME_BF16)
-        swiglu_kernel<<<blocks, threads, 0, stream>>>(partial, splits, (size_t)split_stride,
-                                                      static_cast<__nv_bfloat16*>(out), tokens, inter);
-    else
-        swiglu_kernel<<<blocks, threads, 0, stream>>>(partial, splits, (size_t)split_stride,
-                                                      static_cast<float*>(out), tokens, inter);
-    return launch_status();
+        return launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, partial, splits,
+                             (size_t)split_stride, static_cast<__nv_bfloat16*>(out), tokens, inter);
+    return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, stream, partial, splits, (size_t)split_stride,
+                         static_cast<float*>(out), tokens, inter);
 }
 
 // ------------------------------------------------- per-head norm + rotary + cache write
@@ -225,6 +227,8 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     const int column_head = static_cast<int>(item % heads_total);
     const int d = a.head_dim, half = d / 2;
     float* vec = staged + warp * d;
+    pdl_trigger();
+    pdl_wait();
 
     const size_t row_width = static_cast<size_t>(heads_total) * d;
     const float* src = a.qkv + static_cast<size_t>(token) * row_width + static_cast<size_t>(column_head) * d;
@@ -289,6 +293,8 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
     const int token = static_cast<int>(item / heads_total);
     const int column_head = static_cast<int>(item % heads_total);
     constexpr int D = 128;
+    pdl_trigger();
+    pdl_wait();
     const float* src = a.qkv + static_cast<size_t>(token) * heads_total * D + static_cast<size_t>(column_head) * D + lane * 4;
     float4 part[MAX_UNROLLED_SPLITS];
 #pragma unroll
@@ -360,13 +366,11 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
                      aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(inv_freq);
     if (out_type == ME_BF16) {
-        if (vec) qk_norm_rope_store_128_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, 0, stream>>>(a);
-        else qk_norm_rope_store_kernel<__nv_bfloat16><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
-    } else {
-        if (vec) qk_norm_rope_store_128_kernel<float><<<blocks, QKV_WARPS * 32, 0, stream>>>(a);
-        else qk_norm_rope_store_kernel<float><<<blocks, QKV_WARPS * 32, smem, stream>>>(a);
+        if (vec) return launch_kernel(qk_norm_rope_store_128_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, 0, stream, a);
+        return launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, smem, stream, a);
     }
-    return launch_status();
+    if (vec) return launch_kernel(qk_norm_rope_store_128_kernel<float>, blocks, QKV_WARPS * 32, 0, stream, a);
+    return launch_kernel(qk_norm_rope_store_kernel<float>, blocks, QKV_WARPS * 32, smem, stream, a);
 }
 
 // Dense [tokens][kv_heads][head_dim] keys and values into their slots of the pages.
@@ -375,6 +379,8 @@ __global__ void kv_store_kernel(const T* __restrict__ k_dense, const T* __restri
                                 const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
                                 T* __restrict__ v_pages, int kv_heads, int head_dim, int page_size) {
     const int token = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int slot = slot_mapping[token];
     if (slot < 0) return;
     const size_t page = slot / page_size, offset = slot % page_size;
@@ -392,14 +398,11 @@ ME_EXPORT int me_kv_store(const void* k_dense, const void* v_dense, const int* s
                           cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (type == ME_BF16)
-        kv_store_kernel<<<tokens, 128, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(k_dense), static_cast<const __nv_bfloat16*>(v_dense), slot_mapping,
-            static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), kv_heads, head_dim,
-            page_size);
-    else
-        kv_store_kernel<<<tokens, 128, 0, stream>>>(static_cast<const float*>(k_dense),
-                                                    static_cast<const float*>(v_dense), slot_mapping,
-                                                    static_cast<float*>(k_pages), static_cast<float*>(v_pages),
-                                                    kv_heads, head_dim, page_size);
-    return launch_status();
+        return launch_kernel(kv_store_kernel<__nv_bfloat16>, tokens, 128, 0, stream,
+                             static_cast<const __nv_bfloat16*>(k_dense), static_cast<const __nv_bfloat16*>(v_dense),
+                             slot_mapping, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages),
+                             kv_heads, head_dim, page_size);
+    return launch_kernel(kv_store_kernel<float>, tokens, 128, 0, stream, static_cast<const float*>(k_dense),
+                         static_cast<const float*>(v_dense), slot_mapping, static_cast<float*>(k_pages),
+                         static_cast<float*>(v_pages), kv_heads, head_dim, page_size);
 }

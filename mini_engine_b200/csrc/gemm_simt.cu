@@ -23,6 +23,8 @@ gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __rest
     __shared__ float ws[TILE_K][TILE_N + 4];
     const int t0 = blockIdx.y * TILE_T, n0 = blockIdx.x * TILE_N;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    pdl_trigger();
+    pdl_wait();
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -71,11 +73,9 @@ ME_EXPORT int me_gemm_simt(const void* x, const void* w, float* y, int type, int
     dim3 grid((outs + TILE_N - 1) / TILE_N, (tokens + TILE_T - 1) / TILE_T);
     if (grid.y > 65535) return ME_ERR_UNSUPPORTED;
     if (type == ME_BF16)
-        gemm_simt_kernel<<<grid, SIMT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
-                                                            static_cast<const __nv_bfloat16*>(w), y, tokens, outs,
-                                                            inner);
-    else
-        gemm_simt_kernel<<<grid, SIMT_THREADS, 0, stream>>>(static_cast<const float*>(x),
-                                                            static_cast<const float*>(w), y, tokens, outs, inner);
-    return launch_status();
+        return launch_kernel(gemm_simt_kernel<__nv_bfloat16>, grid, SIMT_THREADS, 0, stream,
+                             static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), y, tokens, outs,
+                             inner);
+    return launch_kernel(gemm_simt_kernel<float>, grid, SIMT_THREADS, 0, stream, static_cast<const float*>(x),
+                         static_cast<const float*>(w), y, tokens, outs, inner);
 }

@@ -24,6 +24,12 @@
 // of tensor memory, and the epilogue applies the gate lane by lane, so the [T, 2 * inter]
 // intermediate never exists.
 //
+// Launch overlap: the kernel is launched as a programmatic dependent of the kernel before it.
+// Its CTAs become resident while that kernel still runs, set up their barriers and tensor memory
+// and already request their first weight tiles (up to 128 KB per CTA); only the activation tiles
+// and the stores wait for the predecessor (griddepcontrol.wait).  In a decode step this keeps
+// the weight stream from HBM going across kernel boundaries.
+//
 // Every wait is bounded: after a limit of polls and of time a role records an error code in a device
 // flag that the host reads, stops, and the CTA still frees its tensor memory and exits.
 #include <cuda.h>
@@ -133,7 +139,10 @@ struct Config {
     static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2 * (DUAL ? 2 : 1);
     static constexpr int B_BYTES = BLOCK_T * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8;
+    // Few tokens: the kernel only streams weights.  Four stages keep a CTA at 72-96 KB of shared
+    // memory, so two or three CTAs share an SM and one's start-up and epilogue hide behind the
+    // others' loads.  Many tokens: as many stages as fit, one CTA per SM.
+    static constexpr int STAGES = BLOCK_T <= 64 ? 4 : ((SMEM_BUDGET / STAGE_BYTES) < 8 ? (SMEM_BUDGET / STAGE_BYTES) : 8);
     static constexpr int ACC_COLUMNS = BLOCK_T * (DUAL ? 2 : 1);
     static constexpr int TMEM_COLUMNS = ACC_COLUMNS < 32 ? 32 : ACC_COLUMNS;  // powers of two here
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -176,8 +185,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < iterations; ++i, ++issued) {
+            pdl_trigger();
+            // Weights are written by no kernel, so the first stages' weight tiles are requested
+            // before the preceding kernel has finished; the activations wait for it.
+            const int early = min(iterations, C::STAGES);
+            for (int i = 0; i < early; ++i) {
+                uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
+                mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(a_tile, &map_w, k, n0, &full[i]);
+                if (DUAL) tma_load_2d(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, k, p.dual_row_offset + n0, &full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb_begin + i) * BLOCK_K, t0, &full[i]);
+            int issued = early;
+            for (int i = early; i < iterations; ++i, ++issued) {
                 const int stage = i % C::STAGES;
                 const uint32_t parity = (i / C::STAGES) & 1;
                 if (!mbar_wait(&empty[stage], parity ^ 1)) { atomicCAS(&g_gemm_error, 0, (1 << 8) | stage); break; }
@@ -228,6 +251,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // a warp may read TMEM lanes [32 * (warp % 4), +32)
         const int n = n0 + quarter * 32 + lane;
+        pdl_wait();  // the output buffer may still be read by the kernel before this one
         bool ok = mbar_wait(accum, 0);
         if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (3 << 8));
         ok = __all_sync(0xffffffffu, ok) && g_gemm_error == 0;
@@ -325,8 +349,7 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Gemm
         configured = true;
     }
     dim3 grid((p.outs + BLOCK_N - 1) / BLOCK_N, (p.tokens + BLOCK_T - 1) / BLOCK_T, splits);
-    kernel<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(map_w, map_x, p);
-    return launch_status();
+    return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
 }
 
 // out[s][t][n] (float32) = sum over the k blocks of split s of x[t][k] * w[n][k].

@@ -22,6 +22,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     __shared__ float row_max_shared;
     __shared__ int best_shared;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_trigger();
+    pdl_wait();
     const float* x = logits + static_cast<size_t>(row) * vocab;
     const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
     const int begin = min(tid * chunk, vocab), end = min(begin + chunk, vocab);
@@ -90,6 +92,5 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
 ME_EXPORT int me_sample(const float* logits, const float* temperatures, const float* uniforms, int* out,
                         int rows, int vocab, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, temperatures, uniforms, out, vocab);
-    return launch_status();
+    return launch_kernel(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, temperatures, uniforms, out, vocab);
 }

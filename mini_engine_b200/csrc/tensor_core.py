@@ -57,9 +57,11 @@ def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> in
     given number of tokens the same split is always chosen), and no split is empty."""
     if tokens > SPLIT_MAX_TOKENS:
         return 1
-    tiles = -(-outs // BLOCK_N) * -(-tokens // token_tile(tokens))
+    tile = token_tile(tokens)
+    tiles = -(-outs // BLOCK_N) * -(-tokens // tile)
     k_blocks = -(-inner // BLOCK_K)
-    wanted = min(max_splits, max(1, (2 * NUM_SMS) // tiles), max(1, k_blocks // MIN_K_BLOCKS_PER_SPLIT))
+    slots = NUM_SMS * (3 if tile <= 32 else 2)  # CTAs of this tile size that are resident at once
+    wanted = min(max_splits, max(1, slots // tiles), max(1, k_blocks // MIN_K_BLOCKS_PER_SPLIT))
     per_split = -(-k_blocks // wanted)
     return -(-k_blocks // per_split)
 
