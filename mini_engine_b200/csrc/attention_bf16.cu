@@ -42,6 +42,7 @@ struct AttnParams {
     float scale_log2;         // scale * log2(e)
     int heads, kv_heads, page_size, table_width, window, max_splits;
     int page_shift;  // log2(page_size) when it is a power of two, else -1
+    int tiles_per_cta;  // decode: consecutive 128-key tiles that one CTA walks
 };
 
 // ------------------------------------------------------------------------ small helpers
@@ -300,13 +301,17 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
 // ----------------------------------------------------------------------- decode kernels
 
 // grid (splits, kv_heads, entries).  Rows of the score tile are the query heads of the group
-// (at most 16; the rest of the 16 rows are zero).  Three CTAs fit an SM, so one CTA's loads
-// overlap another's arithmetic.
+// (at most 16; the rest of the 16 rows are zero).  A CTA takes `tiles_per_cta` consecutive tiles of
+// 128 keys (32 per warp); while a warp multiplies one tile's keys, its values and the next tile's
+// keys are on their way, so loads never stop.  Three CTAs fit an SM.
+constexpr int MAX_DECODE_TILES = 8;
+
 template <int D>
-__global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnParams p) {
+__global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int KEYS = DECODE_WARP_KEYS;
     constexpr int CHUNKS = D / 8;
+    constexpr int ROWS_PER_PASS = 32 / CHUNKS;
     constexpr int WARP_TILE = 2 * KEYS * D;  // elements of one warp's K and V tiles
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
     __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][KEYS][D]
@@ -316,8 +321,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     pdl_wait();
     const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
-    const int chunk_start = split * DECODE_CHUNK;
-    if (chunk_start > position || chunk_start + DECODE_CHUNK <= lowest) return;
+    const int span = p.tiles_per_cta * DECODE_CHUNK;
+    const int cta_start = split * span;
+    if (cta_start > position || cta_start + span <= lowest) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = p.heads / p.kv_heads;
     const int token = p.cu_tokens[entry];
@@ -329,29 +335,29 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
         const __nv_bfloat16* src = p.q + (static_cast<size_t>(token) * p.heads + kv_head * group + row) * D + chunk * 8;
         cp_async_16(q_tile + swizzled<D>(row, chunk) * 8, valid ? src : p.q, valid);
     }
-    const int first_key = chunk_start + warp * KEYS;
-    const bool active = first_key <= position && first_key + KEYS > lowest;
     __nv_bfloat16* k_tile = kv_tiles + warp * WARP_TILE;
     __nv_bfloat16* v_tile = k_tile + KEYS * D;
-    // Lane r resolves key row r once; the copies below fetch the offsets by shuffle.
-    const long long my_offset = active ? key_row_offset(p, table, first_key + lane, lowest, position, kv_head, D) : -1;
-    constexpr int ROWS_PER_PASS = 32 / CHUNKS;
+    // Lane r resolves key row r of a tile; the copies fetch the offsets by shuffle.  The offsets of
+    // the next tile are resolved while the current tile is multiplied.
+    auto resolve = [&](int t) {
+        return key_row_offset(p, table, cta_start + t * DECODE_CHUNK + warp * KEYS + lane, lowest, position, kv_head, D);
+    };
+    auto issue = [&](__nv_bfloat16* tile, const __nv_bfloat16* pages, long long mine) {
 #pragma unroll
-    for (int pass = 0; pass < KEYS / ROWS_PER_PASS; ++pass) {
-        const int row = pass * ROWS_PER_PASS + lane / CHUNKS;
-        const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
-        if (active) cp_async_16(k_tile + swizzled<D>(row, lane % CHUNKS) * 8,
-                                p.k_pages + (offset >= 0 ? offset + (lane % CHUNKS) * 8 : 0), offset >= 0);
-    }
-    cp_async_commit();
-#pragma unroll
-    for (int pass = 0; pass < KEYS / ROWS_PER_PASS; ++pass) {
-        const int row = pass * ROWS_PER_PASS + lane / CHUNKS;
-        const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
-        if (active) cp_async_16(v_tile + swizzled<D>(row, lane % CHUNKS) * 8,
-                                p.v_pages + (offset >= 0 ? offset + (lane % CHUNKS) * 8 : 0), offset >= 0);
-    }
-    cp_async_commit();
+        for (int pass = 0; pass < KEYS / ROWS_PER_PASS; ++pass) {
+            const int row = pass * ROWS_PER_PASS + lane / CHUNKS;
+            const long long offset = __shfl_sync(0xffffffffu, mine, row);
+            cp_async_16(tile + swizzled<D>(row, lane % CHUNKS) * 8, pages + (offset >= 0 ? offset + (lane % CHUNKS) * 8 : 0),
+                        offset >= 0);
+        }
+    };
+    // Tiles of this CTA that hold visible keys.
+    const int tiles = min(p.tiles_per_cta, (position - cta_start) / DECODE_CHUNK + 1);
+    long long offset_now = resolve(0);
+    issue(k_tile, p.k_pages, offset_now);
+    cp_async_commit();  // group: queries + keys of tile 0
+    issue(v_tile, p.v_pages, offset_now);
+    cp_async_commit();  // group: values of tile 0
 
     float acc[D / 8][4];
 #pragma unroll
@@ -359,30 +365,43 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    uint32_t q_frag[D / 16][4];
+    const int row_pos[2] = {position, position};
 
-    cp_async_wait<1>();
-    __syncthreads();  // the queries (loaded by all threads) and this warp's keys have landed
-    if (active) {
-        uint32_t q_frag[D / 16][4];
+#pragma unroll 1
+    for (int t = 0; t < tiles; ++t) {
+        const bool more = t + 1 < tiles;
+        const long long offset_next = more ? resolve(t + 1) : -1;
+        cp_async_wait<1>();  // everything but the newest group (this tile's values) has landed
+        if (t == 0) {
+            __syncthreads();  // the queries were loaded by all threads
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-            const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-            ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(q_frag[kk], q_tile + swizzled<D>(row, kk * 2 + (lane >> 4)) * 8);
+            }
+        } else {
+            __syncwarp();
         }
+        const int first_key = cta_start + t * DECODE_CHUNK + warp * KEYS;
         float scores[KEYS / 8][4];
         scores_tile<D, KEYS>(scores, q_frag, k_tile, lane);
-        const int row_pos[2] = {position, position};
         softmax_step<D, KEYS>(scores, acc, row_max, row_sum, row_pos, first_key, p.window, p.scale_log2, lane);
-        cp_async_wait<0>();
+        __syncwarp();  // every lane has read the keys: the next tile's keys may overwrite them
+        if (more) issue(k_tile, p.k_pages, offset_next);
+        cp_async_commit();
+        cp_async_wait<1>();  // this tile's values have landed (the next keys may still be in flight)
         __syncwarp();
         accumulate_pv<D, KEYS>(acc, scores, v_tile, lane);
+        __syncwarp();
+        if (more) issue(v_tile, p.v_pages, offset_next);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
-            row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
-        }
-    } else {
-        cp_async_wait<0>();
+    for (int r = 0; r < 2; ++r) {
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
     }
     __syncwarp();  // every lane is done reading this warp's tiles: they now hold the warp's partial
 
@@ -406,7 +425,7 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     }
     __syncthreads();
 
-    // Merge the four warps in ascending key order and write the CTA's partial.
+    // Merge the four warps and write the CTA's partial.
     for (int idx = threadIdx.x; idx < group * STRIDE; idx += ATTN_THREADS) {
         const int row = idx / STRIDE, col = idx % STRIDE;
         float warp_max[4], total_max = -INFINITY;
@@ -431,29 +450,43 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_decode_kernel(AttnPara
     }
 }
 
-// One block per (entry, head): merges the splits that the decode kernel wrote, in ascending order.
+// One warp per (entry, head): merges the partials that the decode kernel wrote, in ascending
+// order of their keys.  Each lane owns D / 32 output elements.
 template <int D>
-__global__ void __launch_bounds__(D) attention_decode_merge_kernel(AttnParams p) {
-    const int entry = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+__global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams p, int items) {
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_trigger();
     pdl_wait();
+    if (item >= items) return;
+    const int entry = item / p.heads, head = item % p.heads;
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
-    const int first = lowest / DECODE_CHUNK, last = position / DECODE_CHUNK;
+    const int span = p.tiles_per_cta * DECODE_CHUNK;
+    const int first = lowest / span, last = position / span;
     constexpr int STRIDE = D + 2;
+    constexpr int PER_LANE = D / 32;
     const float* base = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
     float total_max = -INFINITY;
-    for (int s = first; s <= last; ++s) total_max = fmaxf(total_max, base[s * STRIDE + D]);
-    float value = 0.0f, denom = 0.0f;
+    for (int s = first + lane; s <= last; s += 32) total_max = fmaxf(total_max, base[s * STRIDE + D]);
+    total_max = warp_max(total_max);
+    float value[PER_LANE], denom = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) value[i] = 0.0f;
+#pragma unroll 4
     for (int s = first; s <= last; ++s) {
         const float m = base[s * STRIDE + D];
         if (m == -INFINITY) continue;
         const float weight = exp2f(m - total_max);
-        value += base[s * STRIDE + threadIdx.x] * weight;
         denom += base[s * STRIDE + D + 1] * weight;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) value[i] += base[s * STRIDE + lane * PER_LANE + i] * weight;
     }
     const int token = p.cu_tokens[entry];
-    p.out[(static_cast<size_t>(token) * p.heads + head) * D + threadIdx.x] = __float2bfloat16_rn(value / denom);
+    __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
+    const float inv = 1.0f / denom;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; i += 2)
+        *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(value[i] * inv, value[i + 1] * inv);
 }
 
 // -------------------------------------------------------------------------------- host
@@ -485,7 +518,8 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
     dim3 grid(p.max_splits, p.kv_heads, entries);
     const int status = launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
     if (status != 0) return status;
-    return launch_kernel(attention_decode_merge_kernel<D>, entries * p.heads, D, 0, stream, p);
+    const int items = entries * p.heads;
+    return launch_kernel(attention_decode_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
 }
 
 static int shift_of(int page_size) {
@@ -508,25 +542,38 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), nullptr, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, 0, shift_of(page_size)};
+                 window, 0, shift_of(page_size), 1};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
 
 // Every entry brings exactly one token.  `partials` is scratch of
-// entries * heads * max_splits * (head_dim + 2) floats; max_splits covers the longest context
-// that this launch may meet (ceil(max_context / 128)).
+// entries * heads * max_splits * (head_dim + 2) floats; a CTA walks `tiles_per_cta` (1..8) tiles
+// of 128 keys, and max_splits covers the longest context that this launch may meet:
+// ceil(max_context / (128 * tiles_per_cta)).
+ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages, const void* v_pages,
+                                             const int* block_table, const int* cu_tokens, const int* context_lens,
+                                             void* out, float* partials, float scale, int entries, int max_splits,
+                                             int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
+                                             int table_width, int window, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
+    if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
+    AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
+                 static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
+                 static_cast<__nv_bfloat16*>(out), partials, scale * LOG2E, heads, kv_heads, page_size, table_width,
+                 window, max_splits, shift_of(page_size), tiles_per_cta};
+    return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
+}
+
+// The same with one tile of 128 keys per CTA: max_splits = ceil(max_context / 128).
 ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                        const int* cu_tokens, const int* context_lens, void* out, float* partials,
                                        float scale, int entries, int max_splits, int heads, int kv_heads, int head_dim,
                                        int page_size, int table_width, int window, cudaStream_t stream) {
-    if (entries <= 0) return 0;
-    if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
-    AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
-                 static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
-                 static_cast<__nv_bfloat16*>(out), partials, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, max_splits, shift_of(page_size)};
-    return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
+    return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
+                                          scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
+                                          table_width, window, stream);
 }
 
 // ------------------------------------------------- decode attention without allocation

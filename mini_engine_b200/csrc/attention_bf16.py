@@ -25,8 +25,8 @@ def _library():
         lib = load_library("attention_bf16")
         lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
-        lib.me_attention_decode_bf16.argtypes = [c_void_p] * 8 + [c_float] + [c_int] * 8 + [c_void_p]
-        lib.me_attention_decode_bf16.restype = c_int
+        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 8 + [c_float] + [c_int] * 9 + [c_void_p]
+        lib.me_attention_decode_bf16_tiled.restype = c_int
         _lib = lib
     return _lib
 
@@ -35,8 +35,21 @@ def supports(head_dim: int, heads: int, kv_heads: int) -> bool:
     return head_dim in (64, 128) and kv_heads > 0 and heads % kv_heads == 0
 
 
-def decode_splits(max_context_len: int) -> int:
-    return max(1, -(-max_context_len // DECODE_CHUNK))
+def decode_tiles_per_cta(entries: int, kv_heads: int) -> int:
+    """Consecutive 128-key tiles that one CTA walks.  With few (request, KV head) pairs every
+    tile is a CTA of its own, so that all SMs have work; with many, a CTA walks several tiles
+    and pays its start-up once.  The choice changes how partial results are grouped, hence the
+    result in its last bits, never which keys are read."""
+    pairs = entries * kv_heads
+    if pairs <= 128:
+        return 1
+    if pairs <= 256:
+        return 2
+    return 4
+
+
+def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
+    return max(1, -(-max_context_len // (DECODE_CHUNK * tiles_per_cta)))
 
 
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window) -> None:
@@ -51,11 +64,12 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     page_size, width = k_pages.shape[2], block_table.shape[1]
     entries = ctx.num_entries
     if ctx.all_decode and heads // kv_heads <= 16:
-        splits = decode_splits(ctx.max_context_len)
+        tiles = decode_tiles_per_cta(entries, kv_heads)
+        splits = decode_splits(ctx.max_context_len, tiles)
         partials = ctx.workspace.growing("attn.partials", (entries, heads, splits, head_dim + 2), torch.float32)
-        code = _library().me_attention_decode_bf16(
+        code = _library().me_attention_decode_bf16_tiled(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
-            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), scale, entries, splits, heads,
+            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), scale, entries, splits, tiles, heads,
             kv_heads, head_dim, page_size, width, window, stream,
         )  # fmt: skip
         ops._Counter.launches += 1  # the merge kernel; _check counts the first

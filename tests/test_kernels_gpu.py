@@ -327,6 +327,9 @@ BF16_ATTENTION_CASES = [
     ([300, 64, 2, 129], [300, 33, 2, 65], 6, 2, 128, 8),
     ([513, 40], [2, 40], 8, 8, 64, 16),
     ([1000], [1000], 2, 1, 128, 16),
+    # many (request, KV head) pairs: a decode CTA walks two, then four tiles of 128 keys
+    ([1 + (37 * i) % 700 for i in range(40)], [1] * 40, 8, 4, 64, 16),
+    ([1 + (53 * i) % 900 for i in range(70)], [1] * 70, 8, 4, 128, 16),
 ]
 
 
