@@ -9,7 +9,7 @@
 // 2,048-token prompt (BLOCK_T = 256) and a single decoded token (BLOCK_T = 16), where it
 // streams the weight through shared memory at the rate of HBM.
 //
-// Work split.  grid = (out tiles, token tiles, k splits).  With few tokens there are too few
+// Work split.  grid = (token tiles, out tiles, k splits).  With few tokens there are too few
 // output tiles to occupy 148 SMs, so the reduction axis is cut into `splits` ranges of 64-wide
 // k blocks; split s writes its partial sum to out[s][T][out] and the consumer kernel adds the
 // partials in ascending s.  Nothing is added atomically: results are reproducible.
@@ -166,7 +166,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * BLOCK_T, split = blockIdx.z;
+    // Token tiles vary fastest in the grid: CTAs that run at the same time share a weight tile,
+    // which then comes from DRAM once and from L2 for the others.
+    const int n0 = blockIdx.y * BLOCK_N, t0 = blockIdx.x * BLOCK_T, split = blockIdx.z;
     const int kb_begin = split * p.k_blocks_per_split;
     const int kb_end = min(kb_begin + p.k_blocks_per_split, p.k_blocks);
     const int iterations = kb_end - kb_begin;
@@ -286,7 +288,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         for (int c = 0; c < 16; ++c) {
                             const int t = t0 + c0 + c;
                             if (t < p.tokens) {
-                                const float activated = gate[c] / (1.0f + expf(-gate[c]));
+                                // The result is rounded to bfloat16, so the fast exponential and
+                                // division (a few ulp of float32) cost no accuracy here.
+                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
                                 out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
                             }
                         }
@@ -348,7 +352,7 @@ static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const Gemm
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    dim3 grid((p.outs + BLOCK_N - 1) / BLOCK_N, (p.tokens + BLOCK_T - 1) / BLOCK_T, splits);
+    dim3 grid((p.tokens + BLOCK_T - 1) / BLOCK_T, (p.outs + BLOCK_N - 1) / BLOCK_N, splits);
     return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
 }
 
