@@ -202,7 +202,7 @@ struct QkvArgs {
     const float* q_weight;  // [head_dim] or null: no norm
     const float* k_weight;
     float eps;
-    const float* inv_freq;  // [head_dim / 2] or null: no rotation
+    const float2* cos_sin;  // [tokens][head_dim / 2] (cos, sin) of each token's angles, or null: no rotation
     const int* positions;
     const int* slot_mapping;  // null: dense outputs
     void* q_out;
@@ -265,17 +265,16 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
             dst = dense + (static_cast<size_t>(token) * a.kv_heads + kv_head) * d;
         }
     }
-    const bool rotate = (is_q || is_k) && a.inv_freq != nullptr;
-    const float position = rotate ? static_cast<float>(a.positions[token]) : 0.0f;
+    const bool rotate = (is_q || is_k) && a.cos_sin != nullptr;
+    const float2* angles = a.cos_sin + static_cast<size_t>(token) * half;
     for (int i = lane; i < d; i += 32) {
         float value = weight ? weight[i] * (vec[i] * inv) : vec[i];
         if (rotate) {
             // rotate-half: out[i] = x[i] cos - x[i + half] sin (i < half); x[i] cos + x[i - half] sin.
             const int j = i < half ? i + half : i - half;
             const float other = weight ? weight[j] * (vec[j] * inv) : vec[j];
-            const float angle = position * a.inv_freq[i < half ? i : i - half];
-            float sine, cosine;
-            sincosf(angle, &sine, &cosine);
+            const float2 angle = angles[i < half ? i : i - half];
+            const float cosine = angle.x, sine = angle.y;
             value = i < half ? value * cosine - other * sine : value * cosine + other * sine;
         }
         dst[i] = from_float<OutT>(value);
@@ -314,21 +313,16 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
         const float4 w = *reinterpret_cast<const float4*>(weight + lane * 4);
         v = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
     }
-    if ((is_q || is_k) && a.inv_freq != nullptr) {
-        const float position = static_cast<float>(a.positions[token]);
+    if ((is_q || is_k) && a.cos_sin != nullptr) {
         const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
                                          __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
-        const float4 freq = *reinterpret_cast<const float4*>(a.inv_freq + (lane & 15) * 4);
+        const float4* angles = reinterpret_cast<const float4*>(a.cos_sin + static_cast<size_t>(token) * (D / 2) + (lane & 15) * 4);
+        const float4 first = angles[0], second = angles[1];  // (cos, sin) of four consecutive frequencies
         const float sign = lane < 16 ? -1.0f : 1.0f;  // first half: x cos - partner sin; second: x cos + partner sin
-        float sine, cosine;
-        sincosf(position * freq.x, &sine, &cosine);
-        v.x = v.x * cosine + sign * other.x * sine;
-        sincosf(position * freq.y, &sine, &cosine);
-        v.y = v.y * cosine + sign * other.y * sine;
-        sincosf(position * freq.z, &sine, &cosine);
-        v.z = v.z * cosine + sign * other.z * sine;
-        sincosf(position * freq.w, &sine, &cosine);
-        v.w = v.w * cosine + sign * other.w * sine;
+        v.x = v.x * first.x + sign * other.x * first.y;
+        v.y = v.y * first.z + sign * other.y * first.w;
+        v.z = v.z * second.x + sign * other.z * second.y;
+        v.w = v.w * second.z + sign * other.w * second.w;
     }
     OutT* dst;
     if (is_q) {
@@ -349,14 +343,36 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
     store4(dst + lane * 4, v);
 }
 
+// (cos, sin) of position * inv_freq for every token of the step, once per step for all layers
+// (src/mini_engine/model.py:79-83,183 of YuvGev00/mini-engine builds its tables once per step too).
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                  float2* __restrict__ out, int tokens, int half) {
+    pdl_trigger();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= tokens * half) return;
+    const int token = idx / half, i = idx % half;
+    float sine, cosine;
+    sincosf(static_cast<float>(positions[token]) * inv_freq[i], &sine, &cosine);
+    out[idx] = make_float2(cosine, sine);
+}
+
+ME_EXPORT int me_rope_table(const float* inv_freq, const int* positions, float* out, int tokens, int half,
+                            cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int total = tokens * half;
+    return launch_kernel(rope_table_kernel, (total + 255) / 256, 256, 0, stream, inv_freq, positions,
+                         reinterpret_cast<float2*>(out), tokens, half);
+}
+
 ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long split_stride, const float* q_weight,
-                                    const float* k_weight, float eps, const float* inv_freq,
+                                    const float* k_weight, float eps, const float* cos_sin,
                                     const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
                                     void* v_pages, void* k_dense, void* v_dense, int out_type, int tokens,
                                     int heads, int kv_heads, int head_dim, int page_size, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim > MAX_HEAD_DIM || head_dim % 2) return ME_ERR_UNSUPPORTED;
-    QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, inv_freq, positions, slot_mapping,
+    QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin), positions, slot_mapping,
               q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size};
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
@@ -364,7 +380,7 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
     // The choice depends on the model's sizes and the engine's buffers only, never on the batch.
     const bool vec = head_dim == 128 && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
-                     aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(inv_freq);
+                     aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin);
     if (out_type == ME_BF16) {
         if (vec) return launch_kernel(qk_norm_rope_store_128_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, 0, stream, a);
         return launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, smem, stream, a);

@@ -55,6 +55,7 @@ class DecodeGraphs:
             ctx.max_context_len = runner.table_width * runner.block_size
             runner.model.forward(ctx, runner.layout.views, rows)  # warm-up: builds, descriptors, buffers
             torch.cuda.synchronize()
+            ctx.memo.clear()  # what the warm-up computed once per step must be computed inside the graph too
             graph = torch.cuda.CUDAGraph()
             runner.workspace.frozen = True
             before = ops.launch_count()

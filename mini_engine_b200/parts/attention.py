@@ -112,7 +112,7 @@ class GroupedQueryAttention(Mixer):
         kv_in = 0 if self.reads_shared_cache else self.kv_heads
         qkv = self.qkv.forward(h, ctx, "attn.qkv")
         q = ctx.buffer("attn.q", (tokens, self.heads * d), ctx.dtype)
-        table = self.position.fused_rotary_table()
+        table = self.position.step_angles(ctx)
         slots = ctx.slot_mapping[cache.group]
         args: dict[str, Any] = dict(
             qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, q_weight=self.q_norm,
@@ -123,17 +123,17 @@ class GroupedQueryAttention(Mixer):
             # This execution reads another entry's cache: its own keys and values are not kept.
             unused_k = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
             unused_v = ctx.buffer("attn.v_new", (tokens, kv_in * d), ctx.dtype)
-            ops.qk_norm_rope_store(**args, inv_freq=table, k_dense=unused_k, v_dense=unused_v)
+            ops.qk_norm_rope_store(**args, cos_sin=table, k_dense=unused_k, v_dense=unused_v)
             if table is None:
                 self.position.apply(q.view(tokens, self.heads, d), unused_k.view(tokens, kv_in, d), ctx.positions)
         elif table is not None or kv_in == 0:
             ops.qk_norm_rope_store(
-                **args, inv_freq=table, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v
+                **args, cos_sin=table, slot_mapping=slots, k_pages=cache.k, v_pages=cache.v
             )
         else:  # a position encoding that the fused kernel does not know: three steps
             k_new = ctx.buffer("attn.k_new", (tokens, kv_in * d), ctx.dtype)
             v_new = ctx.buffer("attn.v_new", (tokens, kv_in * d), ctx.dtype)
-            ops.qk_norm_rope_store(**args, inv_freq=None, k_dense=k_new, v_dense=v_new)
+            ops.qk_norm_rope_store(**args, cos_sin=None, k_dense=k_new, v_dense=v_new)
             self.position.apply(q.view(tokens, self.heads, d), k_new.view(tokens, kv_in, d), ctx.positions)
             ops.kv_store(k_new, v_new, slots, cache.k, cache.v, kv_in, d, ctx.page_size)
         out = ctx.buffer("attn.out", (tokens, self.heads * d), ctx.dtype)

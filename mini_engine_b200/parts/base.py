@@ -119,6 +119,7 @@ class StepContext:
     workspace: "Any" = None  # Workspace: named persistent buffers
     all_decode: bool = False  # every entry brings exactly one token
     host: Mapping[str, Any] = field(default_factory=dict)  # host copies for parts written in Python
+    memo: dict = field(default_factory=dict)  # what parts compute once per step and share between layers
 
     def buffer(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
@@ -152,6 +153,11 @@ class PositionEncoding(Part):
         """Inverse frequencies ``[rotary_dim / 2]`` (float32, on the device) when the
         encoding is a rotate-half rotation that the mixer's fused kernel can apply; else
         ``None`` and the mixer calls :meth:`apply`."""
+        return None
+
+    def step_angles(self, ctx: "StepContext") -> torch.Tensor | None:
+        """``[T, rotary_dim / 2, 2]`` float32 (cos, sin) for the step's tokens when the
+        encoding is a fusable rotation, made once per step and shared by all layers."""
         return None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:

@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import PositionEncoding, register
 
 
@@ -32,6 +33,15 @@ class RotaryEncoding(PositionEncoding):
         if self._table is None:
             self._table = self.inv_freq().to("cuda")
         return self._table
+
+    def step_angles(self, ctx) -> torch.Tensor:
+        key = ("rope", self.head_dim, self.theta)
+        held = ctx.memo.get(key)
+        if held is None:
+            held = ctx.buffer(f"rope.angles.{self.head_dim}.{self.theta}", (ctx.num_tokens, self.head_dim // 2, 2), torch.float32)
+            ops.rope_table(self.fused_rotary_table(), ctx.positions, held)
+            ctx.memo[key] = held
+        return held
 
 
 @register("position_encoding", "none")

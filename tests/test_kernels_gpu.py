@@ -180,12 +180,16 @@ def test_qk_norm_rope_store(heads, kv_heads, head_dim, page, dtype):
     slots = torch.randperm(pages * page)[:tokens].to(torch.int32)
     slots[4] = -1  # not stored
     inv_freq = (1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).cuda()
+    cos_sin = torch.empty(tokens, head_dim // 2, 2, device="cuda")
+    ops().rope_table(inv_freq, positions.cuda(), cos_sin)
+    angles = positions.float()[:, None] * inv_freq.cpu()[None, :]
+    assert torch.allclose(cos_sin[..., 0].cpu(), angles.cos(), atol=2e-6) and torch.allclose(cos_sin[..., 1].cpu(), angles.sin(), atol=2e-6)
     q_out = torch.empty(tokens, heads * head_dim, device="cuda", dtype=dtype)
     k_pages = torch.zeros(pages, kv_heads, page, head_dim, device="cuda", dtype=dtype)
     v_pages = torch.zeros_like(k_pages)
     ops().qk_norm_rope_store(
         qkv=qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim, q_weight=qw, k_weight=kw, eps=eps,
-        inv_freq=inv_freq, positions=positions.cuda(), q_out=q_out, page_size=page, slot_mapping=slots.cuda(),
+        cos_sin=cos_sin, positions=positions.cuda(), q_out=q_out, page_size=page, slot_mapping=slots.cuda(),
         k_pages=k_pages, v_pages=v_pages,
     )  # fmt: skip
     total = qkv.double().sum(0).cpu()
