@@ -2,7 +2,10 @@
 
 * every entry brings one token and the group has at most 16 query heads: the split decode
   kernel (scratch for the partial results comes from the workspace);
-* otherwise: the portions kernel, for any mix of portion lengths.
+* otherwise, head size 128, no window, pages of 8 to 128 tokens and a portion of at least 32
+  tokens in the batch: the tcgen05 kernel (both products on the tensor cores with accumulators in
+  tensor memory, keys and values fetched by TMA page by page);
+* otherwise: the mma.sync portions kernel, for any mix of portion lengths.
 
 Head sizes 64 and 128 are taken; other sizes use the generic kernel.
 """
@@ -16,7 +19,74 @@ import torch
 from mini_engine_b200.csrc.build import load_library
 
 DECODE_CHUNK = 128
+TENSOR_MEMORY_MIN_TOKENS = 32  # portions at least this long take the tcgen05 kernel
 _lib = None
+_tc_lib = None
+_page_maps: dict[tuple[int, tuple[int, ...]], object] = {}
+_query_maps: dict[tuple[int, int, int], object] = {}
+
+
+def _tc_library():
+    global _tc_lib
+    if _tc_lib is None:
+        import ctypes
+
+        lib = load_library("attention_tcgen05")
+        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p]
+        lib.me_attention_tcgen05.restype = c_int
+        lib.me_attention_take_error.argtypes = [ctypes.POINTER(c_int)]
+        lib.me_attention_take_error.restype = c_int
+        _tc_lib = lib
+    return _tc_lib
+
+
+def take_error() -> int:
+    """First failure that the tcgen05 attention kernel recorded since the last call, or 0."""
+    if _tc_lib is None:
+        return 0
+    import ctypes
+
+    code = c_int(0)
+    status = _tc_lib.me_attention_take_error(ctypes.byref(code))
+    if status != 0:
+        raise RuntimeError(f"could not read the attention kernels' error flag (CUDA error {status})")
+    return code.value
+
+
+def _page_map(pages: torch.Tensor):
+    """TMA descriptor of a page array seen as [(pages * kv_heads * page_size), head_dim]."""
+    from mini_engine_b200.csrc import tensor_core
+
+    key = (pages.data_ptr(), tuple(pages.shape))
+    held = _page_maps.get(key)
+    if held is None:
+        count, kv_heads, page_size, head_dim = pages.shape
+        held = tensor_core._make_map(pages.view(count * kv_heads * page_size, head_dim), page_size)
+        _page_maps[key] = held
+    return held
+
+
+def _query_map(q: torch.Tensor):
+    from mini_engine_b200.csrc import tensor_core
+
+    key = (q.data_ptr(), q.shape[0], q.shape[1])
+    held = _query_maps.get(key)
+    if held is None:
+        if len(_query_maps) > 8192:
+            _query_maps.clear()
+        held = tensor_core._make_map(q, 128)
+        _query_maps[key] = held
+    return held
+
+
+def tensor_memory_kernel_takes(head_dim: int, page_size: int, window: int, max_query_len: int) -> bool:
+    return (
+        head_dim == 128
+        and window == 0
+        and 8 <= page_size <= 128
+        and 128 % page_size == 0
+        and max_query_len >= TENSOR_MEMORY_MIN_TOKENS
+    )
 
 
 def _library():
@@ -74,6 +144,14 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
         )  # fmt: skip
         ops._Counter.launches += 1  # the merge kernel; _check counts the first
         ops._check(code, "attention_decode_bf16")
+        return
+    if tensor_memory_kernel_takes(head_dim, page_size, window, ctx.max_query_len):
+        code = _tc_library().me_attention_tcgen05(
+            _query_map(q), _page_map(k_pages), _page_map(v_pages), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
+            ctx.context_lens.data_ptr(), out.data_ptr(), scale, entries, ctx.max_query_len, heads, kv_heads, head_dim,
+            page_size, width, stream,
+        )  # fmt: skip
+        ops._check(code, "attention_tcgen05")
         return
     code = _library().me_attention_portions_bf16(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),

@@ -1,0 +1,301 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores:
+// both products of attention run as tcgen05.mma with accumulators in tensor memory.
+//
+// One CTA takes 128 consecutive new tokens of one (request, query head) and walks the request's
+// keys in tiles of 128 that start at multiples of 128 in absolute position:
+//
+//   S = Q K^T      tcgen05.mma, A = Q tile and B = K tile from shared memory (K-major, 128-byte
+//                  swizzle as TMA wrote them), D = S in tensor memory columns [0, 128)
+//   P = softmax    128 threads, one query row each (tensor-memory lane = row): two passes over
+//                  S with tcgen05.ld (row maximum, then exp2 and row sum in float32); P is
+//                  rounded to bfloat16 and stored with tcgen05.st over the first 64 columns of S
+//   O += P V       tcgen05.mma with A = P read from tensor memory and B = V tile from shared
+//                  memory as an MN-major operand (V is [key][dim]: rows run along the reduction),
+//                  D = O in columns [128, 256), accumulated over the tiles
+//
+// When a row's maximum grows, O is rescaled in tensor memory (ld, multiply, st) before the next
+// P V product; a warp skips this when none of its rows changed.  Keys and values come from the
+// cache by TMA, one box per page and 64-dimension half, addressed through the request's block
+// table; queries likewise.  Keys beyond the request's length are read from its last page (finite
+// values) and masked by position.
+//
+// Roles (192 threads): warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs, warps 2-5
+// are the softmax rows.  Shared memory is 96 KB and tensor memory 256 columns, so two CTAs share
+// an SM and one's softmax overlaps the other's products.  Every wait is bounded (see tcgen05.cuh).
+//
+// Formula and conventions as in attention_bf16.cu (YuvGev00/mini-engine:
+// src/mini_engine/attention.py:84-86,160-175; probabilities rounded to the value dtype before the
+// second product, :173).  head_dim is 128; pages of 8 to 128 tokens; no window.
+#include "tcgen05.cuh"
+
+constexpr int TC_ROWS = 128;   // query rows per CTA
+constexpr int TC_KEYS = 128;   // keys per tile
+constexpr int TC_DIM = 128;    // head_dim
+constexpr int TC_THREADS = 192;
+constexpr int TC_HALF_BYTES = 128 * 64 * 2;  // a 128-row, 64-column bfloat16 block
+constexpr int TC_TMEM_COLUMNS = 256;
+constexpr float TC_LOG2E = 1.4426950408889634f;
+
+__device__ int g_attention_error = 0;
+
+struct TcAttnParams {
+    const int* block_table;   // [entries][table_width]
+    const int* cu_tokens;     // [entries + 1]
+    const int* context_lens;  // [entries]
+    __nv_bfloat16* out;       // [tokens][heads][128]
+    float scale_log2;
+    int heads, kv_heads, page_size, table_width;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+    return packed;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_tile = tiles;                      // two halves of [128 rows][64 dims]
+    uint8_t* k_tile = tiles + 2 * TC_HALF_BYTES;  // two halves of [128 keys][64 dims]
+    uint8_t* v_tile = tiles + 4 * TC_HALF_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + 6 * TC_HALF_BYTES);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *v_full = bars + 3, *v_empty = bars + 4,
+             *s_full = bars + 5, *p_full = bars + 6, *o_full = bars + 7;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Later blocks of a request see more keys: start them first.
+    const int entry = blockIdx.z, head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        mbar_init(k_full, 1);
+        mbar_init(k_empty, 1);
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 128);
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(tmem_holder, TC_TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_s = *tmem_holder;   // S, then P over its first 64 columns
+    const uint32_t tmem_o = tmem_s + 128;
+
+    pdl_trigger();
+    pdl_wait();
+    const int token0 = p.cu_tokens[entry];
+    const int new_tokens = p.cu_tokens[entry + 1] - token0;
+    const bool has_work = q_block * TC_ROWS < new_tokens;  // uniform for the CTA
+    const int context = p.context_lens[entry];
+    const int rows_valid = min(TC_ROWS, new_tokens - q_block * TC_ROWS);
+    const int pos0 = context - new_tokens + q_block * TC_ROWS;  // position of row 0
+    const int tiles_count = has_work ? (pos0 + rows_valid - 1) / TC_KEYS + 1 : 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0 && has_work) {
+            const int kv_head = head / (p.heads / p.kv_heads);
+            const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+            const int pages_per_tile = TC_KEYS / p.page_size;
+            const int last_page_index = (context - 1) / p.page_size;
+            const int page_bytes = p.page_size * 128;  // one page of one 64-dimension half
+            mbar_expect_tx(q_full, 2 * TC_HALF_BYTES);
+            tma_load_2d(q_tile, &map_q, head * TC_DIM, token0 + q_block * TC_ROWS, q_full);
+            tma_load_2d(q_tile + TC_HALF_BYTES, &map_q, head * TC_DIM + 64, token0 + q_block * TC_ROWS, q_full);
+            for (int j = 0; j < tiles_count; ++j) {
+                const uint32_t parity = j & 1;
+                for (int which = 0; which < 2; ++which) {  // keys, then values
+                    uint64_t* empty = which ? v_empty : k_empty;
+                    uint64_t* full = which ? v_full : k_full;
+                    uint8_t* tile = which ? v_tile : k_tile;
+                    const CUtensorMap* map = which ? &map_v : &map_k;
+                    if (!mbar_wait(empty, parity ^ 1)) { atomicCAS(&g_attention_error, 0, (1 << 8) | which); j = tiles_count; break; }
+                    mbar_expect_tx(full, 2 * TC_HALF_BYTES);
+                    for (int g = 0; g < pages_per_tile; ++g) {
+                        const int page = table[min(j * pages_per_tile + g, last_page_index)];
+                        const int row = (page * p.kv_heads + kv_head) * p.page_size;
+                        tma_load_2d(tile + g * page_bytes, map, 0, row, full);
+                        tma_load_2d(tile + TC_HALF_BYTES + g * page_bytes, map, 64, row, full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && has_work) {
+            constexpr uint32_t idesc_s = make_idesc(TC_KEYS);        // S[128 x 128] = Q K^T, K-major operands
+            constexpr uint32_t idesc_o = make_idesc(TC_DIM, true);   // O[128 x 128] += P V, V is MN-major
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicCAS(&g_attention_error, 0, 2 << 8);
+            for (int j = 0; j < tiles_count && ok; ++j) {
+                const uint32_t parity = j & 1;
+                // The S columns are free once the previous P V product has read P out of them.
+                ok = mbar_wait(k_full, parity) && (j == 0 || mbar_wait(o_full, parity ^ 1));
+                if (!ok) { atomicCAS(&g_attention_error, 0, (2 << 8) | 1); break; }
+                tcgen05_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < TC_DIM / 16; ++kk) {
+                    const uint32_t offset = (kk / 4) * TC_HALF_BYTES + (kk % 4) * 32;
+                    tcgen05_mma_bf16(tmem_s, smem_desc_sw128(smem_u32(q_tile) + offset),
+                                     smem_desc_sw128(smem_u32(k_tile) + offset), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tcgen05_commit(s_full);
+                tcgen05_commit(k_empty);
+                ok = mbar_wait(p_full, parity) && mbar_wait(v_full, parity);
+                if (!ok) { atomicCAS(&g_attention_error, 0, (2 << 8) | 2); break; }
+                tcgen05_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < TC_KEYS / 16; ++kk) {
+                    // 16 keys = 16 rows of 128 bytes; the second 64 dimensions are one half further
+                    const uint64_t v_desc = smem_desc_sw128_mn(smem_u32(v_tile) + kk * 16 * 128, TC_HALF_BYTES);
+                    tcgen05_mma_bf16_ts(tmem_o, tmem_s + kk * 8, v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(o_full);
+                tcgen05_commit(v_empty);
+            }
+        }
+    } else if (has_work) {
+        // ------------------------------------------------------------------ softmax rows
+        const int quarter = warp & 3;  // this warp's tensor-memory lanes are [32 * quarter, +32)
+        const int row = quarter * 32 + lane;
+        const int row_pos = pos0 + row;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        float row_max = -INFINITY, row_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < tiles_count && ok; ++j) {
+            const uint32_t parity = j & 1;
+            ok = mbar_wait(s_full, parity);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) atomicCAS(&g_attention_error, 0, 3 << 8); break; }
+            tcgen05_fence_after();
+            const int first_key = j * TC_KEYS;
+            const bool masked_tile = first_key + TC_KEYS - 1 > pos0;  // some row does not see every key
+            float tile_max = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float s[32];
+                tcgen05_ld32(tmem_s + lane_base + c * 32, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const bool visible = !masked_tile || first_key + c * 32 + i <= row_pos;
+                    if (visible) tile_max = fmaxf(tile_max, s[i] * p.scale_log2);
+                }
+            }
+            const float new_max = fmaxf(row_max, tile_max);
+            const float base = new_max == -INFINITY ? 0.0f : new_max;
+            const float rescale = exp2f(row_max - base);  // 0 while the row has seen nothing
+            row_sum *= rescale;
+            row_max = new_max;
+            if (j > 0) {
+                // O of the previous tiles must be complete before it is rescaled or added to.
+                ok = mbar_wait(o_full, parity ^ 1);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { if (lane == 0) atomicCAS(&g_attention_error, 0, (3 << 8) | 1); break; }
+                tcgen05_fence_after();
+                if (__any_sync(0xffffffffu, rescale != 1.0f)) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        float o[32];
+                        tcgen05_ld32(tmem_o + lane_base + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= rescale;
+                        tcgen05_st32(tmem_o + lane_base + c * 32, o);
+                    }
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float s[32];
+                tcgen05_ld32(tmem_s + lane_base + c * 32, s);
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const bool v0 = !masked_tile || first_key + c * 32 + i <= row_pos;
+                    const bool v1 = !masked_tile || first_key + c * 32 + i + 1 <= row_pos;
+                    const float p0 = v0 ? exp2f(s[i] * p.scale_log2 - base) : 0.0f;
+                    const float p1 = v1 ? exp2f(s[i + 1] * p.scale_log2 - base) : 0.0f;
+                    row_sum += p0 + p1;
+                    packed[i / 2] = pack_bf16x2(p0, p1);
+                }
+                // P chunk c covers columns [16 c, 16 c + 16): all of them were read above already.
+                tcgen05_st16(tmem_s + lane_base + c * 16, packed);
+            }
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok) {
+            ok = mbar_wait(o_full, (tiles_count - 1) & 1);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok && lane == 0) atomicCAS(&g_attention_error, 0, (3 << 8) | 2);
+        }
+        if (ok) {
+            tcgen05_fence_after();
+            const float inv = 1.0f / row_sum;
+            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head) * TC_DIM;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float o[32];
+                tcgen05_ld32(tmem_o + lane_base + c * 32, o);  // collective: every lane takes part
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 chunk;
+                        chunk.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
+                        chunk.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+                        chunk.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
+                        chunk.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = chunk;
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem_s, TC_TMEM_COLUMNS);
+}
+
+// -------------------------------------------------------------------------------- host
+
+// q, k and v are described by TMA maps made with me_make_tensor_map (gemm_tcgen05.cu): q as
+// [tokens][heads * 128] with boxes of 128 rows, the page arrays as [(pages * kv_heads *
+// page_size)][128] with boxes of page_size rows.
+ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const void* map_v, const int* block_table,
+                                   const int* cu_tokens, const int* context_lens, void* out, float scale, int entries,
+                                   int max_new_tokens, int heads, int kv_heads, int head_dim, int page_size,
+                                   int table_width, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (head_dim != TC_DIM || kv_heads < 1 || heads % kv_heads) return ME_ERR_UNSUPPORTED;
+    if (page_size < 8 || page_size > TC_KEYS || TC_KEYS % page_size) return ME_ERR_UNSUPPORTED;
+    alignas(64) CUtensorMap q, k, v;
+    memcpy(&q, map_q, sizeof(q));
+    memcpy(&k, map_k, sizeof(k));
+    memcpy(&v, map_v, sizeof(v));
+    TcAttnParams p{block_table, cu_tokens, context_lens, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
+                   heads, kv_heads, page_size, table_width};
+    constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid((max_new_tokens + TC_ROWS - 1) / TC_ROWS, heads, entries);
+    return launch_kernel(attention_tcgen05_kernel, grid, TC_THREADS, SMEM, stream, q, k, v, p);
+}
+
+ME_EXPORT int me_attention_take_error(int* code) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(code, g_attention_error, sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (*code != 0) e = cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
+    return static_cast<int>(e);
+}

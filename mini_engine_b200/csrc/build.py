@@ -34,6 +34,7 @@ LIBRARIES = {
     "attention_generic": "attention_generic.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_tcgen05": "attention_tcgen05.cu",
     "sampling": "sampling.cu",
 }
 

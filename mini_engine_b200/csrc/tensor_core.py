@@ -67,6 +67,9 @@ def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> in
 
 
 def _make_map(tensor: torch.Tensor, box_rows: int) -> ctypes.Array:
+    """TMA descriptor of a contiguous bfloat16 matrix with boxes of ``box_rows`` x 64 elements."""
+    if tensor.dtype != torch.bfloat16 or not tensor.is_contiguous() or tensor.dim() != 2:
+        raise RuntimeError("TMA descriptors are made for contiguous 2-D bfloat16 tensors")
     rows, inner = tensor.shape
     holder = (ctypes.c_ubyte * 128)()
     code = _library().me_make_tensor_map(holder, tensor.data_ptr(), rows, inner, box_rows)

@@ -368,6 +368,34 @@ def test_paged_attention_bf16_tensor_core(case):
         head_dim, head_dim**-0.5, 0,
     )  # fmt: skip
     assert rel_error(out.cpu(), data["want"]) < 1e-2
+    assert attention_bf16.take_error() == 0
+
+
+TENSOR_MEMORY_CASES = [
+    # lengths, new tokens of each, heads, kv heads, page: head_dim 128, portions of 32 tokens and more
+    ([128], [128], 2, 1, 16),  # exactly one block and one tile
+    ([129, 40], [129, 33], 4, 2, 16),  # a second block of one row; a continuation
+    ([700, 64, 300], [700, 64, 45], 8, 2, 8),  # several tiles, small pages, a portion far into its request
+    ([1000, 3, 257], [256, 3, 257], 4, 4, 32),  # the last 256 tokens of 1000; a tiny entry in the same launch
+    ([2048], [2048], 2, 1, 128),  # pages as large as a tile
+]
+
+
+@pytest.mark.parametrize("case", TENSOR_MEMORY_CASES)
+def test_paged_attention_tcgen05(case):
+    from mini_engine_b200.csrc import attention_bf16
+
+    lengths, news, heads, kv_heads, page = case
+    head_dim = 128
+    assert attention_bf16.tensor_memory_kernel_takes(head_dim, page, 0, max(news))
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=13, spike=(0, 3))
+    out = torch.full_like(data["q"], float("nan"))
+    attention_bf16.paged_attention(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
+        head_dim, head_dim**-0.5, 0,
+    )  # fmt: skip
+    assert attention_bf16.take_error() == 0
+    assert rel_error(out.cpu(), data["want"]) < 1e-2
 
 
 @pytest.mark.parametrize("news", [[1, 1], [90, 5]])
