@@ -47,6 +47,13 @@ struct TcAttnParams {
     int heads, kv_heads, page_size, table_width;
 };
 
+// 2^x by the special-function unit alone (about 2 ulp; the result is rounded to bfloat16 anyway).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -100,31 +107,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0 && has_work) {
+        // The whole warp takes part: lane g looks up page g of the tile in the block table (one
+        // coalesced load for the tile, one tile ahead of its use) and issues that page's copies.
+        if (has_work) {
             const int kv_head = head / (p.heads / p.kv_heads);
             const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
             const int pages_per_tile = TC_KEYS / p.page_size;
             const int last_page_index = (context - 1) / p.page_size;
             const int page_bytes = p.page_size * 128;  // one page of one 64-dimension half
-            mbar_expect_tx(q_full, 2 * TC_HALF_BYTES);
-            tma_load_2d(q_tile, &map_q, head * TC_DIM, token0 + q_block * TC_ROWS, q_full);
-            tma_load_2d(q_tile + TC_HALF_BYTES, &map_q, head * TC_DIM + 64, token0 + q_block * TC_ROWS, q_full);
-            for (int j = 0; j < tiles_count; ++j) {
+            if (lane == 0) {
+                mbar_expect_tx(q_full, 2 * TC_HALF_BYTES);
+                tma_load_2d(q_tile, &map_q, head * TC_DIM, token0 + q_block * TC_ROWS, q_full);
+                tma_load_2d(q_tile + TC_HALF_BYTES, &map_q, head * TC_DIM + 64, token0 + q_block * TC_ROWS, q_full);
+            }
+            const bool loads = lane < pages_per_tile;
+            int page = loads ? table[min(lane, last_page_index)] : 0;
+            bool ok = true;
+            for (int j = 0; j < tiles_count && ok; ++j) {
                 const uint32_t parity = j & 1;
-                for (int which = 0; which < 2; ++which) {  // keys, then values
+                const int next_page = (loads && j + 1 < tiles_count) ? table[min((j + 1) * pages_per_tile + lane, last_page_index)] : 0;
+                const int row = (page * p.kv_heads + kv_head) * p.page_size;
+                for (int which = 0; which < 2 && ok; ++which) {  // keys, then values
                     uint64_t* empty = which ? v_empty : k_empty;
                     uint64_t* full = which ? v_full : k_full;
                     uint8_t* tile = which ? v_tile : k_tile;
                     const CUtensorMap* map = which ? &map_v : &map_k;
-                    if (!mbar_wait(empty, parity ^ 1)) { atomicCAS(&g_attention_error, 0, (1 << 8) | which); j = tiles_count; break; }
-                    mbar_expect_tx(full, 2 * TC_HALF_BYTES);
-                    for (int g = 0; g < pages_per_tile; ++g) {
-                        const int page = table[min(j * pages_per_tile + g, last_page_index)];
-                        const int row = (page * p.kv_heads + kv_head) * p.page_size;
-                        tma_load_2d(tile + g * page_bytes, map, 0, row, full);
-                        tma_load_2d(tile + TC_HALF_BYTES + g * page_bytes, map, 64, row, full);
+                    if (lane == 0) {
+                        ok = mbar_wait(empty, parity ^ 1);
+                        if (ok) mbar_expect_tx(full, 2 * TC_HALF_BYTES);
+                        else atomicCAS(&g_attention_error, 0, (1 << 8) | which);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok && loads) {
+                        tma_load_2d(tile + lane * page_bytes, map, 0, row, full);
+                        tma_load_2d(tile + TC_HALF_BYTES + lane * page_bytes, map, 64, row, full);
                     }
                 }
+                page = next_page;
             }
         }
     } else if (warp == 1) {
@@ -176,18 +195,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!ok) { if (lane == 0) atomicCAS(&g_attention_error, 0, 3 << 8); break; }
             tcgen05_fence_after();
             const int first_key = j * TC_KEYS;
-            const bool masked_tile = first_key + TC_KEYS - 1 > pos0;  // some row does not see every key
+            // Only the last tile or two of a block hold keys that some row must not see; every other
+            // tile takes the path without per-element position tests.
+            const bool masked_tile = first_key + TC_KEYS - 1 > pos0;
             float tile_max = -INFINITY;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 float s[32];
                 tcgen05_ld32(tmem_s + lane_base + c * 32, s);
+                if (masked_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const bool visible = !masked_tile || first_key + c * 32 + i <= row_pos;
-                    if (visible) tile_max = fmaxf(tile_max, s[i] * p.scale_log2);
+                    for (int i = 0; i < 32; ++i)
+                        if (first_key + c * 32 + i <= row_pos) tile_max = fmaxf(tile_max, s[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) tile_max = fmaxf(tile_max, fmaxf(s[i], s[i + 1]));
                 }
             }
+            tile_max *= p.scale_log2;  // the scale is positive: the maximum of the scaled scores
             const float new_max = fmaxf(row_max, tile_max);
             const float base = new_max == -INFINITY ? 0.0f : new_max;
             const float rescale = exp2f(row_max - base);  // 0 while the row has seen nothing
@@ -210,19 +235,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                 }
             }
+            const float negative_base = -base;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 float s[32];
                 tcgen05_ld32(tmem_s + lane_base + c * 32, s);
                 uint32_t packed[16];
+                if (masked_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const bool v0 = !masked_tile || first_key + c * 32 + i <= row_pos;
-                    const bool v1 = !masked_tile || first_key + c * 32 + i + 1 <= row_pos;
-                    const float p0 = v0 ? exp2f(s[i] * p.scale_log2 - base) : 0.0f;
-                    const float p1 = v1 ? exp2f(s[i + 1] * p.scale_log2 - base) : 0.0f;
-                    row_sum += p0 + p1;
-                    packed[i / 2] = pack_bf16x2(p0, p1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = first_key + c * 32 + i;
+                        const float p0 = key <= row_pos ? fast_exp2(fmaf(s[i], p.scale_log2, negative_base)) : 0.0f;
+                        const float p1 = key + 1 <= row_pos ? fast_exp2(fmaf(s[i + 1], p.scale_log2, negative_base)) : 0.0f;
+                        row_sum += p0 + p1;
+                        packed[i / 2] = pack_bf16x2(p0, p1);
+                    }
+                } else {
+                    float partial = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(fmaf(s[i], p.scale_log2, negative_base));
+                        const float p1 = fast_exp2(fmaf(s[i + 1], p.scale_log2, negative_base));
+                        partial += p0 + p1;
+                        packed[i / 2] = pack_bf16x2(p0, p1);
+                    }
+                    row_sum += partial;
                 }
                 // P chunk c covers columns [16 c, 16 c + 16): all of them were read above already.
                 tcgen05_st16(tmem_s + lane_base + c * 16, packed);
