@@ -39,6 +39,7 @@ struct AttnParams {
     const int* context_lens;  // [entries]
     __nv_bfloat16* out;       // [tokens][heads][D]
     float* partials;          // decode: [entries][heads][max_splits][D + 2]
+    int* counters;            // decode: [entries][kv_heads] arrival counts, all zero between launches; or null
     float scale_log2;         // scale * log2(e)
     int heads, kv_heads, page_size, table_width, window, max_splits;
     int page_shift;  // log2(page_size) when it is a power of two, else -1
@@ -307,6 +308,9 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
 constexpr int MAX_DECODE_TILES = 8;
 
 template <int D>
+__device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int head, int first, int last, int lane);
+
+template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int KEYS = DECODE_WARP_KEYS;
@@ -448,10 +452,58 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
         const int head = kv_head * group + row;
         p.partials[((static_cast<size_t>(entry) * p.heads + head) * p.max_splits + split) * STRIDE + col] = value;
     }
+    if (p.counters == nullptr) return;  // a separate kernel merges
+
+    // The CTA that finishes last among those of this (request, KV head) merges all their partials,
+    // always in ascending order of the keys, so the result does not depend on who is last.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int active = position / span - lowest / span + 1;
+        int* counter = p.counters + entry * p.kv_heads + kv_head;
+        const int ticket = atomicAdd(counter, 1);
+        is_last = ticket == active - 1;
+        if (is_last) *counter = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int row = warp; row < group; row += 4)
+        merge_head<D>(p, entry, kv_head * group + row, lowest / span, position / span, lane);
 }
 
-// One warp per (entry, head): merges the partials that the decode kernel wrote, in ascending
-// order of their keys.  Each lane owns D / 32 output elements.
+// One warp merges the partials of one (entry, head) in ascending order of their keys and writes
+// the head's output.  Each lane owns D / 32 output elements.
+template <int D>
+__device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int head, int first, int last, int lane) {
+    constexpr int STRIDE = D + 2;
+    constexpr int PER_LANE = D / 32;
+    const float* base = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
+    float total_max = -INFINITY;
+    for (int s = first + lane; s <= last; s += 32) total_max = fmaxf(total_max, __ldcg(base + s * STRIDE + D));
+    total_max = warp_max(total_max);
+    float value[PER_LANE], denom = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) value[i] = 0.0f;
+#pragma unroll 4
+    for (int s = first; s <= last; ++s) {
+        const float m = __ldcg(base + s * STRIDE + D);
+        if (m == -INFINITY) continue;
+        const float weight = exp2f(m - total_max);
+        denom += __ldcg(base + s * STRIDE + D + 1) * weight;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) value[i] += __ldcg(base + s * STRIDE + lane * PER_LANE + i) * weight;
+    }
+    const int token = p.cu_tokens[entry];
+    __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
+    const float inv = 1.0f / denom;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; i += 2)
+        *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(value[i] * inv, value[i + 1] * inv);
+}
+
+// One warp per (entry, head), for callers that give the decode kernel no arrival counters.
 template <int D>
 __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams p, int items) {
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -462,31 +514,7 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int span = p.tiles_per_cta * DECODE_CHUNK;
-    const int first = lowest / span, last = position / span;
-    constexpr int STRIDE = D + 2;
-    constexpr int PER_LANE = D / 32;
-    const float* base = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
-    float total_max = -INFINITY;
-    for (int s = first + lane; s <= last; s += 32) total_max = fmaxf(total_max, base[s * STRIDE + D]);
-    total_max = warp_max(total_max);
-    float value[PER_LANE], denom = 0.0f;
-#pragma unroll
-    for (int i = 0; i < PER_LANE; ++i) value[i] = 0.0f;
-#pragma unroll 4
-    for (int s = first; s <= last; ++s) {
-        const float m = base[s * STRIDE + D];
-        if (m == -INFINITY) continue;
-        const float weight = exp2f(m - total_max);
-        denom += base[s * STRIDE + D + 1] * weight;
-#pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) value[i] += base[s * STRIDE + lane * PER_LANE + i] * weight;
-    }
-    const int token = p.cu_tokens[entry];
-    __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
-    const float inv = 1.0f / denom;
-#pragma unroll
-    for (int i = 0; i < PER_LANE; i += 2)
-        *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16(value[i] * inv, value[i + 1] * inv);
+    merge_head<D>(p, entry, head, lowest / span, position / span, lane);
 }
 
 // -------------------------------------------------------------------------------- host
@@ -517,7 +545,7 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
     }
     dim3 grid(p.max_splits, p.kv_heads, entries);
     const int status = launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
-    if (status != 0) return status;
+    if (status != 0 || p.counters != nullptr) return status;
     const int items = entries * p.heads;
     return launch_kernel(attention_decode_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
 }
@@ -541,8 +569,8 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
     if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
-                 static_cast<__nv_bfloat16*>(out), nullptr, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, 0, shift_of(page_size), 1};
+                 static_cast<__nv_bfloat16*>(out), nullptr, nullptr, scale * LOG2E, heads, kv_heads, page_size,
+                 table_width, window, 0, shift_of(page_size), 1};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
@@ -550,10 +578,12 @@ ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, con
 // Every entry brings exactly one token.  `partials` is scratch of
 // entries * heads * max_splits * (head_dim + 2) floats; a CTA walks `tiles_per_cta` (1..8) tiles
 // of 128 keys, and max_splits covers the longest context that this launch may meet:
-// ceil(max_context / (128 * tiles_per_cta)).
+// ceil(max_context / (128 * tiles_per_cta)).  `counters` is entries * kv_heads ints that are zero
+// before the launch (the kernel leaves them zero again): the last CTA of a (request, KV head) then
+// merges the partials itself; with null a second kernel does.
 ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages, const void* v_pages,
                                              const int* block_table, const int* cu_tokens, const int* context_lens,
-                                             void* out, float* partials, float scale, int entries, int max_splits,
+                                             void* out, float* partials, int* counters, float scale, int entries, int max_splits,
                                              int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
                                              int table_width, int window, cudaStream_t stream) {
     if (entries <= 0) return 0;
@@ -561,8 +591,8 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
     if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
-                 static_cast<__nv_bfloat16*>(out), partials, scale * LOG2E, heads, kv_heads, page_size, table_width,
-                 window, max_splits, shift_of(page_size), tiles_per_cta};
+                 static_cast<__nv_bfloat16*>(out), partials, counters, scale * LOG2E, heads, kv_heads, page_size,
+                 table_width, window, max_splits, shift_of(page_size), tiles_per_cta};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 
@@ -572,7 +602,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                                        float scale, int entries, int max_splits, int heads, int kv_heads, int head_dim,
                                        int page_size, int table_width, int window, cudaStream_t stream) {
     return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
-                                          scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
+                                          nullptr, scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
                                           table_width, window, stream);
 }
 

@@ -95,7 +95,7 @@ def _library():
         lib = load_library("attention_bf16")
         lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
-        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 8 + [c_float] + [c_int] * 9 + [c_void_p]
+        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
         _lib = lib
     return _lib
@@ -137,12 +137,12 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
         tiles = decode_tiles_per_cta(entries, kv_heads)
         splits = decode_splits(ctx.max_context_len, tiles)
         partials = ctx.workspace.growing("attn.partials", (entries, heads, splits, head_dim + 2), torch.float32)
+        counters = ctx.workspace.zeroed("attn.counters", entries * kv_heads)
         code = _library().me_attention_decode_bf16_tiled(
             q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
-            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), scale, entries, splits, tiles, heads,
-            kv_heads, head_dim, page_size, width, window, stream,
+            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), counters.data_ptr(), scale, entries,
+            splits, tiles, heads, kv_heads, head_dim, page_size, width, window, stream,
         )  # fmt: skip
-        ops._Counter.launches += 1  # the merge kernel; _check counts the first
         ops._check(code, "attention_decode_bf16")
         return
     if tensor_memory_kernel_takes(head_dim, page_size, window, ctx.max_query_len):

@@ -28,10 +28,11 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
     const int begin = min(tid * chunk, vocab), end = min(begin + chunk, vocab);
 
-    // 1. maximum and its lowest index
+    // 1. maximum and its lowest index.  Threads stride through the row together (coalesced
+    //    loads); a thread meets its indices in ascending order, so "greater than" keeps the lowest.
     float best = -INFINITY;
     int best_index = vocab;
-    for (int i = begin; i < end; ++i) {
+    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
         const float v = x[i];
         if (v > best || (best_index == vocab && !(v < best))) { best = v; best_index = i; }
     }

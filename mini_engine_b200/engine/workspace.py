@@ -52,5 +52,17 @@ class Workspace:
         flat = self._flat(name, math.prod(shape), dtype)
         return flat[: math.prod(shape)].view(shape)
 
+    def zeroed(self, name: str, count: int) -> torch.Tensor:
+        """``count`` int32 values that are zero when first handed out.  Kernels that use them
+        (arrival counters) leave them zero again, so they are never cleared between steps."""
+        key = (name, torch.int32)
+        held = self._buffers.get(key)
+        if held is None or held.numel() < count:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow during graph capture")
+            held = torch.zeros(max(count, 1024), dtype=torch.int32, device=self.device)
+            self._buffers[key] = held
+        return held[:count]
+
     def bytes_held(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._buffers.values())
