@@ -40,6 +40,7 @@ struct AttnParams {
     __nv_bfloat16* out;       // [tokens][heads][D]
     float* partials;          // decode: [entries][heads][max_splits][D + 2]
     int* counters;            // decode: [entries][kv_heads] arrival counts, all zero between launches; or null
+    const int* entry_ids;     // the batch entries this launch covers (grid.z of them), or null: all, in order
     float scale_log2;         // scale * log2(e)
     int heads, kv_heads, page_size, table_width, window, max_splits;
     int page_shift;  // log2(page_size) when it is a power of two, else -1
@@ -203,9 +204,10 @@ __global__ void __launch_bounds__(ATTN_THREADS) attention_portions_kernel(AttnPa
     constexpr int PASSES = BLOCK_KEYS / ROWS_PER_PASS;
 
     // Later blocks of a request see more keys: start them first so that the grid's tail is short.
-    const int entry = blockIdx.z, head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
+    const int head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
     pdl_trigger();
     pdl_wait();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.z] : blockIdx.z;
     const int token0 = p.cu_tokens[entry];
     const int new_tokens = p.cu_tokens[entry + 1] - token0;
     if (q_block * BLOCK_M >= new_tokens) return;
@@ -320,9 +322,10 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
     __nv_bfloat16* kv_tiles = q_tile + 16 * D;                       // [4 warps][K | V][KEYS][D]
 
-    const int entry = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+    const int kv_head = blockIdx.y, split = blockIdx.x;
     pdl_trigger();
     pdl_wait();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.z] : blockIdx.z;
     const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int span = p.tiles_per_cta * DECODE_CHUNK;
@@ -510,7 +513,8 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
     pdl_trigger();
     pdl_wait();
     if (item >= items) return;
-    const int entry = item / p.heads, head = item % p.heads;
+    const int listed = item / p.heads, head = item % p.heads;
+    const int entry = p.entry_ids ? p.entry_ids[listed] : listed;
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int span = p.tiles_per_cta * DECODE_CHUNK;
@@ -560,17 +564,20 @@ static bool sizes_ok(int head_dim, int heads, int kv_heads) {
     return (head_dim == 64 || head_dim == 128) && kv_heads > 0 && heads % kv_heads == 0;
 }
 
-// Any mix of portions and single tokens.  grid.x covers the longest portion.
+// Any mix of portions and single tokens.  grid.x covers the longest portion.  `entry_ids` lists
+// the batch entries to run (`entries` of them), or is null for all of them in order; the partial
+// results and counters of the decode kernel are indexed by the entry's number in the batch.
 ME_EXPORT int me_attention_portions_bf16(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                          const int* cu_tokens, const int* context_lens, void* out, float scale,
                                          int entries, int max_new_tokens, int heads, int kv_heads, int head_dim,
-                                         int page_size, int table_width, int window, cudaStream_t stream) {
+                                         int page_size, int table_width, int window, const int* entry_ids,
+                                         cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads)) return ME_ERR_UNSUPPORTED;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
-                 static_cast<__nv_bfloat16*>(out), nullptr, nullptr, scale * LOG2E, heads, kv_heads, page_size,
-                 table_width, window, 0, shift_of(page_size), 1};
+                 static_cast<__nv_bfloat16*>(out), nullptr, nullptr, entry_ids, scale * LOG2E, heads, kv_heads,
+                 page_size, table_width, window, 0, shift_of(page_size), 1};
     return head_dim == 128 ? launch_portions<128>(p, entries, max_new_tokens, stream)
                            : launch_portions<64>(p, entries, max_new_tokens, stream);
 }
@@ -585,14 +592,14 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                                              const int* block_table, const int* cu_tokens, const int* context_lens,
                                              void* out, float* partials, int* counters, float scale, int entries, int max_splits,
                                              int tiles_per_cta, int heads, int kv_heads, int head_dim, int page_size,
-                                             int table_width, int window, cudaStream_t stream) {
+                                             int table_width, int window, const int* entry_ids, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 16 || max_splits < 1) return ME_ERR_UNSUPPORTED;
     if (tiles_per_cta < 1 || tiles_per_cta > MAX_DECODE_TILES) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
                  static_cast<const __nv_bfloat16*>(v_pages), block_table, cu_tokens, context_lens,
-                 static_cast<__nv_bfloat16*>(out), partials, counters, scale * LOG2E, heads, kv_heads, page_size,
-                 table_width, window, max_splits, shift_of(page_size), tiles_per_cta};
+                 static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
+                 page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
 }
 
@@ -603,7 +610,7 @@ ME_EXPORT int me_attention_decode_bf16(const void* q, const void* k_pages, const
                                        int page_size, int table_width, int window, cudaStream_t stream) {
     return me_attention_decode_bf16_tiled(q, k_pages, v_pages, block_table, cu_tokens, context_lens, out, partials,
                                           nullptr, scale, entries, max_splits, 1, heads, kv_heads, head_dim, page_size,
-                                          table_width, window, stream);
+                                          table_width, window, nullptr, stream);
 }
 
 // ------------------------------------------------- decode attention without allocation

@@ -32,7 +32,7 @@ def _tc_library():
         import ctypes
 
         lib = load_library("attention_tcgen05")
-        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p]
+        lib.me_attention_tcgen05.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 7 + [c_void_p, c_void_p]
         lib.me_attention_tcgen05.restype = c_int
         lib.me_attention_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_take_error.restype = c_int
@@ -93,9 +93,9 @@ def _library():
     global _lib
     if _lib is None:
         lib = load_library("attention_bf16")
-        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p]
+        lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
-        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p]
+        lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
         _lib = lib
     return _lib
@@ -123,6 +123,9 @@ def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
 
 
 def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window) -> None:
+    """Attention of the batch's new tokens.  Entries that bring one token take the split decode
+    kernel, the others a portions kernel; a step that holds both kinds is two launches, each over
+    its own list of entries."""
     from mini_engine_b200.csrc import ops
 
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
@@ -132,30 +135,40 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
         raise ops.KernelError("block_table must be contiguous int32")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     page_size, width = k_pages.shape[2], block_table.shape[1]
-    entries = ctx.num_entries
-    if ctx.all_decode and heads // kv_heads <= 16:
-        tiles = decode_tiles_per_cta(entries, kv_heads)
-        splits = decode_splits(ctx.max_context_len, tiles)
-        partials = ctx.workspace.growing("attn.partials", (entries, heads, splits, head_dim + 2), torch.float32)
-        counters = ctx.workspace.zeroed("attn.counters", entries * kv_heads)
-        code = _library().me_attention_decode_bf16_tiled(
-            q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
-            ctx.context_lens.data_ptr(), out.data_ptr(), partials.data_ptr(), counters.data_ptr(), scale, entries,
-            splits, tiles, heads, kv_heads, head_dim, page_size, width, window, stream,
-        )  # fmt: skip
-        ops._check(code, "attention_decode_bf16")
-        return
-    if tensor_memory_kernel_takes(head_dim, page_size, window, ctx.max_query_len):
-        code = _tc_library().me_attention_tcgen05(
-            _query_map(q), _page_map(k_pages), _page_map(v_pages), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
-            ctx.context_lens.data_ptr(), out.data_ptr(), scale, entries, ctx.max_query_len, heads, kv_heads, head_dim,
-            page_size, width, stream,
-        )  # fmt: skip
-        ops._check(code, "attention_tcgen05")
-        return
-    code = _library().me_attention_portions_bf16(
-        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
-        ctx.context_lens.data_ptr(), out.data_ptr(), scale, entries, ctx.max_query_len, heads, kv_heads, head_dim,
-        page_size, width, window, stream,
-    )  # fmt: skip
-    ops._check(code, "attention_portions_bf16")
+    common = (q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
+              ctx.context_lens.data_ptr(), out.data_ptr())  # fmt: skip
+    decode_ok = heads // kv_heads <= 16
+    if ctx.all_decode and decode_ok:
+        launches = [("decode", ctx.num_entries, None, 1)]
+    else:
+        decodes = getattr(ctx, "num_decode_entries", 0) if decode_ok else 0
+        if decodes and decodes < ctx.num_entries:
+            launches = [
+                ("decode", decodes, ctx.decode_entries, 1),
+                ("portions", ctx.num_entries - decodes, ctx.portion_entries, ctx.max_query_len),
+            ]
+        else:
+            launches = [("portions", ctx.num_entries, None, ctx.max_query_len)]
+    for kind, entries, ids, longest in launches:
+        ids_ptr = None if ids is None else ids.data_ptr()
+        if kind == "decode":
+            tiles = decode_tiles_per_cta(entries, kv_heads)
+            splits = decode_splits(ctx.max_context_len, tiles)
+            partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32)
+            counters = ctx.workspace.zeroed("attn.counters", ctx.num_entries * kv_heads)
+            code = _library().me_attention_decode_bf16_tiled(
+                *common, partials.data_ptr(), counters.data_ptr(), scale, entries, splits, tiles, heads, kv_heads,
+                head_dim, page_size, width, window, ids_ptr, stream,
+            )  # fmt: skip
+            ops._check(code, "attention_decode_bf16")
+        elif tensor_memory_kernel_takes(head_dim, page_size, window, longest):
+            code = _tc_library().me_attention_tcgen05(
+                _query_map(q), _page_map(k_pages), _page_map(v_pages), *common[3:], scale, entries, longest, heads,
+                kv_heads, head_dim, page_size, width, ids_ptr, stream,
+            )  # fmt: skip
+            ops._check(code, "attention_tcgen05")
+        else:
+            code = _library().me_attention_portions_bf16(
+                *common, scale, entries, longest, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, stream
+            )
+            ops._check(code, "attention_portions_bf16")

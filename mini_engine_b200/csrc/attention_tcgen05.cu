@@ -42,6 +42,7 @@ struct TcAttnParams {
     const int* block_table;   // [entries][table_width]
     const int* cu_tokens;     // [entries + 1]
     const int* context_lens;  // [entries]
+    const int* entry_ids;     // the batch entries this launch covers (grid.z of them), or null: all
     __nv_bfloat16* out;       // [tokens][heads][128]
     float scale_log2;
     int heads, kv_heads, page_size, table_width;
@@ -75,7 +76,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Later blocks of a request see more keys: start them first.
-    const int entry = blockIdx.z, head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
+    const int head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -97,6 +98,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     pdl_trigger();
     pdl_wait();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.z] : blockIdx.z;
     const int token0 = p.cu_tokens[entry];
     const int new_tokens = p.cu_tokens[entry + 1] - token0;
     const bool has_work = q_block * TC_ROWS < new_tokens;  // uniform for the CTA
@@ -308,7 +310,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const void* map_v, const int* block_table,
                                    const int* cu_tokens, const int* context_lens, void* out, float scale, int entries,
                                    int max_new_tokens, int heads, int kv_heads, int head_dim, int page_size,
-                                   int table_width, cudaStream_t stream) {
+                                   int table_width, const int* entry_ids, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (head_dim != TC_DIM || kv_heads < 1 || heads % kv_heads) return ME_ERR_UNSUPPORTED;
     if (page_size < 8 || page_size > TC_KEYS || TC_KEYS % page_size) return ME_ERR_UNSUPPORTED;
@@ -316,7 +318,7 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     memcpy(&q, map_q, sizeof(q));
     memcpy(&k, map_k, sizeof(k));
     memcpy(&v, map_v, sizeof(v));
-    TcAttnParams p{block_table, cu_tokens, context_lens, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
+    TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
                    heads, kv_heads, page_size, table_width};
     constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256;
     static bool configured = false;

@@ -73,7 +73,7 @@ class ModelRunner:
         # One int32 block holds every index array of a step; two pinned copies alternate so a
         # step never overwrites what an earlier copy may still be reading.
         g, t, b = self.num_groups, self.max_tokens, self.max_entries
-        self._capacity = (3 + g) * t + (4 * b + 1) + t + g * b * self.table_width
+        self._capacity = (3 + g) * t + (5 * b + 1) + t + g * b * self.table_width
         self._host = [torch.empty(self._capacity, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._host_np = [h.numpy() for h in self._host]
         self._device = torch.zeros(self._capacity, dtype=torch.int32, device=self.device)
@@ -170,6 +170,14 @@ class ModelRunner:
             cu[b + 1] = cursor + 1
             ctx_len[b], state[b], fresh[b] = 1, self.spare_slot, 1
             cursor += 1
+        # Entries that bring one token and entries that bring more, for kernels that treat them
+        # differently within one step.
+        all_counts = counts + [1] * (total_entries - real)
+        decode_list = [b for b, n in enumerate(all_counts) if n == 1]
+        portion_list = [b for b, n in enumerate(all_counts) if n > 1]
+        kinds_view, o_kinds = take(total_entries)
+        kinds_view[: len(decode_list)] = decode_list
+        kinds_view[len(decode_list) :] = portion_list
         if want_every_entry:
             wanted_rows = [int(cu[b + 1]) - 1 for b in range(total_entries)]
         rows_view, o_rows = take(len(wanted_rows))
@@ -202,6 +210,9 @@ class ModelRunner:
             page_size=bs,
             workspace=self.workspace,
             all_decode=max_q == 1,
+            num_decode_entries=len(decode_list),
+            decode_entries=at(o_kinds, len(decode_list)),
+            portion_entries=at(o_kinds + len(decode_list), len(portion_list)),
             host={
                 "counts": counts + [1] * (total_entries - real),
                 "starts": [e.start for e in entries] + [0] * (total_entries - real),

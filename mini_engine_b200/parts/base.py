@@ -118,6 +118,9 @@ class StepContext:
     page_size: int = 16
     workspace: "Any" = None  # Workspace: named persistent buffers
     all_decode: bool = False  # every entry brings exactly one token
+    num_decode_entries: int = 0  # entries that bring exactly one token ...
+    decode_entries: torch.Tensor | None = None  # ... their numbers, ascending (int32)
+    portion_entries: torch.Tensor | None = None  # the numbers of the entries that bring more
     host: Mapping[str, Any] = field(default_factory=dict)  # host copies for parts written in Python
     memo: dict = field(default_factory=dict)  # what parts compute once per step and share between layers
 

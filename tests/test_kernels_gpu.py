@@ -347,7 +347,11 @@ def fake_context(data):
     cu = [0]
     for n in news:
         cu.append(cu[-1] + n)
+    ones = [b for b, n in enumerate(news) if n == 1]
+    more = [b for b, n in enumerate(news) if n > 1]
     return SimpleNamespace(
+        num_decode_entries=len(ones), decode_entries=torch.tensor(ones, dtype=torch.int32, device="cuda"),
+        portion_entries=torch.tensor(more, dtype=torch.int32, device="cuda"),
         num_entries=len(news), all_decode=max(news) == 1, max_query_len=max(news), max_context_len=max(lengths),
         cu_tokens=torch.tensor(cu, dtype=torch.int32, device="cuda"),
         context_lens=torch.tensor(lengths, dtype=torch.int32, device="cuda"),
@@ -377,6 +381,7 @@ TENSOR_MEMORY_CASES = [
     ([129, 40], [129, 33], 4, 2, 16),  # a second block of one row; a continuation
     ([700, 64, 300], [700, 64, 45], 8, 2, 8),  # several tiles, small pages, a portion far into its request
     ([1000, 3, 257], [256, 3, 257], 4, 4, 32),  # the last 256 tokens of 1000; a tiny entry in the same launch
+    ([500, 90, 300, 64, 17], [1, 90, 1, 64, 1], 8, 2, 16),  # decoded tokens of some beside portions of others
     ([2048], [2048], 2, 1, 128),  # pages as large as a tile
 ]
 
