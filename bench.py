@@ -252,6 +252,9 @@ def run_ours(args) -> dict:
 
     e2e_value, h2d_bytes, d2h_bytes = time_e2e(args.batch, args.steps, args.warmup)
     device_error = tensor_core.take_error()
+    fp32_check = None
+    if args.fp32_check:
+        fp32_check = check_against_fp32(engine, cfg, random_prompt(args.fp32_check))
 
     achieved_gbs = decode_bytes(cfg, layers, args.batch, CONTEXT + args.warmup + args.steps // 2) / (ms_per_step / 1e3) / 1e9
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
@@ -311,6 +314,43 @@ def run_ours(args) -> dict:
         "points": points,
         "clocks": clock_summary,
         "device_error": device_error,
+        **({"fp32_check": fp32_check} if fp32_check else {}),
+    }
+
+
+def check_against_fp32(engine, cfg, prompt: list[int]) -> dict:
+    """Logits of one prompt from the bfloat16 engine against the true 32-bit path of the same
+    model (the same weights, widened to float32; CUDA-core products, no tensor cores)."""
+    import torch
+
+    from mini_engine_b200.cache.manager import CacheManager
+    from mini_engine_b200.engine.loading import random_model
+    from mini_engine_b200.engine.runner import ModelRunner, StepEntry
+
+    def logits_of(runner, manager) -> "torch.Tensor":
+        cache = manager.new_request()
+        assert manager.try_allocate(cache, len(prompt))
+        out = runner.execute([StepEntry(cache, 0, prompt, tuple(range(len(prompt))))]).float().cpu()
+        manager.free(cache)
+        return out
+
+    low = logits_of(engine.runner, engine.block_manager)
+    pages = -(-len(prompt) // BLOCK_SIZE) + 1
+    began = time.perf_counter()
+    model32 = random_model(cfg, seed=0, dtype=torch.float32, store=torch.bfloat16)
+    runner32 = ModelRunner(model32, dtype=torch.float32, num_blocks=pages, block_size=BLOCK_SIZE, max_num_seqs=1,
+                           max_num_batched_tokens=len(prompt), max_model_len=pages * BLOCK_SIZE)  # fmt: skip
+    manager32 = CacheManager(runner32.layout.groups, pages, BLOCK_SIZE, 1, False)
+    high = logits_of(runner32, manager32)
+    torch.cuda.synchronize()
+    scale = float(high.abs().max())
+    return {
+        "tokens": len(prompt),
+        "max_abs_err": round(float((low - high).abs().max()), 5),
+        "max_abs_logit": round(scale, 4),
+        "rel_err": round(float((low - high).abs().max()) / scale, 5),
+        "argmax_agree": round(float((low.argmax(-1) == high.argmax(-1)).float().mean()), 4),
+        "fp32_seconds": round(time.perf_counter() - began, 1),
     }
 
 
@@ -323,6 +363,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--skip-points", action="store_true", help="do not time batch 1 and 64")
+    parser.add_argument("--fp32-check", type=int, default=0, metavar="TOKENS",
+                        help="also run a prompt of this many tokens through the float32 path and compare logits")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({

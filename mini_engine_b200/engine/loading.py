@@ -23,12 +23,22 @@ def load_model(folder: str | Path, dtype: torch.dtype, device: str = "cuda") -> 
     return arch, config, model
 
 
-def random_model(config: Any, seed: int, dtype: torch.dtype, device: str = "cuda", scale: float = 1.0) -> DecoderModel:
-    """A model with seeded random weights made directly on the device (no folder)."""
+def random_model(
+    config: Any,
+    seed: int,
+    dtype: torch.dtype,
+    device: str = "cuda",
+    scale: float = 1.0,
+    store: torch.dtype | None = None,
+) -> DecoderModel:
+    """A model with seeded random weights made directly on the device (no folder).  ``store`` is
+    the dtype the values are rounded to when they are made (default: the compute dtype); a float32
+    model made with ``store=torch.bfloat16`` holds exactly the bfloat16 model's weights."""
     arch = architecture_for(config.architecture)
     model = DecoderModel(arch.build_spec(config))
     specs = model.weight_specs()
-    store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    if store is None:
+        store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
     tensors = {}
     for spec in specs:  # one tensor at a time keeps the peak at one float32 copy of the largest
         if spec.alias_of is None:
