@@ -214,6 +214,150 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 1) tcgen05_dealloc(tmem_base, C::TMEM_COLUMNS);
 }
 
+// ----------------------------------------------------------- CTA-pair kernel (many tokens)
+
+// For prompts, a pair of CTAs (a cluster of two, on the two SMs of a TPC) computes a tile of 256
+// output features x 256 tokens with cta_group::2 MMAs (M = 256, N = 256).  Each CTA loads its own
+// 128 weight rows and its own 128 of the 256 tokens, i.e. 32 KB per k block instead of the 48 KB
+// that a lone CTA needs for its 128 x 256 tile, so a third less comes out of L2 per flop and six
+// stages fit where four did.  No load is multicast: every CTA fetches its own tiles, and their
+// bytes are counted on the barrier of the pair's rank-0 CTA, which issues the MMAs; its
+// tcgen05.commit arrives on the stage and accumulator barriers of both CTAs.  Each CTA reads its
+// own 128 accumulator rows from its own tensor memory in the epilogue.
+template <bool DUAL>
+struct PairConfig {
+    static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2 * (DUAL ? 2 : 1);
+    static constexpr int B_BYTES = 128 * BLOCK_K * 2;  // this CTA's half of the 256 tokens
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int TMEM_COLUMNS = DUAL ? 512 : 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+constexpr int PAIR_T = 256;
+
+template <bool DUAL>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    using C = PairConfig<DUAL>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* accum = empty + C::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
+    // blockIdx.x = 2 * token tile + rank: the clusters that run together share a weight tile.
+    const int t0 = (blockIdx.x >> 1) * PAIR_T;
+    const int n0 = (blockIdx.y * 2 + rank) * BLOCK_N;
+    const int iterations = p.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc_pair(tmem_holder, C::TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // both CTAs' barriers exist before either signals the other's
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_trigger();
+            const int early = min(iterations, C::STAGES);
+            for (int i = 0; i < early; ++i) {
+                uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
+                if (rank == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);  // the bytes of both CTAs
+                tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[i]);
+                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, t0 + rank * 128, &full[i]);
+            for (int i = early; i < iterations; ++i) {
+                const int stage = i % C::STAGES;
+                if (!mbar_wait(&empty[stage], ((i / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (10 << 8) | stage); break; }
+                uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
+                if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
+                tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
+                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, t0 + rank * 128, &full[stage]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_pair(PAIR_T);
+            bool ok = true;
+            for (int i = 0; i < iterations && ok; ++i) {
+                const int stage = i % C::STAGES;
+                if (!mbar_wait(&full[stage], (i / C::STAGES) & 1)) { atomicCAS(&g_gemm_error, 0, (11 << 8) | stage); ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+                const uint64_t a_desc = smem_desc_sw128(a_addr);
+                const uint64_t b_desc = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t step = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);
+                    const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+                    tcgen05_mma_bf16_pair(tmem_base, a_desc + step, b_desc + step, idesc, accumulate);
+                    if (DUAL) {
+                        const uint64_t a2_desc = smem_desc_sw128(a_addr + BLOCK_N * BLOCK_K * 2);
+                        tcgen05_mma_bf16_pair(tmem_base + PAIR_T, a2_desc + step, b_desc + step, idesc, accumulate);
+                    }
+                }
+                tcgen05_commit_pair(&empty[stage]);
+            }
+            tcgen05_commit_pair(accum);
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;
+        pdl_wait();
+        bool ok = mbar_wait(accum, 0);
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (12 << 8));
+        ok = __all_sync(0xffffffffu, ok) && g_gemm_error == 0;
+        tcgen05_fence_after();
+        if (ok) {
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < PAIR_T; c0 += 16) {
+                if (t0 + c0 >= p.tokens) break;
+                if (!DUAL) {
+                    float v[16];
+                    tcgen05_ld16(lane_base + c0, v);
+                    if (n < p.outs) {
+                        float* out = static_cast<float*>(p.out);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (t0 + c0 + c < p.tokens) out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = v[c];
+                    }
+                } else {
+                    float gate[16], up[16];
+                    tcgen05_ld16(lane_base + c0, gate);
+                    tcgen05_ld16(lane_base + PAIR_T + c0, up);
+                    if (n < p.outs) {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (t0 + c0 + c < p.tokens) {
+                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                                out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
+                            }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // neither CTA leaves while the other may still read its shared or tensor memory
+    if (warp == 1) tcgen05_dealloc_pair(tmem_base, C::TMEM_COLUMNS);
+}
+
 // -------------------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -285,6 +429,56 @@ ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, 
         case 256: return launch<256, false>(w, x, p, splits, stream);
         default: return ME_ERR_ARGUMENT;
     }
+}
+
+
+template <bool DUAL>
+static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+    using C = PairConfig<DUAL>;
+    auto kernel = gemm_tcgen05_pair_kernel<DUAL>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * ((p.tokens + PAIR_T - 1) / PAIR_T), (p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N), 1);
+    config.blockDim = dim3(GEMM_THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, p));
+}
+
+// out[t][n] (float32) = x[t] . w[n] by CTA pairs.  The weight map has boxes of 128 rows, the
+// activation map boxes of 128 rows too (each CTA of a pair loads half of the 256 tokens).
+ME_EXPORT int me_gemm_tcgen05_pair(const void* map_w, const void* map_x, float* out, int tokens, int outs, int inner,
+                                   cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0};
+    return launch_pair<false>(w, x, p, stream);
+}
+
+ME_EXPORT int me_gemm_tcgen05_pair_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,
+                                          int dual_row_offset, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset};
+    return launch_pair<true>(w, x, p, stream);
 }
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.

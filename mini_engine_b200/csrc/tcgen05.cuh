@@ -155,3 +155,55 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+// Two CTAs of a cluster work on one 256-row accumulator tile: each holds its own 128 rows of A
+// and its own half of B in shared memory and its own 128 accumulator rows in tensor memory; the
+// MMAs are issued by the CTA of cluster rank 0 only.  Loads carry no multicast: every CTA
+// fetches its own tiles.
+
+constexpr uint32_t PAIR_LEADER_MASK = 0xFEFFFFFFu;  // clears the bit that tells the pair's CTAs apart
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_alloc_pair(uint32_t* holder, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+// A tile load whose bytes are counted on the barrier of the pair's rank-0 CTA (same offset).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int inner, int row, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(inner), "r"(row), "r"(smem_u32(bar) & PAIR_LEADER_MASK)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+          "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far retire.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+// Instruction descriptor of a pair's MMA: M = 256 (128 rows in each CTA), N = n.
+__host__ __device__ constexpr uint32_t make_idesc_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+}

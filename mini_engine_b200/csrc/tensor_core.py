@@ -8,6 +8,7 @@ live in the engine's persistent workspace.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_uint, c_ulonglong, c_void_p
 
 import torch
@@ -20,6 +21,8 @@ BLOCK_K = 64
 TOKEN_TILES = (16, 32, 64, 128, 256)
 SPLIT_MAX_TOKENS = 64  # products of more tokens have enough tiles without splitting
 MIN_K_BLOCKS_PER_SPLIT = 4
+PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles)
+USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
 
 _lib = None
 
@@ -34,6 +37,10 @@ def _library():
         lib.me_gemm_tcgen05.restype = c_int
         lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_swiglu.restype = c_int
+        lib.me_gemm_tcgen05_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_pair.restype = c_int
+        lib.me_gemm_tcgen05_pair_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_pair_swiglu.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_gemm_take_error.restype = c_int
         _lib = lib
@@ -118,9 +125,14 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
         raise RuntimeError(f"output {tuple(out.shape)} does not fit [{splits}, {tokens}, {plan.rows}] float32")
     tile = token_tile(tokens)
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    code = _library().me_gemm_tcgen05(
-        plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream
-    )
+    if tokens > PAIR_MIN_TOKENS and splits == 1 and USE_PAIRS:
+        code = _library().me_gemm_tcgen05_pair(
+            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream
+        )
+    else:
+        code = _library().me_gemm_tcgen05(
+            plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream
+        )
     _count_launch()
     if code != 0:
         raise RuntimeError(f"tensor-core product failed to launch (code {code})")
@@ -136,11 +148,16 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    tile = 256 if tokens > 128 else 128
-    code = _library().me_gemm_tcgen05_swiglu(
-        plan.map, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, tile,
-        stream,
-    )
+    if tokens > PAIR_MIN_TOKENS and USE_PAIRS:
+        code = _library().me_gemm_tcgen05_pair_swiglu(
+            plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
+        )
+    else:
+        tile = 256 if tokens > 128 else 128
+        code = _library().me_gemm_tcgen05_swiglu(
+            plan.map, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
+            tile, stream,
+        )
     _count_launch()
     if code != 0:
         raise RuntimeError(f"gated tensor-core product failed to launch (code {code})")
