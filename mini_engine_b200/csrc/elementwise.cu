@@ -283,64 +283,77 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
 
 // The same for head_dim == 128: each lane owns four consecutive elements, all partial sums are
 // loaded before they are added, and the rotation partner (64 elements away) is 16 lanes away.
-template <typename OutT>
+// A warp takes HEADS consecutive heads of one token and requests all of them before it uses any:
+// with one partial sum (prompts) four heads per warp keep enough loads in flight to fill HBM.
+template <typename OutT, int HEADS, int MAX_SPLITS>
 __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(QkvArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = a.heads + 2 * a.kv_heads;
+    const int groups = heads_total / HEADS;  // the launcher makes sure this divides
     const long long item = static_cast<long long>(blockIdx.x) * QKV_WARPS + warp;
-    if (item >= static_cast<long long>(a.tokens) * heads_total) return;
-    const int token = static_cast<int>(item / heads_total);
-    const int column_head = static_cast<int>(item % heads_total);
+    if (item >= static_cast<long long>(a.tokens) * groups) return;
+    const int token = static_cast<int>(item / groups);
+    const int first_head = static_cast<int>(item % groups) * HEADS;
     constexpr int D = 128;
     pdl_trigger();
     pdl_wait();
-    const float* src = a.qkv + static_cast<size_t>(token) * heads_total * D + static_cast<size_t>(column_head) * D + lane * 4;
-    float4 part[MAX_UNROLLED_SPLITS];
+    const float* src = a.qkv + static_cast<size_t>(token) * heads_total * D + static_cast<size_t>(first_head) * D + lane * 4;
+    float4 part[HEADS][MAX_SPLITS];
 #pragma unroll
-    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
-        if (s < a.splits) part[s] = *reinterpret_cast<const float4*>(src + s * a.split_stride);
-    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int u = 0; u < HEADS; ++u)
 #pragma unroll
-    for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
-        if (s < a.splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
-    const bool is_q = column_head < a.heads;
-    const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
-    const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
-    if (weight) {
-        float sum_sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
-        sum_sq = warp_sum(sum_sq);
-        const float inv = rsqrtf(sum_sq / static_cast<float>(D) + a.eps);
-        const float4 w = *reinterpret_cast<const float4*>(weight + lane * 4);
-        v = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
-    }
-    if ((is_q || is_k) && a.cos_sin != nullptr) {
-        const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
-                                         __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
+        for (int s = 0; s < MAX_SPLITS; ++s)
+            if (s < a.splits) part[u][s] = *reinterpret_cast<const float4*>(src + u * D + s * a.split_stride);
+    float4 first = make_float4(1.0f, 0.0f, 1.0f, 0.0f), second = first;
+    if (a.cos_sin != nullptr) {
         const float4* angles = reinterpret_cast<const float4*>(a.cos_sin + static_cast<size_t>(token) * (D / 2) + (lane & 15) * 4);
-        const float4 first = angles[0], second = angles[1];  // (cos, sin) of four consecutive frequencies
-        const float sign = lane < 16 ? -1.0f : 1.0f;  // first half: x cos - partner sin; second: x cos + partner sin
-        v.x = v.x * first.x + sign * other.x * first.y;
-        v.y = v.y * first.z + sign * other.y * first.w;
-        v.z = v.z * second.x + sign * other.z * second.y;
-        v.w = v.w * second.z + sign * other.w * second.w;
+        first = angles[0];   // (cos, sin) of four consecutive frequencies
+        second = angles[1];
     }
-    OutT* dst;
-    if (is_q) {
-        dst = static_cast<OutT*>(a.q_out) + (static_cast<size_t>(token) * a.heads + column_head) * D;
-    } else {
-        const int kv_head = is_k ? column_head - a.heads : column_head - a.heads - a.kv_heads;
-        if (a.slot_mapping) {
-            const int slot = a.slot_mapping[token];
-            if (slot < 0) return;
-            const size_t page = slot / a.page_size, offset = slot % a.page_size;
-            OutT* pages = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages);
-            dst = pages + ((page * a.kv_heads + kv_head) * a.page_size + offset) * D;
-        } else {
-            OutT* dense = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense);
-            dst = dense + (static_cast<size_t>(token) * a.kv_heads + kv_head) * D;
+    const int slot = a.slot_mapping ? a.slot_mapping[token] : 0;
+#pragma unroll
+    for (int u = 0; u < HEADS; ++u) {
+        const int column_head = first_head + u;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int s = 0; s < MAX_SPLITS; ++s)
+            if (s < a.splits) { v.x += part[u][s].x; v.y += part[u][s].y; v.z += part[u][s].z; v.w += part[u][s].w; }
+        const bool is_q = column_head < a.heads;
+        const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
+        const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
+        if (weight) {
+            float sum_sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+            sum_sq = warp_sum(sum_sq);
+            const float inv = rsqrtf(sum_sq / static_cast<float>(D) + a.eps);
+            const float4 w = *reinterpret_cast<const float4*>(weight + lane * 4);
+            v = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
         }
+        if ((is_q || is_k) && a.cos_sin != nullptr) {
+            const float4 other = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
+                                             __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
+            const float sign = lane < 16 ? -1.0f : 1.0f;  // first half: x cos - partner sin; second: x cos + partner sin
+            v.x = v.x * first.x + sign * other.x * first.y;
+            v.y = v.y * first.z + sign * other.y * first.w;
+            v.z = v.z * second.x + sign * other.z * second.y;
+            v.w = v.w * second.z + sign * other.w * second.w;
+        }
+        OutT* dst;
+        if (is_q) {
+            dst = static_cast<OutT*>(a.q_out) + (static_cast<size_t>(token) * a.heads + column_head) * D;
+        } else {
+            const int kv_head = is_k ? column_head - a.heads : column_head - a.heads - a.kv_heads;
+            if (a.slot_mapping) {
+                if (slot < 0) continue;
+                const size_t page = slot / a.page_size, offset = slot % a.page_size;
+                OutT* pages = static_cast<OutT*>(is_k ? a.k_pages : a.v_pages);
+                dst = pages + ((page * a.kv_heads + kv_head) * a.page_size + offset) * D;
+            } else {
+                OutT* dense = static_cast<OutT*>(is_k ? a.k_dense : a.v_dense);
+                dst = dense + (static_cast<size_t>(token) * a.kv_heads + kv_head) * D;
+            }
+        }
+        store4(dst + lane * 4, v);
     }
-    store4(dst + lane * 4, v);
 }
 
 // (cos, sin) of position * inv_freq for every token of the step, once per step for all layers
@@ -381,11 +394,20 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
     const bool vec = head_dim == 128 && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
                      aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin);
-    if (out_type == ME_BF16) {
-        if (vec) return launch_kernel(qk_norm_rope_store_128_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, 0, stream, a);
-        return launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, smem, stream, a);
+    if (vec) {
+        // The number of heads per warp depends on the number of partial sums and on the model's
+        // head counts only, never on the batch.
+        const bool four = splits == 1 && (heads + 2 * kv_heads) % 4 == 0;
+        const long long warps = static_cast<long long>(tokens) * ((heads + 2 * kv_heads) / (four ? 4 : 1));
+        const int vec_blocks = static_cast<int>((warps + QKV_WARPS - 1) / QKV_WARPS);
+        if (out_type == ME_BF16)
+            return four ? launch_kernel(qk_norm_rope_store_128_kernel<__nv_bfloat16, 4, 1>, vec_blocks, QKV_WARPS * 32, 0, stream, a)
+                        : launch_kernel(qk_norm_rope_store_128_kernel<__nv_bfloat16, 1, MAX_UNROLLED_SPLITS>, vec_blocks, QKV_WARPS * 32, 0, stream, a);
+        return four ? launch_kernel(qk_norm_rope_store_128_kernel<float, 4, 1>, vec_blocks, QKV_WARPS * 32, 0, stream, a)
+                    : launch_kernel(qk_norm_rope_store_128_kernel<float, 1, MAX_UNROLLED_SPLITS>, vec_blocks, QKV_WARPS * 32, 0, stream, a);
     }
-    if (vec) return launch_kernel(qk_norm_rope_store_128_kernel<float>, blocks, QKV_WARPS * 32, 0, stream, a);
+    if (out_type == ME_BF16)
+        return launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, blocks, QKV_WARPS * 32, smem, stream, a);
     return launch_kernel(qk_norm_rope_store_kernel<float>, blocks, QKV_WARPS * 32, smem, stream, a);
 }
 

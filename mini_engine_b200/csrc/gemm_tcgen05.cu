@@ -62,6 +62,7 @@ struct GemmParams {
     void* out;            // float [splits][tokens][outs], or bfloat16 [tokens][outs] in DUAL mode
     int tokens, outs, k_blocks, k_blocks_per_split;
     int dual_row_offset;  // row of W where the second (up) half starts
+    int token_tiles, full_tiles, tail_parts;  // pair kernel: tiles of 256 tokens; whole ones; cuts of the rest
 };
 
 template <int BLOCK_T, bool DUAL>
@@ -224,6 +225,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // bytes are counted on the barrier of the pair's rank-0 CTA, which issues the MMAs; its
 // tcgen05.commit arrives on the stage and accumulator barriers of both CTAs.  Each CTA reads its
 // own 128 accumulator rows from its own tensor memory in the epilogue.
+//
+// The grid is one-dimensional over tiles (token tiles fastest).  When the number of tiles is not a
+// multiple of the number of SM pairs and the last wave is less than half full, its tiles are cut
+// into 2 or 4 narrower ones (N = 128 or 64 in the instruction descriptor) that run side by side.
 template <bool DUAL>
 struct PairConfig {
     static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2 * (DUAL ? 2 : 1);
@@ -248,9 +253,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
-    // blockIdx.x = 2 * token tile + rank: the clusters that run together share a weight tile.
-    const int t0 = (blockIdx.x >> 1) * PAIR_T;
-    const int n0 = (blockIdx.y * 2 + rank) * BLOCK_N;
+    // blockIdx.x = 2 * cluster + rank; clusters walk the tiles with the token tile fastest, so the
+    // clusters that run together share a weight tile.
+    const int cluster = blockIdx.x >> 1;
+    int tile = cluster, token_offset = 0, width = PAIR_T;
+    if (cluster >= p.full_tiles) {
+        // Part i of a tile cut in `tail_parts`: the 16 units of 16 tokens are shared as evenly as
+        // they divide (3 parts: 96, 80, 80 tokens).
+        const int j = cluster - p.full_tiles;
+        tile = p.full_tiles + j / p.tail_parts;
+        const int part = j % p.tail_parts;
+        const int base = (PAIR_T / 16) / p.tail_parts, extra = (PAIR_T / 16) % p.tail_parts;
+        width = (base + (part < extra ? 1 : 0)) * 16;
+        token_offset = (part * base + min(part, extra)) * 16;
+    }
+    const int t0 = (tile % p.token_tiles) * PAIR_T + token_offset;
+    const int n0 = ((tile / p.token_tiles) * 2 + rank) * BLOCK_N;
+    const int b_row = t0 + rank * (width / 2);  // this CTA's half of the tile's tokens
     const int iterations = p.k_blocks;
 
     if (threadIdx.x == 0) {
@@ -277,7 +296,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             }
             pdl_wait();
             for (int i = 0; i < early; ++i)
-                tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, t0 + rank * 128, &full[i]);
+                tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, b_row, &full[i]);
             for (int i = early; i < iterations; ++i) {
                 const int stage = i % C::STAGES;
                 if (!mbar_wait(&empty[stage], ((i / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (10 << 8) | stage); break; }
@@ -285,12 +304,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
                 tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
                 if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
-                tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, t0 + rank * 128, &full[stage]);
+                tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, b_row, &full[stage]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_pair(PAIR_T);
+            const uint32_t idesc = make_idesc_pair(width);
             bool ok = true;
             for (int i = 0; i < iterations && ok; ++i) {
                 const int stage = i % C::STAGES;
@@ -324,7 +343,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         if (ok) {
             const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < PAIR_T; c0 += 16) {
+            for (int c0 = 0; c0 < width; c0 += 16) {
                 if (t0 + c0 >= p.tokens) break;
                 if (!DUAL) {
                     float v[16];
@@ -417,7 +436,7 @@ ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, 
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0};
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1};
     if (splits < 1 || splits > p.k_blocks) return ME_ERR_ARGUMENT;
     p.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
     if ((splits - 1) * p.k_blocks_per_split >= p.k_blocks) return ME_ERR_ARGUMENT;  // an empty split
@@ -442,8 +461,24 @@ static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    GemmParams q = p;
+    q.token_tiles = (p.tokens + PAIR_T - 1) / PAIR_T;
+    const int tiles = q.token_tiles * ((p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N));
+    const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+    q.full_tiles = tiles / pairs * pairs;
+    // A narrow tile still streams its whole weight tile, so it costs well over its share of a full
+    // tile's time; cutting pays only when the last wave is so empty that two or four parts of every
+    // tile in it run side by side (measured: 6 % on the gate-up product of a 2,048-token prompt;
+    // cutting a half-full wave in three or four made the products 20-60 % slower).
+    q.tail_parts = 1;
+    while (q.tail_parts < 4 && (tiles - q.full_tiles) * q.tail_parts * 2 <= pairs) q.tail_parts *= 2;
+    if (tiles < pairs) { q.full_tiles = tiles; q.tail_parts = 1; }  // a single, partly filled wave: nothing to gain
+    const int clusters = q.full_tiles + (tiles - q.full_tiles) * q.tail_parts;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(2 * ((p.tokens + PAIR_T - 1) / PAIR_T), (p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N), 1);
+    config.gridDim = dim3(2 * clusters, 1, 1);
     config.blockDim = dim3(GEMM_THREADS);
     config.dynamicSmemBytes = C::SMEM_BYTES;
     config.stream = stream;
@@ -456,7 +491,7 @@ static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
-    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, p));
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, q));
 }
 
 // out[t][n] (float32) = x[t] . w[n] by CTA pairs.  The weight map has boxes of 128 rows, the
@@ -467,7 +502,7 @@ ME_EXPORT int me_gemm_tcgen05_pair(const void* map_w, const void* map_x, float* 
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0};
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1};
     return launch_pair<false>(w, x, p, stream);
 }
 
@@ -477,7 +512,7 @@ ME_EXPORT int me_gemm_tcgen05_pair_swiglu(const void* map_w, const void* map_x, 
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset};
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
     return launch_pair<true>(w, x, p, stream);
 }
 
@@ -488,7 +523,7 @@ ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void*
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset};
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
     p.k_blocks_per_split = p.k_blocks;
     if (block_t == 256) return launch<256, true>(w, x, p, 1, stream);  // both accumulators fill all 512 TMEM columns
     if (block_t == 128) return launch<128, true>(w, x, p, 1, stream);

@@ -56,6 +56,9 @@ TC_SHAPES = [
     (100, 256, 256),
     (300, 520, 1160),  # token tile 256 with a ragged second tile
     (700, 130, 72),
+    # CTA pairs with a partly filled last wave: its tiles are cut in two (88 tiles) and in four (82)
+    (2048, 2600, 128),
+    (512, 10496, 72),
 ]
 
 
@@ -92,7 +95,7 @@ def test_gemm_tensor_core_finds_one_large_product():
         assert int(out[0].argmax()) == t * outs + n
 
 
-@pytest.mark.parametrize("tokens,inter,inner", [(65, 160, 96), (128, 128, 64), (300, 300, 264)])
+@pytest.mark.parametrize("tokens,inter,inner", [(65, 160, 96), (128, 128, 64), (300, 300, 264), (2048, 2600, 136)])
 def test_gemm_tensor_core_swiglu(tokens, inter, inner):
     from mini_engine_b200.csrc import tensor_core
 
