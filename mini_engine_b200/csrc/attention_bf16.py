@@ -105,17 +105,16 @@ def supports(head_dim: int, heads: int, kv_heads: int) -> bool:
     return head_dim in (64, 128) and kv_heads > 0 and heads % kv_heads == 0
 
 
-def decode_tiles_per_cta(entries: int, kv_heads: int) -> int:
-    """Consecutive 128-key tiles that one CTA walks.  With few (request, KV head) pairs every
-    tile is a CTA of its own, so that all SMs have work; with many, a CTA walks several tiles
-    and pays its start-up once.  The choice changes how partial results are grouped, hence the
-    result in its last bits, never which keys are read."""
-    pairs = entries * kv_heads
-    if pairs <= 128:
-        return 1
-    if pairs <= 256:
-        return 2
-    return 4
+RESIDENT_DECODE_CTAS = 3 * 148  # three CTAs of the decode kernel fit an SM
+
+
+def decode_tiles_per_cta(entries: int, kv_heads: int, max_context_len: int) -> int:
+    """Consecutive 128-key tiles that one CTA walks (1 to 8): as few CTAs as cover the longest
+    context the launch may meet in one resident wave, so that every CTA pays its start-up once and
+    keeps loads in flight from tile to tile.  The choice changes how partial results are grouped,
+    hence the result in its last bits, never which keys are read."""
+    tiles = entries * kv_heads * max(1, -(-max_context_len // DECODE_CHUNK))
+    return max(1, min(8, -(-tiles // RESIDENT_DECODE_CTAS)))
 
 
 def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
@@ -152,7 +151,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     for kind, entries, ids, longest in launches:
         ids_ptr = None if ids is None else ids.data_ptr()
         if kind == "decode":
-            tiles = decode_tiles_per_cta(entries, kv_heads)
+            tiles = decode_tiles_per_cta(entries, kv_heads, ctx.max_context_len)
             splits = decode_splits(ctx.max_context_len, tiles)
             partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32)
             counters = ctx.workspace.zeroed("attn.counters", ctx.num_entries * kv_heads)
