@@ -41,7 +41,7 @@ def make_model_folder(tmp_path_factory, name: str, seed: int, dtype=torch.float3
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """Tiny A and B with the nominal init (N(0, 0.02) matrices), float32 storage."""
-    return {name: make_model_folder(tmp_path_factory, name, seed=11) for name in ("A", "B", "C")}
+    return {name: make_model_folder(tmp_path_factory, name, seed=11) for name in ("A", "B", "C", "D")}
 
 
 @pytest.fixture(scope="session")

@@ -27,7 +27,8 @@ pytestmark = pytest.mark.gpu
 # activations to 8 mantissa bits between kernels, a few times per layer.
 TOLERANCE = {"float32": 1e-4, "bfloat16": 4e-2}
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
-LENGTHS = {"A": [70, 45, 133, 64, 97, 33], "B": [41, 150, 9, 88, 120, 65], "C": [300, 64, 129, 17, 257, 80]}
+LENGTHS = {"A": [70, 45, 133, 64, 97, 33], "B": [41, 150, 9, 88, 120, 65], "C": [300, 64, 129, 17, 257, 80],
+           "D": [200, 33, 150, 64, 97, 260]}
 
 
 def requests_for(name: str, vocab: int) -> dict[str, list[int]]:
@@ -69,7 +70,7 @@ def compare(got, expected, requests, tolerance):
 
 
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("schedule", ["whole", "tail_one_by_one", "changing_portions", "mixed"])
 def test_schedules_match_plain(name, dtype_name, schedule, model_folders):
     folder = model_folders[name]

@@ -61,8 +61,27 @@ TINY_C = {
     "max_position_embeddings": 2048,
     "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# A fourth size with head_dim 128 and a feed-forward width that is a multiple of 128: the sizes
+# at which the tcgen05 attention kernel runs and at which decode steps let the QKV and gate-up
+# products do their consumers' work (norm, rotation and cache write; the SwiGLU gate).
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 2,
+    "hidden_size": 192,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "head_dim": 128,
+    "intermediate_size": 384,
+    "vocab_size": 300,
+    "rope_theta": 20000.0,
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True,
+    "max_position_embeddings": 2048,
+    "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def random_ids(seed: int, count: int, vocab: int) -> list[int]:
