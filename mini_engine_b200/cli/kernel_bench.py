@@ -21,12 +21,28 @@ from types import SimpleNamespace
 import torch
 
 
+GRAPH = False  # set by --graph: launches are captured into one CUDA graph and replayed
+
+
 def timed(run, iters: int, warmup: int = 3) -> float:
-    """Milliseconds per call of ``run(i)``, device time."""
+    """Milliseconds per call of ``run(i)``, device time.  A kernel of a few microseconds is
+    launched faster by a graph than by this Python loop; use --graph for those."""
     for i in range(warmup):
         run(i)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                run(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / iters
     start.record()
     for i in range(iters):
         run(i)
@@ -120,7 +136,10 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--head-dim", type=int, default=128)
     parser.add_argument("--page", type=int, default=16)
     parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph")
     args = parser.parse_args(argv)
+    global GRAPH
+    GRAPH = args.graph
     if args.kernel in ("gemm", "swiglu-gemm"):
         bench_gemm(args, gated=args.kernel == "swiglu-gemm")
     else:

@@ -23,7 +23,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
 sys.path.insert(0, str(HERE.parent.parent))
-sys.path.insert(0, os.environ.get("MINI_ENGINE_REF", "/root/reference/src"))
+if "MINI_ENGINE_REF" not in os.environ:
+    sys.exit("set MINI_ENGINE_REF to the src folder of a YuvGev00/mini-engine checkout")
+sys.path.insert(0, os.environ["MINI_ENGINE_REF"])
 
 from tiny_configs import CONFIGS, PAGE_SIZE, random_ids  # noqa: E402
 

@@ -61,9 +61,9 @@ TINY_C = {
     "max_position_embeddings": 2048,
     "hidden_act": "silu",
 }
-# A fourth size with head_dim 128 and a feed-forward width that is a multiple of 128: the sizes
-# at which the tcgen05 attention kernel runs and at which decode steps let the QKV and gate-up
-# products do their consumers' work (norm, rotation and cache write; the SwiGLU gate).
+# A fourth size with head_dim 128, the size at which the tcgen05 attention kernel and the
+# vector paths of the q/k norm + rotation kernel run, one KV head for four query heads, and
+# pages of 32 tokens.
 TINY_D = {
     "architectures": ["Qwen3ForCausalLM"],
     "model_type": "qwen3",
