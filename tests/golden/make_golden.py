@@ -33,7 +33,7 @@ from mini_engine_b200.config import Qwen3Config  # noqa: E402
 from mini_engine_b200.weights import write_random_model  # noqa: E402
 
 GOLDEN_SEED = 7
-GOLDEN_LEN = {"A": 33, "B": 41}
+GOLDEN_LEN = {"A": 33, "B": 41, "C": 50, "D": 37}
 
 
 def main() -> None:

@@ -13,10 +13,10 @@ from tiny_configs import CONFIGS, random_ids
 
 GOLDEN = Path(__file__).parent / "golden"
 GOLDEN_SEED = 7
-GOLDEN_LEN = {"A": 33, "B": 41}
+GOLDEN_LEN = {"A": 33, "B": 41, "C": 50, "D": 37}
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_plain_matches_reference_model_code(name, tmp_path_factory):
     """tests/golden/make_golden.py ran YuvGev00/mini-engine's model on CPU in float32."""
     folder = make_model_folder(tmp_path_factory, name, seed=GOLDEN_SEED)
