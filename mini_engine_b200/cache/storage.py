@@ -58,6 +58,38 @@ def group_names(specs: list[PagedCacheSpec]) -> list[GroupSpec]:
     ]
 
 
+def bytes_per_token(
+    needs: list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]], dtype: torch.dtype
+) -> int:
+    """Bytes of keys and values that one token occupies over all order entries that own a cache."""
+    element = torch.empty((), dtype=dtype).element_size()
+    return sum(
+        2 * paged.kv_heads * paged.head_dim * element
+        for paged, _state, cache_of in needs
+        if paged is not None and cache_of is None
+    )
+
+
+def blocks_for_budget(
+    needs: list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]],
+    dtype: torch.dtype,
+    block_size: int,
+    budget_bytes: int,
+) -> int:
+    """Pages per group that ``budget_bytes`` of device memory hold (every group gets the same
+    number of pages, and one spare page each is paid for first)."""
+    per_page = bytes_per_token(needs, dtype) * block_size
+    if per_page == 0:
+        return 1
+    blocks = budget_bytes // per_page - 1
+    if blocks < 1:
+        raise ValueError(
+            f"{budget_bytes} bytes hold no KV page of {per_page} bytes (plus the spare page): "
+            "raise kv_memory_fraction or lower block_size"
+        )
+    return int(blocks)
+
+
 def allocate_cache(
     needs: list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]],
     num_blocks: int,

@@ -35,6 +35,8 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--num-blocks", type=int, default=128)
+    parser.add_argument("--kv-memory-fraction", type=float, default=None,
+                        help="size the KV pool as this fraction of free device memory instead of --num-blocks")
     parser.add_argument("--max-num-seqs", type=int, default=16)
     parser.add_argument("--max-num-batched-tokens", type=int, default=2048)
     parser.add_argument("--max-model-len", type=int, default=4096)
@@ -59,7 +61,7 @@ def main(argv: list[str] | None = None) -> int:
         block_size=args.block_size, num_blocks=args.num_blocks, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
         enable_prefix_caching=not args.no_prefix_cache, dtype=dtype, seed=args.seed,
-        cuda_graphs=not args.no_cuda_graphs,
+        cuda_graphs=not args.no_cuda_graphs, kv_memory_fraction=args.kv_memory_fraction,
     )  # fmt: skip
     scratch = None
     folder = args.model

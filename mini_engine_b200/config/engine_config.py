@@ -23,6 +23,9 @@ class EngineConfig:
     dtype: torch.dtype = torch.float32  # torch.float32 or torch.bfloat16
     seed: int = 0  # seed of temperature sampling
     cuda_graphs: bool = True  # replay captured graphs for decode-only steps
+    # When set (0 < f <= 1), num_blocks is ignored and the pool takes this fraction of the device
+    # memory that is free after the weights are loaded.  The reference sizes by num_blocks only.
+    kv_memory_fraction: float | None = None
 
     def __post_init__(self) -> None:
         if self.dtype not in (torch.float32, torch.bfloat16):
@@ -30,3 +33,5 @@ class EngineConfig:
         for name in ("block_size", "num_blocks", "max_num_seqs", "max_num_batched_tokens", "max_model_len"):
             if getattr(self, name) < 1:
                 raise ValueError(f"{name} must be positive")
+        if self.kv_memory_fraction is not None and not 0.0 < self.kv_memory_fraction <= 1.0:
+            raise ValueError("kv_memory_fraction must lie in (0, 1]")

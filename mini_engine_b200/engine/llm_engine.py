@@ -8,6 +8,7 @@ tokenisation is the caller's business.
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Iterable
@@ -15,6 +16,7 @@ from typing import Any, Iterable
 import torch
 
 from mini_engine_b200.cache.manager import CacheManager
+from mini_engine_b200.cache.storage import blocks_for_budget
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.engine.graphs import DecodeGraphs
 from mini_engine_b200.engine.loading import load_model, random_model
@@ -44,6 +46,12 @@ def kv_cache_bytes_per_token(runner: ModelRunner) -> int:
 
 class LLMEngine:
     def __init__(self, model: DecoderModel, config: EngineConfig, eos_token_ids: Iterable[int] = ()):
+        if config.kv_memory_fraction is not None:
+            free_bytes, _total = torch.cuda.mem_get_info()
+            blocks = blocks_for_budget(
+                model.cache_needs(), config.dtype, config.block_size, int(free_bytes * config.kv_memory_fraction)
+            )
+            config = dataclasses.replace(config, num_blocks=blocks)
         self.config = config
         self.model = model
         self.runner = ModelRunner(

@@ -177,3 +177,23 @@ def test_random_orders_lose_no_page(seed):
         mgr.free(item["req"])
     mgr.check_invariants([])
     assert all(pool.num_free == 12 for pool in mgr.pools)
+
+
+def test_pages_that_a_memory_budget_holds():
+    import torch
+
+    from mini_engine_b200.cache.storage import blocks_for_budget, bytes_per_token
+    from mini_engine_b200.parts.base import PagedCacheSpec, StateSpec
+
+    full, window = PagedCacheSpec(2, 16), PagedCacheSpec(4, 32, window=8)
+    # three owners and one entry that reads the first entry's cache (it holds nothing itself)
+    needs = [(full, None, None), (window, None, None), (full, None, 0), (None, StateSpec((4,)), None), (full, None, None)]
+    per_token = 2 * (2 * 16 + 4 * 32 + 2 * 16)
+    assert bytes_per_token(needs, torch.bfloat16) == per_token * 2
+    assert bytes_per_token(needs, torch.float32) == per_token * 4
+    page = per_token * 2 * 8
+    assert blocks_for_budget(needs, torch.bfloat16, 8, 10 * page) == 9  # one page is the spare
+    assert blocks_for_budget(needs, torch.bfloat16, 8, 10 * page + page - 1) == 9
+    with pytest.raises(ValueError, match="hold no KV page"):
+        blocks_for_budget(needs, torch.bfloat16, 8, 2 * page - 1)
+    assert blocks_for_budget([(None, StateSpec((4,)), None)], torch.float32, 8, 0) == 1

@@ -177,3 +177,20 @@ def test_command_line(peaked_model_folders):
         capture_output=True, text=True, timeout=600,
     )  # fmt: skip
     assert refused.returncode == 2 and "CUDA only" in refused.stderr
+
+
+def test_pool_sized_from_free_memory(peaked_model_folders):
+    """``kv_memory_fraction`` replaces ``num_blocks``: the pool takes that share of what is free."""
+    from mini_engine_b200 import SamplingParams
+    from mini_engine_b200.engine.llm_engine import kv_cache_bytes_per_token
+
+    folder = peaked_model_folders["A"]
+    free_before, _ = torch.cuda.mem_get_info()
+    engine = engine_for(folder, "A", num_blocks=3, kv_memory_fraction=0.001)
+    blocks = engine.config.num_blocks
+    page_bytes = kv_cache_bytes_per_token(engine.runner) * PAGE_SIZE["A"]
+    assert blocks == engine.block_manager.num_free_blocks != 3
+    assert 0.5 * 0.001 * free_before <= (blocks + 1) * page_bytes <= 0.001 * free_before
+    _, cfg = load_plain(folder)
+    prompts = [random_ids(900, 21, cfg["vocab"])]
+    assert_same_tokens(engine.generate(prompts, SamplingParams(max_tokens=4)), plain_greedy(folder, prompts, 4))
