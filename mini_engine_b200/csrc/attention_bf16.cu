@@ -21,7 +21,9 @@
 // Pages are [page][kv_head][slot][head_dim]; a key's address comes from the request's block
 // table, so any page size works.  Keys outside the visible range are zero-filled in shared
 // memory (never read from the cache), so stale contents of reused pages cannot leak.
-#include "common.cuh"
+#include <string.h>
+
+#include "tcgen05.cuh"
 
 constexpr int BLOCK_M = 64;   // query rows per CTA (portions)
 constexpr int BLOCK_KEYS = 64;  // keys per tile
@@ -477,26 +479,50 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
 }
 
 // One warp merges the partials of one (entry, head) in ascending order of their keys and writes
-// the head's output.  Each lane owns D / 32 output elements.
+// the head's output.  Each lane owns D / 32 output elements.  Partials are taken eight at a time,
+// all of a batch's loads in flight together; between batches the running maximum rescales what
+// has been summed.
 template <int D>
 __device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int head, int first, int last, int lane) {
     constexpr int STRIDE = D + 2;
     constexpr int PER_LANE = D / 32;
+    constexpr int BATCH = 8;
     const float* base = p.partials + (static_cast<size_t>(entry) * p.heads + head) * p.max_splits * STRIDE;
-    float total_max = -INFINITY;
-    for (int s = first + lane; s <= last; s += 32) total_max = fmaxf(total_max, __ldcg(base + s * STRIDE + D));
-    total_max = warp_max(total_max);
-    float value[PER_LANE], denom = 0.0f;
+    float value[PER_LANE], denom = 0.0f, total_max = -INFINITY;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) value[i] = 0.0f;
-#pragma unroll 4
-    for (int s = first; s <= last; ++s) {
-        const float m = __ldcg(base + s * STRIDE + D);
-        if (m == -INFINITY) continue;
-        const float weight = exp2f(m - total_max);
-        denom += __ldcg(base + s * STRIDE + D + 1) * weight;
+    for (int s0 = first; s0 <= last; s0 += BATCH) {
+        float m[BATCH], l[BATCH];
+        float2 v[BATCH][PER_LANE / 2];
 #pragma unroll
-        for (int i = 0; i < PER_LANE; ++i) value[i] += __ldcg(base + s * STRIDE + lane * PER_LANE + i) * weight;
+        for (int j = 0; j < BATCH; ++j) {
+            const float* part = base + min(s0 + j, last) * STRIDE;
+            const float2 tail = __ldcg(reinterpret_cast<const float2*>(part + D));
+            m[j] = s0 + j <= last ? tail.x : -INFINITY;
+            l[j] = tail.y;
+#pragma unroll
+            for (int i = 0; i < PER_LANE / 2; ++i) v[j][i] = __ldcg(reinterpret_cast<const float2*>(part + lane * PER_LANE) + i);
+        }
+        float batch_max = m[0];
+#pragma unroll
+        for (int j = 1; j < BATCH; ++j) batch_max = fmaxf(batch_max, m[j]);
+        if (batch_max == -INFINITY) continue;
+        const float new_max = fmaxf(total_max, batch_max);
+        const float keep = exp2f(total_max - new_max);  // 0 while nothing has been summed
+        total_max = new_max;
+        denom *= keep;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) value[i] *= keep;
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j) {
+            const float weight = m[j] == -INFINITY ? 0.0f : exp2f(m[j] - new_max);
+            denom += l[j] * weight;
+#pragma unroll
+            for (int i = 0; i < PER_LANE / 2; ++i) {
+                value[2 * i] += v[j][i].x * weight;
+                value[2 * i + 1] += v[j][i].y * weight;
+            }
+        }
     }
     const int token = p.cu_tokens[entry];
     __nv_bfloat16* dst = p.out + (static_cast<size_t>(token) * p.heads + head) * D + lane * PER_LANE;
@@ -519,6 +545,323 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int span = p.tiles_per_cta * DECODE_CHUNK;
     merge_head<D>(p, entry, head, lowest / span, position / span, lane);
+}
+
+// ------------------------------------------------- decode kernel with TMA page loads
+//
+// grid (splits, kv_heads, entries).  The 128-key tiles that a request's query can see are divided
+// evenly among the `splits` CTAs of its (request, KV head): the division depends on the request's
+// own length (at least two tiles per CTA; CTAs left without tiles exit), so every CTA of a
+// request has the same work whatever the longest request of the batch is, and `splits` is chosen
+// from the batch size alone.  Built for few instructions per key:
+// eight warps of 16 keys each; a warp's keys and values arrive as TMA boxes of whole page rows in
+// the 128-byte swizzle, one mbarrier each for K and V; the products are transposed so that the 16
+// rows of an mma tile are keys or head dimensions, never padding:
+//     S^T [16 keys x 8 heads] = K [16 x D] Q^T [D x 8]
+//     O^T [D x 8 heads]      += V^T [D x 16 keys] P^T [16 x 8]
+// P^T's B fragments come from S^T's accumulators through movmatrix.  Groups of up to 8 query
+// heads, pages of a power of two >= 8 keys.  Rows of V outside the visible range are zeroed in
+// shared memory before the second product, so what a reused page still holds there cannot leak.
+// With one split the CTA writes the output itself; else partials as in the kernel above.
+constexpr int TMA_DECODE_WARPS = 8;
+constexpr int TMA_DECODE_THREADS = TMA_DECODE_WARPS * 32;
+constexpr int TMA_WARP_KEYS = 16;
+constexpr int TMA_MIN_TILES = 2;  // a CTA takes at least this many tiles: a partial more costs more than a tile
+
+__device__ int g_decode_error = 0;
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+template <int D>
+constexpr int tma_decode_smem_bytes() {
+    return 1024 + TMA_DECODE_WARPS * 2 * (D / 64) * TMA_WARP_KEYS * 128 + 8 * D * 2 + TMA_DECODE_WARPS * 2 * 8;
+}
+
+template <int D>
+__global__ void __launch_bounds__(TMA_DECODE_THREADS, 3)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                            AttnParams p) {
+    extern __shared__ uint8_t raw_smem[];
+    constexpr int HALVES = D / 64;                         // 64-element (128-byte) column blocks of a row
+    constexpr int HALF_BYTES = TMA_WARP_KEYS * 128;        // one column block of a warp's 16 keys
+    constexpr int OPERAND_BYTES = HALVES * HALF_BYTES;     // a warp's K (or V) tile
+    constexpr int STRIDE = D + 2;
+    static_assert(8 * STRIDE * 4 <= 2 * OPERAND_BYTES, "a warp's partial must fit its tiles");
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem + TMA_DECODE_WARPS * 2 * OPERAND_BYTES);  // [8][D]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(q_tile + 8 * D);
+
+    const int kv_head = blockIdx.y, split = blockIdx.x, splits = gridDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* k_tile = smem + warp * 2 * OPERAND_BYTES;
+    uint8_t* v_tile = k_tile + OPERAND_BYTES;
+    uint64_t* k_bar = bars + warp * 2;
+    uint64_t* v_bar = k_bar + 1;
+    if (lane == 0) {
+        mbar_init(k_bar, 1);
+        mbar_init(v_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // The batch's description (entry list, block table, lengths) was written before the step's
+    // first kernel started, so it is read ahead of the wait for the previous kernel; only the
+    // queries and the newest keys and values come from that kernel.
+    pdl_trigger();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.z] : blockIdx.z;
+    const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+    const int position = p.context_lens[entry] - 1;  // the query's position; it sees keys <= position
+    const int token = p.cu_tokens[entry];
+    const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
+    const int group = p.heads / p.kv_heads;
+    // This CTA's tiles [tile, tile_end) among the request's visible ones.
+    const int lowest_tile = lowest / DECODE_CHUNK, tile_count = position / DECODE_CHUNK - lowest_tile + 1;
+    const int per_cta = max((tile_count + splits - 1) / splits, TMA_MIN_TILES);
+    const int active = (tile_count + per_cta - 1) / per_cta;  // CTAs of this (request, KV head) with work
+    int tile = lowest_tile + split * per_cta;
+    const int tile_end = min(tile + per_cta, lowest_tile + tile_count);
+
+    // Lane j holds the page of box j of a run of tiles of this warp: box = (tile, half of the 16
+    // keys when pages hold 8).  The run is renewed when the walk leaves it.
+    const int box_rows = min(p.page_size, TMA_WARP_KEYS);
+    const int boxes = TMA_WARP_KEYS / box_rows;  // 1 or 2
+    const int run_tiles = 32 / boxes;
+    int run_start = tile, my_page = -1;
+    auto load_pages = [&]() {
+        const int mine = run_start + lane / boxes;
+        const int index = (mine * DECODE_CHUNK + warp * TMA_WARP_KEYS + (lane % boxes) * box_rows) >> p.page_shift;
+        my_page = mine < tile_end && index < p.table_width ? table[index] : -1;
+    };
+    if (split < active) load_pages();
+    __syncwarp();  // the warp's barriers are initialised
+    pdl_wait();
+    if (split >= active) return;
+
+    auto first_key_of = [&](int t) { return t * DECODE_CHUNK + warp * TMA_WARP_KEYS; };
+    auto visible = [&](int t) {  // this warp's 16 keys of tile t hold something the query sees
+        const int first = first_key_of(t);
+        return t < tile_end && first <= position && first + TMA_WARP_KEYS > lowest;
+    };
+    // Lanes 0 .. boxes * HALVES - 1 each fetch one box of a tile: `box_rows` rows of 64 elements.
+    auto issue = [&](int t, uint8_t* dst, const CUtensorMap* map, uint64_t* bar) {
+        if (t - run_start >= run_tiles) {
+            run_start = t;
+            load_pages();
+        }
+        const int box = lane / HALVES, half = lane % HALVES;
+        const int first = first_key_of(t) + box * box_rows;
+        const int page = __shfl_sync(0xffffffffu, my_page, (t - run_start) * boxes + (box < boxes ? box : 0));
+        const bool wanted = lane < boxes * HALVES && page >= 0 && first <= position && first + box_rows > lowest;
+        const uint32_t count = __popc(__ballot_sync(0xffffffffu, wanted));
+        if (lane == 0) mbar_expect_tx(bar, count * box_rows * 128);
+        __syncwarp();
+        if (wanted) {
+            const int row = (page * p.kv_heads + kv_head) * p.page_size + (first & (p.page_size - 1));
+            tma_load_2d(dst + half * HALF_BYTES + box * box_rows * 128, map, half * 64, row, bar);
+        }
+    };
+    while (tile < tile_end && !visible(tile)) ++tile;  // a window may start inside the first tile
+    if (tile < tile_end) {
+        issue(tile, k_tile, &k_map, k_bar);
+        issue(tile, v_tile, &v_map, v_bar);
+    }
+
+    // Queries of the group: rows beyond it are zero.
+    for (int idx = threadIdx.x; idx < 8 * (D / 8); idx += TMA_DECODE_THREADS) {
+        const int row = idx / (D / 8), chunk = idx % (D / 8);
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (row < group)
+            value = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(token) * p.heads + kv_head * group + row) * D + chunk * 8);
+        *reinterpret_cast<uint4*>(q_tile + swizzled<D>(row, chunk) * 8) = value;
+    }
+    __syncthreads();
+
+    uint32_t q_frag[D / 16][2];  // B fragments of Q^T: [k = 16 elements][n = 8 heads]
+#pragma unroll
+    for (int kk = 0; kk < D / 16; kk += 2) {
+        uint32_t r[4];
+        ldmatrix_x4(r, q_tile + swizzled<D>(lane & 7, kk * 2 + (lane >> 3)) * 8);
+        q_frag[kk][0] = r[0], q_frag[kk][1] = r[1], q_frag[kk + 1][0] = r[2], q_frag[kk + 1][1] = r[3];
+    }
+
+    float acc[D / 16][4];  // O^T: rows 16 i + lane / 4 (+ 8), heads 2 (lane % 4) (+ 1)
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};  // of heads 2 (lane % 4) and + 1
+    uint32_t phase = 0;
+    bool failed = false;
+
+    // ldmatrix addresses inside a tile: row r, 16-byte chunk c of column block h live at
+    // h * HALF_BYTES + r * 128 + ((c ^ (r & 7)) << 4).
+    const int k_row = lane & 15, k_hi = lane >> 4;
+    const int v_row = (lane & 7) + ((lane >> 4) << 3), v_hi = (lane >> 3) & 1;
+#pragma unroll 1
+    for (; visible(tile); ++tile) {
+        const bool more = visible(tile + 1);
+        const int first_key = first_key_of(tile);
+        if (!__all_sync(0xffffffffu, mbar_wait(k_bar, phase))) {
+            failed = true;
+            break;
+        }
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t a[4];
+            const int chunk = kk * 2 + k_hi;
+            ldmatrix_x4(a, k_tile + (chunk >> 3) * HALF_BYTES + k_row * 128 + (((chunk & 7) ^ (k_row & 7)) << 4));
+            mma_bf16(s, a, q_frag[kk][0], q_frag[kk][1]);
+        }
+        __syncwarp();  // every lane has read the keys: the next tile's keys may overwrite them
+        if (more) issue(tile + 1, k_tile, &k_map, k_bar);
+
+        // Online softmax over the 16 keys, per head column.
+        const int key0 = first_key + (lane >> 2);
+        const bool seen0 = key0 <= position && key0 >= lowest, seen1 = key0 + 8 <= position && key0 + 8 >= lowest;
+        float rescale[2];
+        uint32_t packed[2];
+        {
+            float prob[4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float a = seen0 ? s[j] * p.scale_log2 : -INFINITY;
+                const float b = seen1 ? s[j + 2] * p.scale_log2 : -INFINITY;
+                float tile_max = fmaxf(a, b);
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
+                tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
+                const float new_max = fmaxf(row_max[j], tile_max);
+                const float base = new_max == -INFINITY ? 0.0f : new_max;  // a head that has seen nothing yet
+                rescale[j] = exp2f(row_max[j] - base);                     // 0 while row_max is -inf
+                row_max[j] = new_max;
+                prob[j] = exp2f(a - base);
+                prob[j + 2] = exp2f(b - base);
+                row_sum[j] = row_sum[j] * rescale[j] + prob[j] + prob[j + 2];
+            }
+            packed[0] = movmatrix_trans(pack_bf16(prob[0], prob[1]));  // keys 0-7 of the tile
+            packed[1] = movmatrix_trans(pack_bf16(prob[2], prob[3]));  // keys 8-15
+        }
+        if (__any_sync(0xffffffffu, rescale[0] != 1.0f || rescale[1] != 1.0f)) {
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+                acc[i][0] *= rescale[0], acc[i][2] *= rescale[0];
+                acc[i][1] *= rescale[1], acc[i][3] *= rescale[1];
+            }
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(v_bar, phase))) {
+            failed = true;
+            break;
+        }
+        const bool ragged = first_key < lowest || first_key + TMA_WARP_KEYS - 1 > position;
+        if (ragged) {  // zero the value rows that the query must not see (or that were never fetched)
+            for (int idx = lane; idx < TMA_WARP_KEYS * HALVES * 8; idx += 32) {
+                const int row = idx / (HALVES * 8), rest = idx % (HALVES * 8);
+                const int key = first_key + row;
+                if (key < lowest || key > position)
+                    *reinterpret_cast<uint4*>(v_tile + (rest >> 3) * HALF_BYTES + row * 128 + ((rest & 7) << 4)) =
+                        make_uint4(0u, 0u, 0u, 0u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // before a TMA box lands there again
+            __syncwarp();
+        }
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            uint32_t a[4];
+            const int chunk = i * 2 + v_hi;
+            ldmatrix_x4_trans(a, v_tile + (chunk >> 3) * HALF_BYTES + v_row * 128 + (((chunk & 7) ^ (v_row & 7)) << 4));
+            mma_bf16(acc[i], a, packed[0], packed[1]);
+        }
+        __syncwarp();
+        if (more) issue(tile + 1, v_tile, &v_map, v_bar);
+        phase ^= 1u;
+    }
+    if (failed && lane == 0) atomicCAS(&g_decode_error, 0, 1);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        row_sum[j] += __shfl_xor_sync(0xffffffffu, row_sum[j], 4);
+        row_sum[j] += __shfl_xor_sync(0xffffffffu, row_sum[j], 8);
+        row_sum[j] += __shfl_xor_sync(0xffffffffu, row_sum[j], 16);
+    }
+    __syncwarp();  // every lane is done reading this warp's tiles: they now hold the warp's partial
+
+    // Per-warp partial [8 heads][D + 2] float32 over the warp's own K and V tiles.
+    float* mine = reinterpret_cast<float*>(k_tile);
+    {
+        const int head = 2 * (lane & 3), dim = lane >> 2;
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            mine[head * STRIDE + i * 16 + dim] = acc[i][0];
+            mine[(head + 1) * STRIDE + i * 16 + dim] = acc[i][1];
+            mine[head * STRIDE + i * 16 + dim + 8] = acc[i][2];
+            mine[(head + 1) * STRIDE + i * 16 + dim + 8] = acc[i][3];
+        }
+        if (lane < 4) {
+            mine[head * STRIDE + D] = row_max[0], mine[head * STRIDE + D + 1] = row_sum[0];
+            mine[(head + 1) * STRIDE + D] = row_max[1], mine[(head + 1) * STRIDE + D + 1] = row_sum[1];
+        }
+    }
+    __syncthreads();
+
+    // Merge the eight warps (ascending keys): the CTA's partial, or with one split the output.
+    const bool direct = splits == 1;
+    for (int idx = threadIdx.x; idx < group * STRIDE; idx += TMA_DECODE_THREADS) {
+        const int row = idx / STRIDE, col = idx % STRIDE;
+        float weight[TMA_DECODE_WARPS], total_max = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < TMA_DECODE_WARPS; ++w) {
+            weight[w] = reinterpret_cast<const float*>(smem + w * 2 * OPERAND_BYTES)[row * STRIDE + D];
+            total_max = fmaxf(total_max, weight[w]);
+        }
+        float value = 0.0f, denom = 0.0f;
+#pragma unroll
+        for (int w = 0; w < TMA_DECODE_WARPS; ++w) {
+            if (weight[w] == -INFINITY) continue;
+            const float* part = reinterpret_cast<const float*>(smem + w * 2 * OPERAND_BYTES);
+            const float scale = exp2f(weight[w] - total_max);
+            value += part[row * STRIDE + (col == D ? D + 1 : col)] * scale;
+            if (direct) denom += part[row * STRIDE + D + 1] * scale;
+        }
+        if (col == D) value = total_max;
+        const int head = kv_head * group + row;
+        if (!direct)
+            p.partials[((static_cast<size_t>(entry) * p.heads + head) * p.max_splits + split) * STRIDE + col] = value;
+        else if (col < D)
+            p.out[(static_cast<size_t>(token) * p.heads + head) * D + col] = __float2bfloat16(value / denom);
+    }
+    if (direct || p.counters == nullptr) return;  // nothing to merge, or a separate kernel merges
+
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* counter = p.counters + entry * p.kv_heads + kv_head;
+        const int ticket = atomicAdd(counter, 1);
+        is_last = ticket == active - 1;
+        if (is_last) *counter = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int row = warp; row < group; row += TMA_DECODE_WARPS) merge_head<D>(p, entry, kv_head * group + row, 0, active - 1, lane);
+}
+
+// One warp per (entry, head) merges the partials of the kernel above when it got no counters.
+template <int D>
+__global__ void __launch_bounds__(128) attention_decode_tma_merge_kernel(AttnParams p, int items) {
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
+    if (item >= items) return;
+    const int listed = item / p.heads, head = item % p.heads;
+    const int entry = p.entry_ids ? p.entry_ids[listed] : listed;
+    const int position = p.context_lens[entry] - 1;
+    const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
+    const int tile_count = position / DECODE_CHUNK - lowest / DECODE_CHUNK + 1;
+    const int per_cta = max((tile_count + p.max_splits - 1) / p.max_splits, TMA_MIN_TILES);
+    merge_head<D>(p, entry, head, 0, (tile_count + per_cta - 1) / per_cta - 1, lane);
 }
 
 // -------------------------------------------------------------------------------- host
@@ -552,6 +895,24 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
     if (status != 0 || p.counters != nullptr) return status;
     const int items = entries * p.heads;
     return launch_kernel(attention_decode_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
+}
+
+template <int D>
+static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map, const AttnParams& p, int entries,
+                             cudaStream_t stream) {
+    constexpr int SMEM = tma_decode_smem_bytes<D>();
+    auto kernel = attention_decode_tma_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid(p.max_splits, p.kv_heads, entries);
+    const int status = launch_kernel(kernel, grid, TMA_DECODE_THREADS, SMEM, stream, k_map, v_map, p);
+    if (status != 0 || p.counters != nullptr || p.max_splits == 1) return status;
+    const int items = entries * p.heads;
+    return launch_kernel(attention_decode_tma_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
 }
 
 static int shift_of(int page_size) {
@@ -601,6 +962,40 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
                  page_size, table_width, window, max_splits, shift_of(page_size), tiles_per_cta};
     return head_dim == 128 ? launch_decode<128>(p, entries, stream) : launch_decode<64>(p, entries, stream);
+}
+
+// Every entry brings one token, through the TMA kernel.  `k_map` and `v_map` are 128-byte TMA
+// descriptors of the page arrays seen as [(pages * kv_heads * page_size)][head_dim] with boxes of
+// min(page_size, 16) rows by 64 elements in the 128-byte swizzle.  `splits` CTAs share the keys
+// of one (request, KV head); `partials` holds entries * heads * splits * (head_dim + 2) floats and
+// `counters` entries * kv_heads zeros (both unused with one split).  Groups of up to 8 query
+// heads, pages of a power of two of at least 8 keys; other sizes are refused.
+ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map, const void* q, const int* block_table,
+                                           const int* cu_tokens, const int* context_lens, void* out, float* partials,
+                                           int* counters, float scale, int entries, int splits, int heads,
+                                           int kv_heads, int head_dim, int page_size, int table_width, int window,
+                                           const int* entry_ids, cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 8) return ME_ERR_UNSUPPORTED;
+    if (shift_of(page_size) < 3) return ME_ERR_UNSUPPORTED;
+    if (splits < 1 || splits > 65535 || (splits > 1 && partials == nullptr)) return ME_ERR_ARGUMENT;
+    AttnParams p{static_cast<const __nv_bfloat16*>(q), nullptr, nullptr, block_table, cu_tokens, context_lens,
+                 static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
+                 page_size, table_width, window, splits, shift_of(page_size), 0};
+    CUtensorMap maps[2];
+    memcpy(&maps[0], k_map, sizeof(CUtensorMap));
+    memcpy(&maps[1], v_map, sizeof(CUtensorMap));
+    return head_dim == 128 ? launch_decode_tma<128>(maps[0], maps[1], p, entries, stream)
+                           : launch_decode_tma<64>(maps[0], maps[1], p, entries, stream);
+}
+
+// First failure that a decode kernel recorded since the last call (a wait that ran out), or 0.
+ME_EXPORT int me_attention_bf16_take_error(int* code) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(code, g_decode_error, sizeof(int));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (*code != 0) e = cudaMemcpyToSymbol(g_decode_error, &zero, sizeof(int));
+    return static_cast<int>(e);
 }
 
 // The same with one tile of 128 keys per CTA: max_splits = ceil(max_context / 128).

@@ -1,7 +1,9 @@
 """Host side of the bfloat16 tensor-core attention kernels: which kernel a batch takes.
 
-* every entry brings one token and the group has at most 16 query heads: the split decode
-  kernel (scratch for the partial results comes from the workspace);
+* every entry brings one token and the group has at most 16 query heads: a split decode kernel
+  (scratch for the partial results comes from the workspace): with groups of at most 8 heads and
+  pages of a power of two of at least 8 keys the one that fetches whole page rows by TMA, else
+  the one that gathers keys row by row;
 * otherwise, head size 128, no window, pages of 8 to 128 tokens and a portion of at least 32
   tokens in the batch: the tcgen05 kernel (both products on the tensor cores with accumulators in
   tensor memory, keys and values fetched by TMA page by page);
@@ -22,7 +24,7 @@ DECODE_CHUNK = 128
 TENSOR_MEMORY_MIN_TOKENS = 32  # portions at least this long take the tcgen05 kernel
 _lib = None
 _tc_lib = None
-_page_maps: dict[tuple[int, tuple[int, ...]], object] = {}
+_page_maps: dict[tuple[int, tuple[int, ...], int], object] = {}
 _query_maps: dict[tuple[int, int, int], object] = {}
 
 
@@ -41,29 +43,42 @@ def _tc_library():
 
 
 def take_error() -> int:
-    """First failure that the tcgen05 attention kernel recorded since the last call, or 0."""
-    if _tc_lib is None:
-        return 0
+    """First failure (a wait that ran out) that an attention kernel recorded since the last call,
+    or 0.  Only libraries that were loaded are asked."""
     import ctypes
 
-    code = c_int(0)
-    status = _tc_lib.me_attention_take_error(ctypes.byref(code))
-    if status != 0:
-        raise RuntimeError(f"could not read the attention kernels' error flag (CUDA error {status})")
-    return code.value
+    found = 0
+    for lib, symbol in ((_tc_lib, "me_attention_take_error"), (_lib, "me_attention_bf16_take_error")):
+        if lib is None:
+            continue
+        code = c_int(0)
+        status = getattr(lib, symbol)(ctypes.byref(code))
+        if status != 0:
+            raise RuntimeError(f"could not read the attention kernels' error flag (CUDA error {status})")
+        found = found or code.value
+    return found
 
 
-def _page_map(pages: torch.Tensor):
-    """TMA descriptor of a page array seen as [(pages * kv_heads * page_size), head_dim]."""
+def _page_map(pages: torch.Tensor, box_rows: int | None = None):
+    """TMA descriptor of a page array seen as [(pages * kv_heads * page_size), head_dim], with
+    boxes of ``box_rows`` rows (a whole page by default)."""
     from mini_engine_b200.csrc import tensor_core
 
-    key = (pages.data_ptr(), tuple(pages.shape))
+    count, kv_heads, page_size, head_dim = pages.shape
+    box_rows = box_rows or page_size
+    key = (pages.data_ptr(), tuple(pages.shape), box_rows)
     held = _page_maps.get(key)
     if held is None:
-        count, kv_heads, page_size, head_dim = pages.shape
-        held = tensor_core._make_map(pages.view(count * kv_heads * page_size, head_dim), page_size)
+        held = tensor_core._make_map(pages.view(count * kv_heads * page_size, head_dim), box_rows)
         _page_maps[key] = held
     return held
+
+
+TMA_DECODE_KEYS = 16  # keys of one warp's box in the TMA decode kernel
+
+
+def tma_decode_kernel_takes(heads: int, kv_heads: int, page_size: int) -> bool:
+    return heads // kv_heads <= 8 and page_size >= 8 and page_size & (page_size - 1) == 0
 
 
 def _query_map(q: torch.Tensor):
@@ -92,11 +107,17 @@ def tensor_memory_kernel_takes(head_dim: int, page_size: int, window: int, max_q
 def _library():
     global _lib
     if _lib is None:
+        import ctypes
+
         lib = load_library("attention_bf16")
         lib.me_attention_portions_bf16.argtypes = [c_void_p] * 7 + [c_float] + [c_int] * 8 + [c_void_p, c_void_p]
         lib.me_attention_portions_bf16.restype = c_int
         lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
+        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 8 + [c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tma.restype = c_int
+        lib.me_attention_bf16_take_error.argtypes = [ctypes.POINTER(c_int)]
+        lib.me_attention_bf16_take_error.restype = c_int
         _lib = lib
     return _lib
 
@@ -115,6 +136,19 @@ def decode_tiles_per_cta(entries: int, kv_heads: int, max_context_len: int) -> i
     hence the result in its last bits, never which keys are read."""
     tiles = entries * kv_heads * max(1, -(-max_context_len // DECODE_CHUNK))
     return max(1, min(8, -(-tiles // RESIDENT_DECODE_CTAS)))
+
+
+FORCED_TMA_SPLITS = 0  # > 0: what kernel_bench's --splits asks for
+
+
+def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int) -> int:
+    """CTAs that share the keys of one (request, KV head) in the TMA decode kernel: as many as
+    fill one resident wave, at most one per 256 keys of the longest context.  The kernel divides
+    each request's own tiles evenly among them (two tiles of 128 keys or more per CTA)."""
+    if FORCED_TMA_SPLITS > 0:
+        return FORCED_TMA_SPLITS
+    tiles = max(1, -(-max_context_len // DECODE_CHUNK))
+    return max(1, min(RESIDENT_DECODE_CTAS // max(1, entries * kv_heads), -(-tiles // 2), 64))
 
 
 def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
@@ -150,7 +184,19 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             launches = [("portions", ctx.num_entries, None, ctx.max_query_len)]
     for kind, entries, ids, longest in launches:
         ids_ptr = None if ids is None else ids.data_ptr()
-        if kind == "decode":
+        if kind == "decode" and tma_decode_kernel_takes(heads, kv_heads, page_size):
+            splits = tma_decode_splits(entries, kv_heads, ctx.max_context_len)
+            partials = counters = None
+            if splits > 1:
+                partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32).data_ptr()
+                counters = ctx.workspace.zeroed("attn.counters", ctx.num_entries * kv_heads).data_ptr()
+            rows = min(page_size, TMA_DECODE_KEYS)
+            code = _library().me_attention_decode_bf16_tma(
+                _page_map(k_pages, rows), _page_map(v_pages, rows), common[0], *common[3:], partials, counters, scale,
+                entries, splits, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, stream,
+            )  # fmt: skip
+            ops._check(code, "attention_decode_bf16_tma")
+        elif kind == "decode":
             tiles = decode_tiles_per_cta(entries, kv_heads, ctx.max_context_len)
             splits = decode_splits(ctx.max_context_len, tiles)
             partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32)

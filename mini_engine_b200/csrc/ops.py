@@ -59,6 +59,19 @@ def _check(code: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {code} ({_cuda_error_name(code)})")
 
 
+def raise_on_device_error() -> None:
+    """Ask the tensor-core and attention libraries that are loaded whether a kernel gave up a
+    bounded wait since the last call, and raise if one did: what such a kernel wrote is invalid.
+    Reads a flag from the device, so it waits for the work in flight."""
+    from mini_engine_b200.csrc import attention_bf16, tensor_core
+
+    for what, code in (("tensor-core product", tensor_core.take_error()), ("attention", attention_bf16.take_error())):
+        if code:
+            raise KernelError(
+                f"a {what} kernel ran into the limit of a wait (code {code}): the results since the last check are invalid"
+            )
+
+
 def _cuda_error_name(code: int) -> str:
     try:
         runtime = ctypes.CDLL("libcudart.so")

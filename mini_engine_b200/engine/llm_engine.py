@@ -18,6 +18,7 @@ import torch
 from mini_engine_b200.cache.manager import CacheManager
 from mini_engine_b200.cache.storage import blocks_for_budget
 from mini_engine_b200.config.engine_config import EngineConfig
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.engine.graphs import DecodeGraphs
 from mini_engine_b200.engine.loading import load_model, random_model
 from mini_engine_b200.engine.runner import ModelRunner, StepEntry
@@ -26,6 +27,9 @@ from mini_engine_b200.engine.sequence import Sequence
 from mini_engine_b200.parts.model import DecoderModel
 from mini_engine_b200.sampling.params import SamplingParams
 from mini_engine_b200.sampling.sampler import Sampler
+
+
+DEVICE_CHECK_EVERY = 32  # steps between reads of the kernels' error flags (generate() also reads them at its end)
 
 
 @dataclass
@@ -116,6 +120,7 @@ class LLMEngine:
         seqs = [self.add_request(p, params) for p in prompts]
         while self.scheduler.has_unfinished():
             self.step()
+        ops.raise_on_device_error()
         return [s.output_token_ids for s in seqs]
 
     @torch.inference_mode()
@@ -140,6 +145,8 @@ class LLMEngine:
         tokens = iter(sampled)
         next_tokens = [next(tokens) if item.samples else None for item in batch]
         self._update_stats(batch)
+        if self.stats.steps % DEVICE_CHECK_EVERY == 0:
+            ops.raise_on_device_error()
         return self.scheduler.postprocess(batch, next_tokens)
 
     # ---------------------------------------------------------------- private

@@ -65,6 +65,7 @@ class Replayer:
     def step(self, record: dict) -> torch.Tensor | None:
         """Run one step record; return the wanted logits ``[wanted, vocab]`` on the host, or
         ``None`` when nothing was wanted."""
+        from mini_engine_b200.csrc import ops
         from mini_engine_b200.engine.runner import StepEntry
 
         entries = []
@@ -88,6 +89,7 @@ class Replayer:
                 result = logits.to("cpu")
             else:
                 torch.cuda.synchronize()
+            ops.raise_on_device_error()
             for entry in entries:
                 self.manager.release_behind_window(entry.cache, entry.start + len(entry.token_ids))
         for name in record.get("end", []):

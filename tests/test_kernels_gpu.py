@@ -237,15 +237,19 @@ def attention_reference(q, k, v, scale, window=None):
     return out
 
 
-def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None):
+def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None, stale=None):
     """Sequences of the given lengths in scattered pages; the last ``new_counts[i]`` tokens of
-    each are the batch's queries.  Returns kernel inputs and the expected output rows."""
+    each are the batch's queries.  Returns kernel inputs and the expected output rows.  Slots that
+    no sequence owns hold random numbers, or ``stale`` when given."""
     g = torch.Generator().manual_seed(seed)
     total_pages = sum(-(-n // page) for n in lengths) + 3
     order = torch.randperm(total_pages, generator=g).tolist()
     width = max(-(-n // page) for n in lengths) + 1
     k_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(dtype)  # stale data everywhere
     v_pages = torch.randn(total_pages, kv_heads, page, head_dim, generator=g).to(dtype)
+    if stale is not None:
+        k_pages.fill_(stale)
+        v_pages.fill_(stale)
     table = torch.full((len(lengths), width), -1, dtype=torch.int32)
     q_rows, want_rows, entry_of, positions = [], [], [], []
     for b, (n, new) in enumerate(zip(lengths, new_counts)):
@@ -330,6 +334,9 @@ BF16_ATTENTION_CASES = [
     ([1, 16, 17, 33, 100, 255, 256, 257, 600], [1] * 9, 8, 2, 128, 16),  # decode, group 4
     ([64, 65, 300], [1, 1, 1], 4, 4, 64, 4),  # decode, group 1, small pages
     ([700, 3], [1, 1], 16, 1, 64, 16),  # decode, group 16
+    ([1, 8, 9, 16, 17, 127, 128, 129, 640], [1] * 9, 8, 1, 128, 8),  # decode, group 8, two pages per 16 keys
+    ([5, 250, 1031], [1] * 3, 6, 2, 64, 32),  # decode, group 3, 16 keys are half a page
+    ([2000, 77], [1, 1], 4, 1, 128, 128),  # decode, pages as large as a tile
     ([7, 9, 13], [7, 1, 5], 4, 2, 64, 4),  # fresh prompt, decode, continuation
     ([300, 64, 2, 129], [300, 33, 2, 65], 6, 2, 128, 8),
     ([513, 40], [2, 40], 8, 8, 64, 16),
@@ -376,6 +383,25 @@ def test_paged_attention_bf16_tensor_core(case):
     )  # fmt: skip
     assert rel_error(out.cpu(), data["want"]) < 1e-2
     assert attention_bf16.take_error() == 0
+
+
+@pytest.mark.parametrize("page", [8, 16, 64])
+def test_decode_ignores_what_reused_pages_still_hold(page):
+    """Slots behind a request's last token (and pages it does not own) hold infinities: none of it
+    may reach the output, not even multiplied by a probability of zero."""
+    from mini_engine_b200.csrc import attention_bf16
+
+    lengths, heads, kv_heads, head_dim = [1, 7, 19, 130, 257], 8, 2, 128
+    news = [1] * len(lengths)
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=14, stale=float("inf"))
+    out = torch.full_like(data["q"], float("nan"))
+    attention_bf16.paged_attention(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
+        head_dim, head_dim**-0.5, 0,
+    )  # fmt: skip
+    assert attention_bf16.take_error() == 0
+    assert torch.isfinite(out).all()
+    assert rel_error(out.cpu(), data["want"]) < 1e-2
 
 
 TENSOR_MEMORY_CASES = [
