@@ -11,7 +11,9 @@
 
 // ------------------------------------------------------------------------------ embedding
 
-template <typename T>
+// One block per token.  VEC: the width is a multiple of 8 and both pointers are 16-byte aligned;
+// a thread then moves eight elements per step.
+template <typename T, bool VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
     const int token = blockIdx.x;
@@ -24,23 +26,46 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
         return;
     }
     const T* row = table + static_cast<size_t>(id) * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = to_float(row[i]);
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            if (sizeof(T) == 2) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(row + i);
+                const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(pairs[j]);
+                    v[2 * j] = f.x, v[2 * j + 1] = f.y;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = to_float(row[i + j]);
+            }
+            *reinterpret_cast<float4*>(row_out + i) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(row_out + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = to_float(row[i]);
+    }
 }
 
 ME_EXPORT int me_embedding(const void* table, int table_type, const int* ids, float* out, int tokens,
                            int hidden, int vocab, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    const int threads = hidden >= 1024 ? 256 : 128;
-    if (table_type == ME_BF16)
-        return launch_kernel(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
-                             static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab);
-    return launch_kernel(embedding_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out,
-                         hidden, vocab);
+    const bool vec = hidden % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const int threads = vec ? std::min(512, std::max(32, (hidden / 8 + 31) / 32 * 32)) : (hidden >= 1024 ? 256 : 128);
+    if (table_type == ME_BF16) {
+        const auto* t = static_cast<const __nv_bfloat16*>(table);
+        return vec ? launch_kernel(embedding_kernel<__nv_bfloat16, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab)
+                   : launch_kernel(embedding_kernel<__nv_bfloat16, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab);
+    }
+    const auto* t = static_cast<const float*>(table);
+    return vec ? launch_kernel(embedding_kernel<float, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab)
+               : launch_kernel(embedding_kernel<float, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab);
 }
 
 // --------------------------------------------------------------- residual sum + RMSNorm
 
-constexpr int NORM_THREADS = 256;
 constexpr int MAX_UNROLLED_SPLITS = 8;
 
 __device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
@@ -57,7 +82,10 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
 // the listed rows are read and x is left alone.  out = weight * x_row * rsqrt(mean(x_row^2) + eps).
 // VEC: hidden is a multiple of 4 and every pointer is 16-byte aligned; all loads of a thread are
 // then issued before any of them is used, which is what matters when only a few rows run.
-template <typename OutT, bool VEC>
+// NORM_THREADS (256, 512 or 1024) is chosen from the width alone, so that a thread of the
+// vectorised path has one group of four columns where the width allows it and every load of the
+// row is in flight at once.
+template <typename OutT, bool VEC, int NORM_THREADS>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
                    const float* __restrict__ weight, float eps, OutT* __restrict__ out,
@@ -66,8 +94,12 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     __shared__ float warp_partial[NORM_THREADS / 32];
     const int out_row = blockIdx.x;
     pdl_trigger();
-    pdl_wait();
+    // The norm's weight and the step's row list do not come from the previous kernel: fetch them
+    // ahead of the wait.
     const int src = rows ? rows[out_row] : out_row;
+    float4 first_weight = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (VEC && threadIdx.x * 4 < hidden) first_weight = *reinterpret_cast<const float4*>(weight + threadIdx.x * 4);
+    pdl_wait();
     float* x_row = x + static_cast<size_t>(src) * hidden;
     const float* pending_row = pending + static_cast<size_t>(src) * hidden;
     const bool write_back = !rows && splits > 0;
@@ -109,7 +141,7 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     if (VEC) {
         for (int i = threadIdx.x * 4; i < hidden; i += NORM_THREADS * 4) {
             const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
-            const float4 w = *reinterpret_cast<const float4*>(weight + i);
+            const float4 w = i == threadIdx.x * 4 ? first_weight : *reinterpret_cast<const float4*>(weight + i);
             store4(out_ptr + i, make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv)));
         }
     } else {
@@ -118,14 +150,25 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     }
 }
 
-template <typename OutT, bool VEC>
-static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
-                              float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+template <typename OutT, bool VEC, int NORM_THREADS>
+static int launch_add_rmsnorm_threads(float* x, const float* pending, int splits, size_t split_stride,
+                                      const float* weight, float eps, OutT* out, const int* rows, int count, int hidden,
+                                      cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
-    auto kernel = add_rmsnorm_kernel<OutT, VEC>;
+    auto kernel = add_rmsnorm_kernel<OutT, VEC, NORM_THREADS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_kernel(kernel, count, NORM_THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
                          rows, hidden);
+}
+
+template <typename OutT, bool VEC>
+static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
+                              float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+    if (VEC && hidden > 2048)
+        return launch_add_rmsnorm_threads<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+    if (VEC && hidden > 1024)
+        return launch_add_rmsnorm_threads<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+    return launch_add_rmsnorm_threads<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
@@ -296,6 +339,11 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
     const int first_head = static_cast<int>(item % groups) * HEADS;
     constexpr int D = 128;
     pdl_trigger();
+    // Weights and the step's slot list do not come from the previous kernel: fetch them ahead of the wait.
+    const float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    const float4 q_w = a.q_weight ? *reinterpret_cast<const float4*>(a.q_weight + lane * 4) : one;
+    const float4 k_w = a.k_weight ? *reinterpret_cast<const float4*>(a.k_weight + lane * 4) : one;
+    const int slot = a.slot_mapping ? a.slot_mapping[token] : 0;
     pdl_wait();
     const float* src = a.qkv + static_cast<size_t>(token) * heads_total * D + static_cast<size_t>(first_head) * D + lane * 4;
     float4 part[HEADS][MAX_SPLITS];
@@ -310,7 +358,6 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
         first = angles[0];   // (cos, sin) of four consecutive frequencies
         second = angles[1];
     }
-    const int slot = a.slot_mapping ? a.slot_mapping[token] : 0;
 #pragma unroll
     for (int u = 0; u < HEADS; ++u) {
         const int column_head = first_head + u;
@@ -325,7 +372,7 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
             float sum_sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
             sum_sq = warp_sum(sum_sq);
             const float inv = rsqrtf(sum_sq / static_cast<float>(D) + a.eps);
-            const float4 w = *reinterpret_cast<const float4*>(weight + lane * 4);
+            const float4 w = is_q ? q_w : k_w;
             v = make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv));
         }
         if ((is_q || is_k) && a.cos_sin != nullptr) {

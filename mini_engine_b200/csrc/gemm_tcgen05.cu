@@ -62,7 +62,8 @@ struct GemmParams {
     void* out;            // float [splits][tokens][outs], or bfloat16 [tokens][outs] in DUAL mode
     int tokens, outs, k_blocks, k_blocks_per_split;
     int dual_row_offset;  // row of W where the second (up) half starts
-    int token_tiles, full_tiles, tail_parts;  // pair kernel: tiles of 256 tokens; whole ones; cuts of the rest
+    int token_tiles, full_tiles, tail_parts;  // pair kernels: tiles along the tokens; whole ones; cuts of the rest
+    int items;  // persistent pair kernel: whole tiles + parts of cut tiles
 };
 
 template <int BLOCK_T, bool DUAL>
@@ -377,6 +378,212 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     if (warp == 1) tcgen05_dealloc_pair(tmem_base, C::TMEM_COLUMNS);
 }
 
+// ------------------------------------------- persistent CTA-pair kernel (many tokens)
+
+// The pair kernel above with one pair per two SMs walking a list of tiles (pair c takes tiles c,
+// c + pairs, ...: the pairs that run together still share a weight tile) and two accumulator
+// buffers in tensor memory: while the epilogue warps of both CTAs drain the buffer of tile j, the
+// MMAs of tile j + 1 fill the other one, and the TMA ring never drains between tiles.  Tiles are
+// 256 features x 256 tokens.  A gated product's gate and up accumulators fill all 512 columns, so
+// it has one buffer: its MMAs wait for the epilogue (eight warps per CTA there, to shorten it),
+// but the next tile's operands are already in shared memory by then.
+// Barrier `acc_empty[b]` lives in the rank-0 CTA and counts the epilogue warps of both CTAs.
+template <bool DUAL>
+struct PersistentConfig {
+    static constexpr int TILE_T = 256;
+    static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2 * (DUAL ? 2 : 1);
+    static constexpr int B_BYTES = (TILE_T / 2) * BLOCK_K * 2;  // this CTA's half of the tile's tokens
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int BUFFERS = DUAL ? 1 : 2;          // accumulator buffers in tensor memory
+    static constexpr int BUFFER_COLUMNS = DUAL ? 512 : 256;
+    static constexpr int TMEM_COLUMNS = 512;
+    static constexpr int EPILOGUE_WARPS = DUAL ? 8 : 4;   // per CTA; a quarter of the rows each, the columns shared
+    static constexpr int THREADS = 64 + 32 * EPILOGUE_WARPS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t target_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(target_rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+// Item `item` of the list: its first token, its feature tile (of 256 features) and its width in tokens.
+template <int TILE_T>
+__device__ __forceinline__ void pair_item(const GemmParams& p, int item, int& t0, int& feature_tile, int& width) {
+    int tile = item, token_offset = 0;
+    width = TILE_T;
+    if (item >= p.full_tiles) {
+        const int j = item - p.full_tiles;
+        tile = p.full_tiles + j / p.tail_parts;
+        const int part = j % p.tail_parts;
+        const int base = (TILE_T / 16) / p.tail_parts, extra = (TILE_T / 16) % p.tail_parts;
+        width = (base + (part < extra ? 1 : 0)) * 16;
+        token_offset = (part * base + min(part, extra)) * 16;
+    }
+    t0 = (tile % p.token_tiles) * TILE_T + token_offset;
+    feature_tile = tile / p.token_tiles;
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(PersistentConfig<DUAL>::THREADS)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    using C = PersistentConfig<DUAL>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int iterations = p.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * C::EPILOGUE_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc_pair(tmem_holder, C::TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // both CTAs' barriers exist before either signals the other's
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_trigger();
+            int it = 0;  // k blocks loaded so far, over all items: stage = it % STAGES
+            bool waited = false, ok = true;
+            for (int item = pair; item < p.items && ok; item += pairs) {
+                int t0, feature_tile, width;
+                pair_item<C::TILE_T>(p, item, t0, feature_tile, width);
+                const int n0 = (feature_tile * 2 + rank) * BLOCK_N;
+                const int b_row = t0 + rank * (width / 2);  // this CTA's half of the tile's tokens
+                int i = 0;
+                if (!waited) {
+                    // The weights do not come from the previous kernel: the first stages' weight
+                    // tiles are on their way before the wait for it.
+                    const int early = min(iterations, C::STAGES);
+                    for (; i < early; ++i) {
+                        uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
+                        if (rank == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);  // the bytes of both CTAs
+                        tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[i]);
+                        if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[i]);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int e = 0; e < early; ++e)
+                        tma_load_2d_pair(tiles + e * C::STAGE_BYTES + C::A_BYTES, &map_x, e * BLOCK_K, b_row, &full[e]);
+                    it = early;
+                }
+                for (; i < iterations; ++i, ++it) {
+                    const int stage = it % C::STAGES;
+                    if (!mbar_wait(&empty[stage], ((it / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (20 << 8) | stage); ok = false; break; }
+                    uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
+                    tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
+                    if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
+                    tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, b_row, &full[stage]);
+                }
+            }
+            if (!waited) pdl_wait();
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int it = 0, j = 0;
+            bool ok = true;
+            for (int item = pair; item < p.items && ok; item += pairs, ++j) {
+                int t0, feature_tile, width;
+                pair_item<C::TILE_T>(p, item, t0, feature_tile, width);
+                const int buffer = j % C::BUFFERS;
+                if (!mbar_wait(&acc_empty[buffer], ((j / C::BUFFERS) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (21 << 8) | buffer); break; }
+                tcgen05_fence_after();
+                const uint32_t idesc = make_idesc_pair(width);
+                const uint32_t d_tmem = tmem_base + buffer * C::BUFFER_COLUMNS;
+                for (int i = 0; i < iterations; ++i, ++it) {
+                    const int stage = it % C::STAGES;
+                    if (!mbar_wait(&full[stage], (it / C::STAGES) & 1)) { atomicCAS(&g_gemm_error, 0, (22 << 8) | stage); ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint64_t a_desc = smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t step = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);
+                        const uint32_t accumulate = (i > 0 || k > 0) ? 1u : 0u;
+                        tcgen05_mma_bf16_pair(d_tmem, a_desc + step, b_desc + step, idesc, accumulate);
+                        if (DUAL) {
+                            const uint64_t a2_desc = smem_desc_sw128(a_addr + BLOCK_N * BLOCK_K * 2);
+                            tcgen05_mma_bf16_pair(d_tmem + C::TILE_T, a2_desc + step, b_desc + step, idesc, accumulate);
+                        }
+                    }
+                    tcgen05_commit_pair(&empty[stage]);
+                }
+                if (ok) tcgen05_commit_pair(&acc_full[buffer]);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();
+        int j = 0;
+        for (int item = pair; item < p.items; item += pairs, ++j) {
+            int t0, feature_tile, width;
+            pair_item<C::TILE_T>(p, item, t0, feature_tile, width);
+            const int buffer = j % C::BUFFERS;
+            const int n = (feature_tile * 2 + rank) * BLOCK_N + quarter * 32 + lane;
+            bool ok = mbar_wait(&acc_full[buffer], (j / C::BUFFERS) & 1);
+            if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (23 << 8) | buffer);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            tcgen05_fence_after();
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * C::BUFFER_COLUMNS;
+            // The warps that share a quarter of the rows divide the columns in units of 16.
+            constexpr int SHARERS = C::EPILOGUE_WARPS / 4;
+            const int units = width / 16, sharer = (warp - 2) / 4;
+            const int c_begin = (units * sharer / SHARERS) * 16, c_end = (units * (sharer + 1) / SHARERS) * 16;
+#pragma unroll 1
+            for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+                if (t0 + c0 >= p.tokens) break;
+                if (!DUAL) {
+                    float v[16];
+                    tcgen05_ld16(lane_base + c0, v);
+                    if (n < p.outs) {
+                        float* out = static_cast<float*>(p.out);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (t0 + c0 + c < p.tokens) out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = v[c];
+                    }
+                } else {
+                    float gate[16], up[16];
+                    tcgen05_ld16(lane_base + c0, gate);
+                    tcgen05_ld16(lane_base + C::TILE_T + c0, up);
+                    if (n < p.outs) {
+                        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            if (t0 + c0 + c < p.tokens) {
+                                const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                                out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = __float2bfloat16_rn(activated * up[c]);
+                            }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(&acc_empty[buffer], 0);  // this warp has read its rows of the buffer
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // neither CTA leaves while the other may still read its shared or tensor memory
+    if (warp == 1) tcgen05_dealloc_pair(tmem_base, C::TMEM_COLUMNS);
+}
+
 // -------------------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -514,6 +721,72 @@ ME_EXPORT int me_gemm_tcgen05_pair_swiglu(const void* map_w, const void* map_x, 
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
     return launch_pair<true>(w, x, p, stream);
+}
+
+template <bool DUAL>
+static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+    using C = PersistentConfig<DUAL>;
+    auto kernel = gemm_tcgen05_persistent_kernel<DUAL>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    int device = 0, sms = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    GemmParams q = p;
+    q.token_tiles = (p.tokens + C::TILE_T - 1) / C::TILE_T;
+    const int tiles = q.token_tiles * ((p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N));
+    const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+    // The tiles of a last round that is less than half full are cut in 2 or 4 narrower ones that
+    // run side by side (see the pair kernel's launcher for what was measured).
+    q.full_tiles = tiles / pairs * pairs;
+    q.tail_parts = 1;
+    while (q.tail_parts < 4 && (tiles - q.full_tiles) * q.tail_parts * 2 <= pairs) q.tail_parts *= 2;
+    if (tiles <= pairs) return launch_pair<DUAL>(map_w, map_x, p, stream);  // one tile per pair: nothing to overlap
+    q.items = q.full_tiles + (tiles - q.full_tiles) * q.tail_parts;
+    const int clusters = q.items < pairs ? q.items : pairs;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * clusters, 1, 1);
+    config.blockDim = dim3(C::THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, q));
+}
+
+// out[t][n] (float32) = x[t] . w[n] by persistent CTA pairs.  Weight and activation maps have
+// boxes of 128 rows.
+ME_EXPORT int me_gemm_tcgen05_persistent(const void* map_w, const void* map_x, float* out, int tokens, int outs,
+                                         int inner, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1, 0};
+    return launch_persistent<false>(w, x, p, stream);
+}
+
+// act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) by persistent CTA pairs.
+// Weight and activation maps have boxes of 128 rows.
+ME_EXPORT int me_gemm_tcgen05_persistent_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
+                                                int inner, int dual_row_offset, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0};
+    return launch_persistent<true>(w, x, p, stream);
 }
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.

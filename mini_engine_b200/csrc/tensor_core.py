@@ -23,6 +23,11 @@ SPLIT_MAX_TOKENS = 64  # products of more tokens have enough tiles without split
 MIN_K_BLOCKS_PER_SPLIT = 4
 PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles)
 USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
+# The persistent pair kernel (two accumulator buffers, epilogue under the next tile's MMAs);
+# "0" falls back to one tile per pair of CTAs.
+USE_PERSISTENT = os.environ.get("MINI_ENGINE_B200_PERSISTENT", "1") != "0"
+
+USE_PERSISTENT_GATED = os.environ.get("MINI_ENGINE_B200_PERSISTENT_GATED", "1") != "0"
 
 _lib = None
 
@@ -41,6 +46,10 @@ def _library():
         lib.me_gemm_tcgen05_pair.restype = c_int
         lib.me_gemm_tcgen05_pair_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_swiglu.restype = c_int
+        lib.me_gemm_tcgen05_persistent.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_persistent.restype = c_int
+        lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_gemm_take_error.restype = c_int
         _lib = lib
@@ -126,9 +135,8 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
     tile = token_tile(tokens)
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     if tokens > PAIR_MIN_TOKENS and splits == 1 and USE_PAIRS:
-        code = _library().me_gemm_tcgen05_pair(
-            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream
-        )
+        entry = _library().me_gemm_tcgen05_persistent if USE_PERSISTENT else _library().me_gemm_tcgen05_pair
+        code = entry(plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream)
     else:
         code = _library().me_gemm_tcgen05(
             plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream
@@ -148,7 +156,11 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    if tokens > PAIR_MIN_TOKENS and USE_PAIRS:
+    if tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PERSISTENT_GATED:
+        code = _library().me_gemm_tcgen05_persistent_swiglu(
+            plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
+        )
+    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS:
         code = _library().me_gemm_tcgen05_pair_swiglu(
             plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
         )
