@@ -19,7 +19,7 @@ NUM_SMS = 148
 BLOCK_N = 128
 BLOCK_K = 64
 TOKEN_TILES = (16, 32, 64, 128, 256)
-SPLIT_MAX_TOKENS = 64  # products of more tokens have enough tiles without splitting
+SPLIT_MAX_TOKENS = 1024  # products of more tokens have enough tiles without splitting
 MIN_K_BLOCKS_PER_SPLIT = 4
 PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles)
 USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
@@ -76,7 +76,7 @@ def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> in
     tile = token_tile(tokens)
     tiles = -(-outs // BLOCK_N) * -(-tokens // tile)
     k_blocks = -(-inner // BLOCK_K)
-    slots = NUM_SMS * (3 if tile <= 32 else 2)  # CTAs of this tile size that are resident at once
+    slots = NUM_SMS * (3 if tile <= 32 else 2 if tile <= 64 else 1)  # CTAs of this tile size that are resident at once
     wanted = min(max_splits, max(1, slots // tiles), max(1, k_blocks // MIN_K_BLOCKS_PER_SPLIT))
     per_split = -(-k_blocks // wanted)
     return -(-k_blocks // per_split)

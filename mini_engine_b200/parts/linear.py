@@ -21,14 +21,19 @@ import torch
 from mini_engine_b200.csrc import ops
 from mini_engine_b200.parts.base import StepContext
 
-# A split product returns at most this many partial sums, for at most this many tokens.
+# A split product returns at most this many partial sums.  Up to DECODE_TOKENS tokens (the steps
+# that captured graphs replay) a partial-sum buffer is sized for all of them at once; longer split
+# products (a few hundred tokens, too few tiles to fill the GPU otherwise) let it grow on demand.
 MAX_SPLITS = 8
-SPLIT_MAX_TOKENS = 64
+DECODE_TOKENS = 64
+# The gated product runs as one kernel with the activation in its epilogue from this many tokens
+# on; below, as a split product followed by the activation kernel.
+GATED_FUSED_MIN_TOKENS = 65
 
 
 def partial_rows(max_tokens: int) -> int:
-    """Rows that a ``[S, T, out]`` partial-sum buffer needs for any ``T <= max_tokens``."""
-    return max(max_tokens, MAX_SPLITS * min(max_tokens, SPLIT_MAX_TOKENS))
+    """Rows that a ``[S, T, out]`` partial-sum buffer starts with."""
+    return max(max_tokens, MAX_SPLITS * min(max_tokens, DECODE_TOKENS))
 
 
 class Linear:
@@ -76,7 +81,7 @@ class GatedLinear:
         """``x [T, in]`` -> activated ``[T, inter]`` in the compute dtype."""
         tokens = x.shape[0]
         act = ctx.buffer(name + ".act", (tokens, self.inter), x.dtype)
-        if self.tensor_core and tokens > SPLIT_MAX_TOKENS:
+        if self.tensor_core and tokens >= GATED_FUSED_MIN_TOKENS:
             ops.gemm_tensor_core_swiglu(self.plan, x, act)
             return act
         both = self.linear.forward(x, ctx, name + ".gate_up")
