@@ -18,6 +18,7 @@ compute, all-or-nothing allocation, tail-first release.  Nothing here touches te
 from __future__ import annotations
 
 import hashlib
+import itertools
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Sequence as Seq
@@ -50,6 +51,9 @@ class RequestCache:
     block_tables: list[list[int]]
     page_hashes: list[bytes] = field(default_factory=list)
     state_slot: int = -1
+    version: int = 0  # grows whenever a block table changes: whoever keeps a copy knows when it is stale
+    serial: int = field(default_factory=itertools.count().__next__)  # unlike id(), never used twice
+    packed: object = field(default=None, repr=False, compare=False)  # the step function's copy of the tables
 
     def holds_nothing(self) -> bool:
         return self.state_slot < 0 and not any(self.block_tables)
@@ -224,8 +228,10 @@ class CacheManager:
             for page in seed:
                 pool.share(page)
                 table.append(page)
+                req.version += 1
             while len(table) < target:
                 table.append(pool.take_fresh())
+                req.version += 1
         return True
 
     def release_behind_window(self, req: RequestCache, num_computed: int) -> int:
@@ -238,6 +244,7 @@ class CacheManager:
                     pool.release(table[i])
                     table[i] = NULL_PAGE
                     count += 1
+        req.version += count
         return count
 
     def free(self, req: RequestCache) -> None:
@@ -249,6 +256,7 @@ class CacheManager:
                 if page != NULL_PAGE:
                     pool.release(page)
             table.clear()
+        req.version += 1
         req.page_hashes.clear()
         if req.state_slot >= 0:
             self.slots.give_back(req.state_slot)

@@ -216,6 +216,153 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (warp == 1) tcgen05_dealloc(tmem_base, C::TMEM_COLUMNS);
 }
 
+// ------------------------------------------- gated product for few tokens, gate on up stacked
+
+// act[t][n] = silu(x . w[n]) * (x . w[dual_row_offset + n]) for up to 64 tokens without splitting
+// the reduction: a CTA takes 64 gate rows and the 64 matching up rows as ONE 128-row operand (two
+// TMA boxes of 64 rows, one under the other), so a single MMA per k step fills accumulator rows
+// 0-63 with gate sums and 64-127 with up sums.  In the epilogue the two warps that hold the up
+// rows pass them through shared memory to the two that hold the gate rows, which apply SwiGLU
+// and write bfloat16: no partial sums in global memory and no separate activation kernel.
+// `map_w` has boxes of 64 rows.  grid (token tiles, ceil(outs / 64)).
+constexpr int STACK_ROWS = 64;
+
+// All of a product's CTAs (192 for 12,288 features) are resident at once, two per SM where they
+// do not go round, so the stages of each are what keeps loads in flight.
+template <int BLOCK_T>
+struct StackedConfig {
+    static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;  // 64 gate rows on 64 up rows
+    static constexpr int B_BYTES = BLOCK_T * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (100 * 1024) / STAGE_BYTES + (BLOCK_T == 16 ? 1 : 0);  // 6, 5, 4
+    static constexpr int TMEM_COLUMNS = BLOCK_T < 32 ? 32 : BLOCK_T;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BLOCK_T>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+    using C = StackedConfig<BLOCK_T>;
+    static_assert(BLOCK_T <= 64 && STACK_ROWS * BLOCK_T * 4 <= C::STAGES * C::STAGE_BYTES, "the exchange buffer reuses the stages");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* accum = empty + C::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.y * STACK_ROWS, t0 = blockIdx.x * BLOCK_T;
+    const int iterations = p.k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(tmem_holder, C::TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    constexpr int HALF_A = STACK_ROWS * BLOCK_K * 2;  // bytes of 64 rows of a k block
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_trigger();
+            const int early = min(iterations, C::STAGES);
+            for (int i = 0; i < early; ++i) {
+                uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
+                mbar_expect_tx(&full[i], C::STAGE_BYTES);
+                tma_load_2d(a_tile, &map_w, i * BLOCK_K, n0, &full[i]);
+                tma_load_2d(a_tile + HALF_A, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[i]);
+            }
+            pdl_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, t0, &full[i]);
+            int issued = early;
+            for (int i = early; i < iterations; ++i, ++issued) {
+                const int stage = i % C::STAGES;
+                if (!mbar_wait(&empty[stage], ((i / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (30 << 8) | stage); break; }
+                uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
+                mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+                tma_load_2d(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
+                tma_load_2d(a_tile + HALF_A, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, t0, &full[stage]);
+            }
+            if (issued < iterations || g_gemm_error != 0) {
+                for (int i = max(issued - C::STAGES, 0); i < issued; ++i)
+                    mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BLOCK_T);
+            for (int i = 0; i < iterations; ++i) {
+                const int stage = i % C::STAGES;
+                if (!mbar_wait(&full[stage], (i / C::STAGES) & 1)) { atomicCAS(&g_gemm_error, 0, (31 << 8) | stage); break; }
+                tcgen05_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+                const uint64_t a_desc = smem_desc_sw128(a_addr);
+                const uint64_t b_desc = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t step = static_cast<uint64_t>((k * UMMA_K * 2) >> 4);
+                    tcgen05_mma_bf16(tmem_base, a_desc + step, b_desc + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&empty[stage]);
+            }
+            tcgen05_commit(accum);
+        }
+    } else {
+        const int quarter = warp & 3;  // a warp may read TMEM lanes [32 * (warp % 4), +32): 0, 1 gate rows; 2, 3 up rows
+        pdl_wait();
+        bool ok = mbar_wait(accum, 0);
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (32 << 8));
+        ok = __all_sync(0xffffffffu, ok) && g_gemm_error == 0;
+        tcgen05_fence_after();
+        // All copies have landed and all MMAs have read them: the stages now carry the up sums,
+        // [token of the tile][feature of the 64].
+        float* exchange = reinterpret_cast<float*>(tiles);
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int feature = (quarter & 1) * 32 + lane;
+        if (ok && quarter >= 2) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BLOCK_T; c0 += 16) {
+                if (t0 + c0 >= p.tokens) break;
+                float up[16];
+                tcgen05_ld16(lane_base + c0, up);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) exchange[(c0 + c) * STACK_ROWS + feature] = up[c];
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (ok && quarter < 2) {
+            const int n = n0 + feature;
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BLOCK_T; c0 += 16) {
+                if (t0 + c0 >= p.tokens) break;
+                float gate[16];
+                tcgen05_ld16(lane_base + c0, gate);
+                if (n < p.outs) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int t = t0 + c0 + c;
+                        if (t < p.tokens) {
+                            const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                            out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * exchange[(c0 + c) * STACK_ROWS + feature]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem_base, C::TMEM_COLUMNS);
+}
+
 // ----------------------------------------------------------- CTA-pair kernel (many tokens)
 
 // For prompts, a pair of CTAs (a cluster of two, on the two SMs of a TPC) computes a tile of 256
@@ -801,6 +948,37 @@ ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void*
     if (block_t == 256) return launch<256, true>(w, x, p, 1, stream);  // both accumulators fill all 512 TMEM columns
     if (block_t == 128) return launch<128, true>(w, x, p, 1, stream);
     return ME_ERR_ARGUMENT;
+}
+
+template <int BLOCK_T>
+static int launch_stacked(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+    using C = StackedConfig<BLOCK_T>;
+    auto kernel = gemm_tcgen05_stacked_swiglu_kernel<BLOCK_T>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        configured = true;
+    }
+    dim3 grid((p.tokens + BLOCK_T - 1) / BLOCK_T, (p.outs + STACK_ROWS - 1) / STACK_ROWS, 1);
+    return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
+}
+
+// act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for few tokens (block_t 16,
+// 32 or 64), the reduction unsplit.  The weight map has boxes of 64 rows.
+ME_EXPORT int me_gemm_tcgen05_stacked_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
+                                             int inner, int dual_row_offset, int block_t, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0};
+    switch (block_t) {
+        case 16: return launch_stacked<16>(w, x, p, stream);
+        case 32: return launch_stacked<32>(w, x, p, stream);
+        case 64: return launch_stacked<64>(w, x, p, stream);
+        default: return ME_ERR_ARGUMENT;
+    }
 }
 
 // The first failure a kernel of this library recorded since the last call (0: none); clears it.

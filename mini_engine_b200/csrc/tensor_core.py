@@ -27,6 +27,7 @@ USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
 # "0" falls back to one tile per pair of CTAs.
 USE_PERSISTENT = os.environ.get("MINI_ENGINE_B200_PERSISTENT", "1") != "0"
 
+STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
 USE_PERSISTENT_GATED = os.environ.get("MINI_ENGINE_B200_PERSISTENT_GATED", "1") != "0"
 
 _lib = None
@@ -50,6 +51,8 @@ def _library():
         lib.me_gemm_tcgen05_persistent.restype = c_int
         lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
+        lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_gemm_take_error.restype = c_int
         _lib = lib
@@ -102,6 +105,8 @@ class GemmPlan:
         self.rows, self.inner = weight.shape
         self.dual_rows = dual_rows  # gate rows [0, dual_rows), up rows [dual_rows, 2 * dual_rows)
         self.map = _make_map(weight, BLOCK_N)
+        # Boxes of 64 rows, for the few-token gated kernel that stacks gate rows on up rows.
+        self.map_half = _make_map(weight, BLOCK_N // 2) if dual_rows is not None else None
 
 
 _activation_maps: dict[tuple[int, int, int, int], ctypes.Array] = {}
@@ -156,7 +161,13 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
-    if tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PERSISTENT_GATED:
+    if tokens <= STACKED_MAX_TOKENS:
+        tile = token_tile(tokens)
+        code = _library().me_gemm_tcgen05_stacked_swiglu(
+            plan.map_half, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
+            tile, stream,
+        )  # fmt: skip
+    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PERSISTENT_GATED:
         code = _library().me_gemm_tcgen05_persistent_swiglu(
             plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
         )

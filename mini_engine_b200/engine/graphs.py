@@ -79,6 +79,6 @@ class DecodeGraphs:
         """Logits ``[len(entries), vocab]``: one decoded token per entry, the logits of each."""
         real = len(entries)
         bucket = self.bucket_for(real)
-        self.runner.pack(entries, pad_entries_to=bucket, want_every_entry=True)
+        self.runner.pack(entries, pad_entries_to=bucket, want_every_entry=True, build_context=False)
         self.graphs[bucket].replay()
         return self.logits[bucket][:real]

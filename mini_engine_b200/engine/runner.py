@@ -80,17 +80,40 @@ class ModelRunner:
         self._copied = [torch.cuda.Event(), torch.cuda.Event()]  # the copy out of each pinned block
         self._flip = 0
         self.last_h2d_bytes = 0
+        # What each pinned block holds in its table region: where the region lies and, row by
+        # row, whose tables (request, version) were written there last.
+        self._row_layout: list[tuple[int, int] | None] = [None, None]
+        self._row_owners: list[dict[int, tuple[int, int] | None]] = [{}, {}]
 
     # ------------------------------------------------------------------ packing
 
+    def _tables_of(self, cache: RequestCache) -> list[np.ndarray]:
+        """The request's block tables as int32 rows of the device table's width, ``NULL_PAGE``
+        behind their ends; converted again only when the cache manager has changed them."""
+        held = cache.packed
+        if held is None or held[0] is not self or held[1] != cache.version:
+            rows = []
+            for table in cache.block_tables:
+                row = np.full(self.table_width, NULL_PAGE, dtype=np.int32)
+                row[: len(table)] = table
+                rows.append(row)
+            held = (self, cache.version, rows, [len(table) for table in cache.block_tables])
+            cache.packed = held
+        return held
+
     def pack(
-        self, entries: Seq[StepEntry], pad_entries_to: int | None = None, want_every_entry: bool = False
-    ) -> tuple[StepContext, torch.Tensor]:
+        self,
+        entries: Seq[StepEntry],
+        pad_entries_to: int | None = None,
+        want_every_entry: bool = False,
+        build_context: bool = True,
+    ) -> tuple[StepContext | None, torch.Tensor | None]:
         """Lay the batch out as int32 arrays on the device.  With ``pad_entries_to`` the batch
         is filled up with one-token dummy entries on the spare page (for a captured graph of
         that size); with ``want_every_entry`` the wanted rows are the last token of every entry,
         padding included, whatever the entries ask for.  Returns the context and the int32 row
-        numbers of the wanted logits."""
+        numbers of the wanted logits (both ``None`` without ``build_context``: a captured graph
+        reads the arrays where they always lie)."""
         real = len(entries)
         total_entries = max(real, pad_entries_to or 0)
         counts = [len(e.token_ids) for e in entries]
@@ -105,8 +128,9 @@ class ModelRunner:
             )
         g, bs, width = self.num_groups, self.block_size, self.table_width
         self._flip ^= 1
-        self._copied[self._flip].synchronize()  # the host may run ahead of the device by many steps
-        host = self._host_np[self._flip]
+        flip = self._flip
+        self._copied[flip].synchronize()  # the host may run ahead of the device by many steps
+        host = self._host_np[flip]
         offset = 0
 
         def take(n: int) -> tuple[np.ndarray, int]:
@@ -124,49 +148,98 @@ class ModelRunner:
         state, o_state = take(total_entries)
         fresh, o_fresh = take(total_entries)
         tables = [take(total_entries * width) for _ in range(g)]
-        wanted_rows: list[int] = []
+        table_rows = [t[0].reshape(total_entries, width) for t in tables]
+        # A pinned block keeps the table rows it was given: a row is written again only when its
+        # request, or that request's tables, differ from what the block holds at that place.
+        layout = (tables[0][1] if g else 0, total_entries)
+        owners = self._row_owners[flip]
+        if self._row_layout[flip] != layout:
+            self._row_layout[flip] = layout
+            owners.clear()
 
-        cursor = 0
-        cu[0] = 0
-        max_q = max_ctx = 1
-        for b, entry in enumerate(entries):
-            n = counts[b]
-            end = entry.start + n
-            if end > width * bs:
-                raise ValueError(f"request of {end} tokens exceeds max_model_len {width * bs}")
-            ids[cursor : cursor + n] = entry.token_ids
-            span = np.arange(entry.start, end, dtype=np.int32)
-            pos[cursor : cursor + n] = span
-            ent[cursor : cursor + n] = b
+        def put_row(b: int, cache: RequestCache | None, rows: list[np.ndarray] | None) -> None:
+            key = (cache.serial, cache.version) if cache is not None else None
+            if owners.get(b, 0) == key:
+                return
+            owners[b] = key
             for gi in range(g):
-                table = np.asarray(entry.cache.block_tables[gi], dtype=np.int32)
-                if table.shape[0] * bs < end:
-                    raise ValueError(f"entry {b}: block table covers {table.shape[0] * bs} tokens, {end} needed")
-                pages = table[span // bs]
+                if rows is None:
+                    table_rows[gi][b] = self.spare_page
+                else:
+                    table_rows[gi][b] = rows[gi]
+
+        wanted_rows: list[int] = []
+        starts = [e.start for e in entries]
+        if real_tokens == real:
+            # Every entry brings one token: the arrays are filled column-wise.
+            start_arr = np.array(starts, dtype=np.int32)
+            if int(start_arr.max()) >= width * bs:
+                raise ValueError(f"request of {int(start_arr.max()) + 1} tokens exceeds max_model_len {width * bs}")
+            ids[:real] = [e.token_ids[0] for e in entries]
+            pos[:real] = start_arr
+            ent[:real] = np.arange(real, dtype=np.int32)
+            page_index = start_arr // bs
+            for b, entry in enumerate(entries):
+                held = self._tables_of(entry.cache)
+                if held[3] and min(held[3]) <= page_index[b]:
+                    raise ValueError(f"entry {b}: block table covers {min(held[3]) * bs} tokens, {starts[b] + 1} needed")
+                put_row(b, entry.cache, held[2])
+                slot = entry.cache.state_slot
+                state[b] = slot if slot >= 0 else self.spare_slot
+                for place in entry.want:
+                    if place != 0:
+                        raise ValueError(f"entry {b}: wanted place {place} is outside its 1 tokens")
+                    wanted_rows.append(b)
+            lanes = np.arange(real)
+            for gi in range(g):
+                pages = table_rows[gi][lanes, page_index]
                 if (pages == NULL_PAGE).any():
-                    raise ValueError(f"entry {b}: a new token falls on a page that was given back")
-                slots[gi][0][cursor : cursor + n] = pages * bs + span % bs
-                row = tables[gi][0][b * width : (b + 1) * width]
-                row[: table.shape[0]] = table
-                row[table.shape[0] :] = NULL_PAGE
-            cu[b + 1] = cursor + n
-            ctx_len[b] = end
-            state[b] = entry.cache.state_slot if entry.cache.state_slot >= 0 else self.spare_slot
-            fresh[b] = 1 if entry.start == 0 else 0
-            for place in entry.want:
-                if not 0 <= place < n:
-                    raise ValueError(f"entry {b}: wanted place {place} is outside its {n} tokens")
-                wanted_rows.append(cursor + place)
-            max_q, max_ctx = max(max_q, n), max(max_ctx, end)
-            cursor += n
+                    raise ValueError("a new token falls on a page that was given back")
+                slots[gi][0][:real] = pages * bs + start_arr % bs
+            cu[: real + 1] = np.arange(real + 1, dtype=np.int32)
+            ctx_len[:real] = start_arr + 1
+            fresh[:real] = start_arr == 0
+            cursor = real
+            max_q, max_ctx = 1, int(start_arr.max()) + 1
+        else:
+            cursor = 0
+            cu[0] = 0
+            max_q = max_ctx = 1
+            for b, entry in enumerate(entries):
+                n = counts[b]
+                end = entry.start + n
+                if end > width * bs:
+                    raise ValueError(f"request of {end} tokens exceeds max_model_len {width * bs}")
+                ids[cursor : cursor + n] = entry.token_ids
+                span = np.arange(entry.start, end, dtype=np.int32)
+                pos[cursor : cursor + n] = span
+                ent[cursor : cursor + n] = b
+                held = self._tables_of(entry.cache)
+                put_row(b, entry.cache, held[2])
+                for gi in range(g):
+                    if held[3][gi] * bs < end:
+                        raise ValueError(f"entry {b}: block table covers {held[3][gi] * bs} tokens, {end} needed")
+                    pages = held[2][gi][span // bs]
+                    if (pages == NULL_PAGE).any():
+                        raise ValueError(f"entry {b}: a new token falls on a page that was given back")
+                    slots[gi][0][cursor : cursor + n] = pages * bs + span % bs
+                cu[b + 1] = cursor + n
+                ctx_len[b] = end
+                state[b] = entry.cache.state_slot if entry.cache.state_slot >= 0 else self.spare_slot
+                fresh[b] = 1 if entry.start == 0 else 0
+                for place in entry.want:
+                    if not 0 <= place < n:
+                        raise ValueError(f"entry {b}: wanted place {place} is outside its {n} tokens")
+                    wanted_rows.append(cursor + place)
+                max_q, max_ctx = max(max_q, n), max(max_ctx, end)
+                cursor += n
         if ids[:real_tokens].min() < 0 or ids[:real_tokens].max() >= self.vocab_size:
             raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
         for b in range(real, total_entries):  # padding: one token at position 0 of the spare page
             ids[cursor], pos[cursor], ent[cursor] = 0, 0, b
             for gi in range(g):
                 slots[gi][0][cursor] = self.spare_page * bs
-                row = tables[gi][0][b * width : (b + 1) * width]
-                row[:] = self.spare_page
+            put_row(b, None, None)
             cu[b + 1] = cursor + 1
             ctx_len[b], state[b], fresh[b] = 1, self.spare_slot, 1
             cursor += 1
@@ -184,9 +257,11 @@ class ModelRunner:
         rows_view[:] = wanted_rows
 
         used = offset
-        self._device[:used].copy_(self._host[self._flip][:used], non_blocking=True)
-        self._copied[self._flip].record()
+        self._device[:used].copy_(self._host[flip][:used], non_blocking=True)
+        self._copied[flip].record()
         self.last_h2d_bytes = used * 4
+        if not build_context:
+            return None, None
         dev = self._device
 
         def at(start: int, n: int) -> torch.Tensor:
@@ -214,8 +289,8 @@ class ModelRunner:
             decode_entries=at(o_kinds, len(decode_list)),
             portion_entries=at(o_kinds + len(decode_list), len(portion_list)),
             host={
-                "counts": counts + [1] * (total_entries - real),
-                "starts": [e.start for e in entries] + [0] * (total_entries - real),
+                "counts": all_counts,
+                "starts": starts + [0] * (total_entries - real),
                 "state_slots": [int(x) for x in state[:total_entries]],
             },
         )

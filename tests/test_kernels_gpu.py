@@ -95,7 +95,13 @@ def test_gemm_tensor_core_finds_one_large_product():
         assert int(out[0].argmax()) == t * outs + n
 
 
-@pytest.mark.parametrize("tokens,inter,inner", [(65, 160, 96), (128, 128, 64), (300, 300, 264), (2048, 2600, 136)])
+@pytest.mark.parametrize(
+    "tokens,inter,inner",
+    [
+        (1, 64, 64), (8, 200, 136), (17, 160, 520), (33, 100, 72), (64, 448, 264),  # gate rows stacked on up rows
+        (65, 160, 96), (128, 128, 64), (300, 300, 264), (2048, 2600, 136),
+    ],
+)  # fmt: skip
 def test_gemm_tensor_core_swiglu(tokens, inter, inner):
     from mini_engine_b200.csrc import tensor_core
 
