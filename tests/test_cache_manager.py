@@ -197,3 +197,21 @@ def test_pages_that_a_memory_budget_holds():
     with pytest.raises(ValueError, match="hold no KV page"):
         blocks_for_budget(needs, torch.bfloat16, 8, 2 * page - 1)
     assert blocks_for_budget([(None, StateSpec((4,)), None)], torch.float32, 8, 0) == 1
+
+
+def test_version_tells_when_a_copy_of_the_tables_is_stale():
+    manager = CacheManager([GroupSpec("full", None), GroupSpec("window", 8)], 16, 4, 4, enable_prefix_caching=False)
+    a, b = manager.new_request(), manager.new_request()
+    assert a.serial != b.serial
+    seen = a.version
+    assert manager.try_allocate(a, 3) and a.version > seen
+    seen = a.version
+    assert manager.try_allocate(a, 4) and a.version == seen  # still one page: nothing changed
+    assert manager.try_allocate(a, 20) and a.version > seen
+    seen = a.version
+    assert manager.release_behind_window(a, 20) > 0 and a.version > seen  # the window group gave pages back
+    seen = a.version
+    assert manager.release_behind_window(a, 20) == 0 and a.version == seen
+    manager.free(a)
+    assert a.version > seen
+    manager.check_invariants([b])
