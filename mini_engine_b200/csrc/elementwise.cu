@@ -82,16 +82,21 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
 // the listed rows are read and x is left alone.  out = weight * x_row * rsqrt(mean(x_row^2) + eps).
 // VEC: hidden is a multiple of 4 and every pointer is 16-byte aligned; all loads of a thread are
 // then issued before any of them is used, which is what matters when only a few rows run.
-// NORM_THREADS (256, 512 or 1024) is chosen from the width alone, so that a thread of the
-// vectorised path has one group of four columns where the width allows it and every load of the
-// row is in flight at once.
-template <typename OutT, bool VEC, int NORM_THREADS>
-__global__ void __launch_bounds__(NORM_THREADS)
+//
+// The sum of squares is defined over LANES "lanes" (256, 512 or 1024, chosen from the width
+// alone): lane v adds the squares of its columns 4v..4v+3 (+ 4 LANES j) in ascending order, the 32
+// lanes of a warp are added by a butterfly, and the warps' sums in ascending order.  A block of
+// THREADS = LANES threads has one lane per thread (every load of a short row in flight at once:
+// few rows); a block of THREADS < LANES threads plays LANES / THREADS lanes per thread with one
+// partial sum each, which gives the same bits with more blocks per SM (many rows).
+template <typename OutT, bool VEC, int LANES, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int splits, size_t split_stride,
                    const float* __restrict__ weight, float eps, OutT* __restrict__ out,
                    const int* __restrict__ rows, int hidden) {
+    constexpr int PLAYED = LANES / THREADS;  // lanes per thread
     extern __shared__ float row_cache[];  // [hidden]
-    __shared__ float warp_partial[NORM_THREADS / 32];
+    __shared__ float warp_partial[LANES / 32];
     const int out_row = blockIdx.x;
     pdl_trigger();
     // The norm's weight and the step's row list do not come from the previous kernel: fetch them
@@ -103,72 +108,99 @@ add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ pending, int
     float* x_row = x + static_cast<size_t>(src) * hidden;
     const float* pending_row = pending + static_cast<size_t>(src) * hidden;
     const bool write_back = !rows && splits > 0;
-    float sum_sq = 0.0f;
+    float sum_sq[PLAYED];
+#pragma unroll
+    for (int k = 0; k < PLAYED; ++k) sum_sq[k] = 0.0f;
     if (VEC && splits <= MAX_UNROLLED_SPLITS) {
-        for (int i = threadIdx.x * 4; i < hidden; i += NORM_THREADS * 4) {
-            float4 v = *reinterpret_cast<const float4*>(x_row + i);
-            float4 part[MAX_UNROLLED_SPLITS];
+        for (int base = 0; base < hidden; base += LANES * 4) {
 #pragma unroll
-            for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
-                if (s < splits) part[s] = *reinterpret_cast<const float4*>(pending_row + s * split_stride + i);
+            for (int k = 0; k < PLAYED; ++k) {
+                const int i = base + (k * THREADS + threadIdx.x) * 4;
+                if (i >= hidden) continue;
+                float4 v = *reinterpret_cast<const float4*>(x_row + i);
+                float4 part[MAX_UNROLLED_SPLITS];
 #pragma unroll
-            for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
-                if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
-            *reinterpret_cast<float4*>(row_cache + i) = v;
-            if (write_back) *reinterpret_cast<float4*>(x_row + i) = v;
-            sum_sq = fmaf(v.x, v.x, sum_sq);
-            sum_sq = fmaf(v.y, v.y, sum_sq);
-            sum_sq = fmaf(v.z, v.z, sum_sq);
-            sum_sq = fmaf(v.w, v.w, sum_sq);
+                for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+                    if (s < splits) part[s] = *reinterpret_cast<const float4*>(pending_row + s * split_stride + i);
+#pragma unroll
+                for (int s = 0; s < MAX_UNROLLED_SPLITS; ++s)
+                    if (s < splits) { v.x += part[s].x; v.y += part[s].y; v.z += part[s].z; v.w += part[s].w; }
+                *reinterpret_cast<float4*>(row_cache + i) = v;
+                if (write_back) *reinterpret_cast<float4*>(x_row + i) = v;
+                sum_sq[k] = fmaf(v.x, v.x, sum_sq[k]);
+                sum_sq[k] = fmaf(v.y, v.y, sum_sq[k]);
+                sum_sq[k] = fmaf(v.z, v.z, sum_sq[k]);
+                sum_sq[k] = fmaf(v.w, v.w, sum_sq[k]);
+            }
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += NORM_THREADS) {
-            float v = x_row[i];
-            for (int s = 0; s < splits; ++s) v += pending_row[s * split_stride + i];
-            row_cache[i] = v;
-            if (write_back) x_row[i] = v;
-            sum_sq = fmaf(v, v, sum_sq);
+        for (int base = 0; base < hidden; base += LANES) {
+#pragma unroll
+            for (int k = 0; k < PLAYED; ++k) {
+                const int i = base + k * THREADS + threadIdx.x;
+                if (i >= hidden) continue;
+                float v = x_row[i];
+                for (int s = 0; s < splits; ++s) v += pending_row[s * split_stride + i];
+                row_cache[i] = v;
+                if (write_back) x_row[i] = v;
+                sum_sq[k] = fmaf(v, v, sum_sq[k]);
+            }
         }
     }
-    sum_sq = warp_sum(sum_sq);
-    if ((threadIdx.x & 31) == 0) warp_partial[threadIdx.x >> 5] = sum_sq;
+#pragma unroll
+    for (int k = 0; k < PLAYED; ++k) {
+        const float warp_total = warp_sum(sum_sq[k]);
+        if ((threadIdx.x & 31) == 0) warp_partial[k * (THREADS / 32) + (threadIdx.x >> 5)] = warp_total;
+    }
     __syncthreads();
     float total = 0.0f;
 #pragma unroll
-    for (int w = 0; w < NORM_THREADS / 32; ++w) total += warp_partial[w];
+    for (int w = 0; w < LANES / 32; ++w) total += warp_partial[w];
     const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
     OutT* out_ptr = out + static_cast<size_t>(out_row) * hidden;
     if (VEC) {
-        for (int i = threadIdx.x * 4; i < hidden; i += NORM_THREADS * 4) {
+        for (int i = threadIdx.x * 4; i < hidden; i += THREADS * 4) {
             const float4 v = *reinterpret_cast<const float4*>(row_cache + i);
             const float4 w = i == threadIdx.x * 4 ? first_weight : *reinterpret_cast<const float4*>(weight + i);
             store4(out_ptr + i, make_float4(w.x * (v.x * inv), w.y * (v.y * inv), w.z * (v.z * inv), w.w * (v.w * inv)));
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += NORM_THREADS)
+        for (int i = threadIdx.x; i < hidden; i += THREADS)
             out_ptr[i] = from_float<OutT>(weight[i] * (row_cache[i] * inv));
     }
 }
 
-template <typename OutT, bool VEC, int NORM_THREADS>
+template <typename OutT, bool VEC, int LANES, int THREADS>
 static int launch_add_rmsnorm_threads(float* x, const float* pending, int splits, size_t split_stride,
                                       const float* weight, float eps, OutT* out, const int* rows, int count, int hidden,
                                       cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(hidden) * sizeof(float);
-    auto kernel = add_rmsnorm_kernel<OutT, VEC, NORM_THREADS>;
+    auto kernel = add_rmsnorm_kernel<OutT, VEC, LANES, THREADS>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel(kernel, count, NORM_THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
+    return launch_kernel(kernel, count, THREADS, smem, stream, x, pending, splits, split_stride, weight, eps, out,
                          rows, hidden);
+}
+
+// Few rows: one lane per thread.  Many rows: 256 threads per row, more rows per SM.  The lanes
+// (hence the bits of the result) depend on the width alone.
+constexpr int NORM_MANY_ROWS = 256;
+
+template <typename OutT, bool VEC, int LANES>
+static int launch_add_rmsnorm_lanes(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
+                                    float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
+    if (count >= NORM_MANY_ROWS)
+        return launch_add_rmsnorm_threads<OutT, VEC, LANES, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+    return launch_add_rmsnorm_threads<OutT, VEC, LANES, LANES>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
 }
 
 template <typename OutT, bool VEC>
 static int launch_add_rmsnorm(float* x, const float* pending, int splits, size_t split_stride, const float* weight,
                               float eps, OutT* out, const int* rows, int count, int hidden, cudaStream_t stream) {
     if (VEC && hidden > 2048)
-        return launch_add_rmsnorm_threads<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 1024>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
     if (VEC && hidden > 1024)
-        return launch_add_rmsnorm_threads<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
-    return launch_add_rmsnorm_threads<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+        return launch_add_rmsnorm_lanes<OutT, VEC, 512>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
+    return launch_add_rmsnorm_lanes<OutT, VEC, 256>(x, pending, splits, split_stride, weight, eps, out, rows, count, hidden, stream);
 }
 
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }

@@ -147,6 +147,25 @@ def test_add_rmsnorm(hidden, out_dtype):
     assert rel_error(plain, want_plain) < (1e-5 if out_dtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("hidden", [136, 1536, 4096, 5120, 2050])
+def test_add_rmsnorm_same_bits_for_few_and_many_rows(hidden):
+    """Many rows run with fewer threads per row than few rows do; a row's result must not tell."""
+    torch.manual_seed(5)
+    tokens = 300
+    x = torch.randn(tokens, hidden, device="cuda")
+    pending = torch.randn(2, tokens, hidden, device="cuda")
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    many = torch.empty(tokens, hidden, device="cuda")
+    ops().add_rmsnorm(x.clone(), pending, weight, 1e-6, many)
+    few = torch.empty(7, hidden, device="cuda")
+    ops().add_rmsnorm(x[:7].clone(), pending[:, :7].contiguous(), weight, 1e-6, few)
+    assert torch.equal(few, many[:7])
+    rows = torch.tensor([299, 5], device="cuda", dtype=torch.int32)
+    picked = torch.empty(2, hidden, device="cuda")
+    ops().add_rmsnorm(x.clone(), pending, weight, 1e-6, picked, rows)
+    assert torch.equal(picked, many[rows.long()])
+
+
 def test_embedding():
     table = torch.randn(50, 24, device="cuda").to(torch.bfloat16)
     ids = torch.tensor([3, 49, 0, 3], device="cuda", dtype=torch.int32)
