@@ -6,9 +6,11 @@
 //
 //   S = Q K^T      tcgen05.mma, A = Q tile and B = K tile from shared memory (K-major, 128-byte
 //                  swizzle as TMA wrote them), D = S in tensor memory columns [0, 128)
-//   P = softmax    128 threads, one query row each (tensor-memory lane = row): two passes over
-//                  S with tcgen05.ld (row maximum, then exp2 and row sum in float32); P is
-//                  rounded to bfloat16 and stored with tcgen05.st over the first 64 columns of S
+//   P = softmax    256 threads, two per query row (tensor-memory lane = row, 64 score columns
+//                  each): the scores are read once with tcgen05.ld and stay in registers for
+//                  the row maximum (the two threads of a row exchange theirs through shared
+//                  memory) and for exp2 and the row sum in float32; P is rounded to bfloat16 and
+//                  stored with tcgen05.st over the first 64 columns of S
 //   O += P V       tcgen05.mma with A = P read from tensor memory and B = V tile from shared
 //                  memory as an MN-major operand (V is [key][dim]: rows run along the reduction),
 //                  D = O in columns [128, 256), accumulated over the tiles
@@ -19,8 +21,9 @@
 // table; queries likewise.  Keys beyond the request's length are read from its last page (finite
 // values) and masked by position.
 //
-// Roles (192 threads): warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs, warps 2-5
-// are the softmax rows.  Shared memory is 96 KB and tensor memory 256 columns, so two CTAs share
+// Roles (320 threads): warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs, warps 2-9
+// are the softmax rows (a row's time is a chain of dependent instructions of one thread: two
+// threads per row halve it).  Shared memory is 96 KB and tensor memory 256 columns, so two CTAs share
 // an SM and one's softmax overlaps the other's products.  Every wait is bounded (see tcgen05.cuh).
 //
 // Formula and conventions as in attention_bf16.cu (YuvGev00/mini-engine:
@@ -31,7 +34,8 @@
 constexpr int TC_ROWS = 128;   // query rows per CTA
 constexpr int TC_KEYS = 128;   // keys per tile
 constexpr int TC_DIM = 128;    // head_dim
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;
+constexpr int TC_SOFTMAX_THREADS = 256;
 constexpr int TC_HALF_BYTES = 128 * 64 * 2;  // a 128-row, 64-column bfloat16 block
 constexpr int TC_TMEM_COLUMNS = 256;
 constexpr float TC_LOG2E = 1.4426950408889634f;
@@ -55,6 +59,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Named barrier 1 of the 256 softmax threads, which also tells every one of them whether any
+// arrived with `flag` set.
+__device__ __forceinline__ bool softmax_barrier_any(bool flag) {
+    uint32_t any;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "barrier.red.or.pred q, 1, 256, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(any)
+        : "r"(static_cast<uint32_t>(flag))
+        : "memory");
+    return any != 0;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -73,10 +92,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *v_full = bars + 3, *v_empty = bars + 4,
              *s_full = bars + 5, *p_full = bars + 6, *o_full = bars + 7;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+    float* exchange = reinterpret_cast<float*>(bars + 10);  // [2 tile parities][2 column halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Later blocks of a request see more keys: start them first.
-    const int head = blockIdx.y, q_block = gridDim.x - 1 - blockIdx.x;
+    // Later blocks of a request see more keys and take longer in proportion.  The grid is (heads,
+    // blocks, requests) and CTAs start in that order, so the longest blocks of all heads start
+    // first and the short ones fill the SMs' slots as they come free.
+    const int head = blockIdx.x, q_block = gridDim.y - 1 - blockIdx.y;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -85,7 +107,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(v_full, 1);
         mbar_init(v_empty, 1);
         mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        mbar_init(p_full, TC_SOFTMAX_THREADS);
         mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -184,37 +206,47 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     } else if (has_work) {
         // ------------------------------------------------------------------ softmax rows
-        const int quarter = warp & 3;  // this warp's tensor-memory lanes are [32 * quarter, +32)
+        const int quarter = warp & 3;      // this warp's tensor-memory lanes are [32 * quarter, +32)
+        const int half = (warp - 2) >> 2;  // its 64 of the 128 score (and output) columns
         const int row = quarter * 32 + lane;
         const int row_pos = pos0 + row;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float row_max = -INFINITY, row_sum = 0.0f;
+        const int col0 = half * 64;
+        float row_max = -INFINITY, row_sum = 0.0f;  // the maximum of the whole row; the sum of this thread's columns
+        // A wait that ran out must not leave other threads at a named barrier: a thread that saw
+        // one keeps walking to the next barrier, where all 256 learn of it and leave together.
         bool ok = true;
-        for (int j = 0; j < tiles_count && ok; ++j) {
+        int j = 0;
+        for (; j < tiles_count; ++j) {
             const uint32_t parity = j & 1;
-            ok = mbar_wait(s_full, parity);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { if (lane == 0) atomicCAS(&g_attention_error, 0, 3 << 8); break; }
+            ok = ok && mbar_wait(s_full, parity);
             tcgen05_fence_after();
-            const int first_key = j * TC_KEYS;
+            const int first_key = j * TC_KEYS + col0;
             // Only the last tile or two of a block hold keys that some row must not see; every other
             // tile takes the path without per-element position tests.
-            const bool masked_tile = first_key + TC_KEYS - 1 > pos0;
-            float tile_max = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float s[32];
-                tcgen05_ld32(tmem_s + lane_base + c * 32, s);
-                if (masked_tile) {
+            const bool masked_tile = j * TC_KEYS + TC_KEYS - 1 > pos0;
+            uint32_t raw[64];
+            tcgen05_ld32_nowait(tmem_s + lane_base + col0, raw);
+            tcgen05_ld32_nowait(tmem_s + lane_base + col0 + 32, raw + 32);
+            tcgen05_wait_ld();
+            tcgen05_pin32(raw);
+            tcgen05_pin32(raw + 32);
+            float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one of 64 links
+            if (masked_tile) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (first_key + c * 32 + i <= row_pos) tile_max = fmaxf(tile_max, s[i]);
-                } else {
+                for (int i = 0; i < 64; ++i)
+                    if (first_key + i <= row_pos) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) tile_max = fmaxf(tile_max, fmaxf(s[i], s[i + 1]));
-                }
+                for (int i = 0; i < 64; ++i) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
             }
-            tile_max *= p.scale_log2;  // the scale is positive: the maximum of the scaled scores
+            float tile_max = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
+            // The row's other thread: through shared memory, one named barrier per tile (the buffer
+            // alternates with the tile's parity, so a slot is read before it is written again).
+            float* slot = exchange + parity * 256;
+            slot[half * 128 + row] = tile_max;
+            if (softmax_barrier_any(!ok)) break;
+            tile_max = fmaxf(tile_max, slot[(half ^ 1) * 128 + row]) * p.scale_log2;  // the scale is positive
             const float new_max = fmaxf(row_max, tile_max);
             const float base = new_max == -INFINITY ? 0.0f : new_max;
             const float rescale = exp2f(row_max - base);  // 0 while the row has seen nothing
@@ -223,66 +255,60 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (j > 0) {
                 // O of the previous tiles must be complete before it is rescaled or added to.
                 ok = mbar_wait(o_full, parity ^ 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) { if (lane == 0) atomicCAS(&g_attention_error, 0, (3 << 8) | 1); break; }
                 tcgen05_fence_after();
                 if (__any_sync(0xffffffffu, rescale != 1.0f)) {
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
-                        float o[32];
-                        tcgen05_ld32(tmem_o + lane_base + c * 32, o);
+                        float o[16];
+                        tcgen05_ld16(tmem_o + lane_base + col0 + c * 16, o);
+                        uint32_t scaled[16];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= rescale;
-                        tcgen05_st32(tmem_o + lane_base + c * 32, o);
+                        for (int i = 0; i < 16; ++i) scaled[i] = __float_as_uint(o[i] * rescale);
+                        tcgen05_st16(tmem_o + lane_base + col0 + c * 16, scaled);
                     }
                 }
             }
             const float negative_base = -base;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                float s[32];
-                tcgen05_ld32(tmem_s + lane_base + c * 32, s);
+            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
-                if (masked_tile) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = first_key + c * 32 + i;
-                        const float p0 = key <= row_pos ? fast_exp2(fmaf(s[i], p.scale_log2, negative_base)) : 0.0f;
-                        const float p1 = key + 1 <= row_pos ? fast_exp2(fmaf(s[i + 1], p.scale_log2, negative_base)) : 0.0f;
-                        row_sum += p0 + p1;
-                        packed[i / 2] = pack_bf16x2(p0, p1);
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = first_key + c * 32 + i;
+                    float p0 = fast_exp2(fmaf(__uint_as_float(raw[c * 32 + i]), p.scale_log2, negative_base));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(raw[c * 32 + i + 1]), p.scale_log2, negative_base));
+                    if (masked_tile) {
+                        p0 = key <= row_pos ? p0 : 0.0f;
+                        p1 = key + 1 <= row_pos ? p1 : 0.0f;
                     }
-                } else {
-                    float partial = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = fast_exp2(fmaf(s[i], p.scale_log2, negative_base));
-                        const float p1 = fast_exp2(fmaf(s[i + 1], p.scale_log2, negative_base));
-                        partial += p0 + p1;
-                        packed[i / 2] = pack_bf16x2(p0, p1);
-                    }
-                    row_sum += partial;
+                    partial[(i >> 1) & 3] += p0 + p1;
+                    packed[i / 2] = pack_bf16x2(p0, p1);
                 }
-                // P chunk c covers columns [16 c, 16 c + 16): all of them were read above already.
-                tcgen05_st16(tmem_s + lane_base + c * 16, packed);
+                // P columns [16 (2 half + c), +16) hold keys [64 half + 32 c, +32).  Both threads of
+                // the row have read their scores (the barrier above) before either writes P over them.
+                tcgen05_st16(tmem_s + lane_base + (half * 2 + c) * 16, packed);
             }
+            row_sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
             tcgen05_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(p_full);
+            if (ok) mbar_arrive(p_full);
         }
-        if (ok) {
-            ok = mbar_wait(o_full, (tiles_count - 1) & 1);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok && lane == 0) atomicCAS(&g_attention_error, 0, (3 << 8) | 2);
-        }
+        if (j == tiles_count) ok = ok && mbar_wait(o_full, (tiles_count - 1) & 1);  // else: left at a barrier, all together
+        // The row's sum is the sum of its two threads' (one more exchange; every thread reaches it).
+        float* slot = exchange + (tiles_count & 1) * 256;
+        slot[half * 128 + row] = row_sum;
+        ok = !softmax_barrier_any(!ok || j < tiles_count);
+        if (!ok && threadIdx.x == 64) atomicCAS(&g_attention_error, 0, 3 << 8);
+        row_sum += slot[(half ^ 1) * 128 + row];
         if (ok) {
             tcgen05_fence_after();
             const float inv = 1.0f / row_sum;
-            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head) * TC_DIM;
+            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head) * TC_DIM + col0;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 float o[32];
-                tcgen05_ld32(tmem_o + lane_base + c * 32, o);  // collective: every lane takes part
+                tcgen05_ld32(tmem_o + lane_base + col0 + c * 32, o);  // collective: every lane takes part
                 if (row < rows_valid) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
@@ -320,14 +346,14 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     memcpy(&v, map_v, sizeof(v));
     TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
                    heads, kv_heads, page_size, table_width};
-    constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256;
+    constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return static_cast<int>(e);
         configured = true;
     }
-    dim3 grid((max_new_tokens + TC_ROWS - 1) / TC_ROWS, heads, entries);
+    dim3 grid(heads, (max_new_tokens + TC_ROWS - 1) / TC_ROWS, entries);
     return launch_kernel(attention_tcgen05_kernel, grid, TC_THREADS, SMEM, stream, q, k, v, p);
 }
 
