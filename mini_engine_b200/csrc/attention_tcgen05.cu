@@ -15,8 +15,10 @@
 //                  memory as an MN-major operand (V is [key][dim]: rows run along the reduction),
 //                  D = O in columns [128, 256), accumulated over the tiles
 //
-// When a row's maximum grows, O is rescaled in tensor memory (ld, multiply, st) before the next
-// P V product; a warp skips this when none of its rows changed.  Keys and values come from the
+// When the maximum of a row has grown by more than 2^8 over the value its probabilities are taken
+// relative to, O is rescaled in tensor memory (ld, multiply, st) before the next P V product;
+// otherwise the older reference stays (a probability may then exceed 1) and the softmax of a tile
+// waits for no product but its own scores.  Keys and values come from the
 // cache by TMA, one box per page and 64-dimension half, addressed through the request's block
 // table; queries likewise.  Keys beyond the request's length are read from its last page (finite
 // values) and masked by position.
@@ -90,8 +92,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint8_t* v_tile = tiles + 4 * TC_HALF_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + 6 * TC_HALF_BYTES);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *v_full = bars + 3, *v_empty = bars + 4,
-             *s_full = bars + 5, *p_full = bars + 6, *o_full = bars + 7;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 8);
+             *s_full = bars + 5, *p_full = bars + 6, *o_full = bars + 7;  // o_full: two, by the tile's parity
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 9);
     float* exchange = reinterpret_cast<float*>(bars + 10);  // [2 tile parities][2 column halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,6 +111,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(s_full, 1);
         mbar_init(p_full, TC_SOFTMAX_THREADS);
         mbar_init(o_full, 1);
+        mbar_init(o_full + 1, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tcgen05_alloc(tmem_holder, TC_TMEM_COLUMNS);
@@ -179,8 +182,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!ok) atomicCAS(&g_attention_error, 0, 2 << 8);
             for (int j = 0; j < tiles_count && ok; ++j) {
                 const uint32_t parity = j & 1;
-                // The S columns are free once the previous P V product has read P out of them.
-                ok = mbar_wait(k_full, parity) && (j == 0 || mbar_wait(o_full, parity ^ 1));
+                // The S columns are free once the previous P V product has read P out of them: the
+                // MMAs of a CTA execute in the order of their issue, so this one needs no wait for it.
+                ok = mbar_wait(k_full, parity);
                 if (!ok) { atomicCAS(&g_attention_error, 0, (2 << 8) | 1); break; }
                 tcgen05_fence_after();
 #pragma unroll
@@ -200,7 +204,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     const uint64_t v_desc = smem_desc_sw128_mn(smem_u32(v_tile) + kk * 16 * 128, TC_HALF_BYTES);
                     tcgen05_mma_bf16_ts(tmem_o, tmem_s + kk * 8, v_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                tcgen05_commit(o_full);
+                tcgen05_commit(o_full + (j & 1));
                 tcgen05_commit(v_empty);
             }
         }
@@ -247,27 +251,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             slot[half * 128 + row] = tile_max;
             if (softmax_barrier_any(!ok)) break;
             tile_max = fmaxf(tile_max, slot[(half ^ 1) * 128 + row]) * p.scale_log2;  // the scale is positive
+            // The row's reference value `row_max` follows its true maximum lazily: only when the
+            // maximum of some row of the warp has grown by more than 2^8 is O rescaled (and the
+            // second product of the tile before waited for); until then probabilities are taken
+            // relative to the older reference and may exceed 1, which float32 sums and bfloat16's
+            // range hold with room to spare.  Both threads of a row decide alike: their warps
+            // hold the same rows.
             const float new_max = fmaxf(row_max, tile_max);
-            const float base = new_max == -INFINITY ? 0.0f : new_max;
-            const float rescale = exp2f(row_max - base);  // 0 while the row has seen nothing
-            row_sum *= rescale;
-            row_max = new_max;
-            if (j > 0) {
-                // O of the previous tiles must be complete before it is rescaled or added to.
-                ok = mbar_wait(o_full, parity ^ 1);
+            if (j == 0) {
+                row_max = new_max;
+            } else if (__any_sync(0xffffffffu, new_max - row_max > 8.0f)) {
+                ok = ok && mbar_wait(o_full + ((j - 1) & 1), ((j - 1) >> 1) & 1);  // the MMAs run in order: all of O is complete
                 tcgen05_fence_after();
-                if (__any_sync(0xffffffffu, rescale != 1.0f)) {
+                const float rescale = exp2f(row_max - new_max);
+                row_sum *= rescale;
+                row_max = new_max;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        float o[16];
-                        tcgen05_ld16(tmem_o + lane_base + col0 + c * 16, o);
-                        uint32_t scaled[16];
+                for (int c = 0; c < 4; ++c) {
+                    float o[16];
+                    tcgen05_ld16(tmem_o + lane_base + col0 + c * 16, o);
+                    uint32_t scaled[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) scaled[i] = __float_as_uint(o[i] * rescale);
-                        tcgen05_st16(tmem_o + lane_base + col0 + c * 16, scaled);
-                    }
+                    for (int i = 0; i < 16; ++i) scaled[i] = __float_as_uint(o[i] * rescale);
+                    tcgen05_st16(tmem_o + lane_base + col0 + c * 16, scaled);
                 }
             }
+            const float base = row_max == -INFINITY ? 0.0f : row_max;
             const float negative_base = -base;
             float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -294,7 +303,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tcgen05_fence_before();
             if (ok) mbar_arrive(p_full);
         }
-        if (j == tiles_count) ok = ok && mbar_wait(o_full, (tiles_count - 1) & 1);  // else: left at a barrier, all together
+        if (j == tiles_count)  // else: left at a barrier, all together
+            ok = ok && mbar_wait(o_full + ((tiles_count - 1) & 1), ((tiles_count - 1) >> 1) & 1);
         // The row's sum is the sum of its two threads' (one more exchange; every thread reaches it).
         float* slot = exchange + (tiles_count & 1) * 256;
         slot[half * 128 + row] = row_sum;

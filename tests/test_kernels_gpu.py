@@ -262,10 +262,12 @@ def attention_reference(q, k, v, scale, window=None):
     return out
 
 
-def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None, stale=None):
+def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None, stale=None, ramp=None):
     """Sequences of the given lengths in scattered pages; the last ``new_counts[i]`` tokens of
     each are the batch's queries.  Returns kernel inputs and the expected output rows.  Slots that
-    no sequence owns hold random numbers, or ``stale`` when given."""
+    no sequence owns hold random numbers, or ``stale`` when given.  With ``ramp`` the scores of
+    every query grow steadily with the key's position (by ``ramp`` per key before the softmax
+    scale), so that a running maximum keeps growing from tile to tile."""
     g = torch.Generator().manual_seed(seed)
     total_pages = sum(-(-n // page) for n in lengths) + 3
     order = torch.randperm(total_pages, generator=g).tolist()
@@ -281,6 +283,9 @@ def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed
         q = torch.randn(n, heads, head_dim, generator=g).to(dtype)
         k = torch.randn(n, kv_heads, head_dim, generator=g).to(dtype)
         v = torch.randn(n, kv_heads, head_dim, generator=g).to(dtype)
+        if ramp is not None:
+            k[:, :, 0] += ramp * torch.arange(n, dtype=torch.float32)[:, None] / 4.0
+            q[:, :, 0] = 4.0
         if spike is not None and n > spike[1]:
             # one far key answers one late query loudly: it must be found among hundreds
             query_pos, key_pos = n - 1, spike[1]
@@ -454,6 +459,24 @@ def test_paged_attention_tcgen05(case):
         head_dim, head_dim**-0.5, 0,
     )  # fmt: skip
     assert attention_bf16.take_error() == 0
+    assert rel_error(out.cpu(), data["want"]) < 1e-2
+
+
+@pytest.mark.parametrize("ramp", [0.04, 0.3, 2.0])
+def test_paged_attention_tcgen05_growing_maximum(ramp):
+    """The kernel rescales its output lazily, when a row's maximum has outgrown the value its
+    probabilities are taken relative to: scores that grow slowly, quickly and very quickly."""
+    from mini_engine_b200.csrc import attention_bf16
+
+    lengths, news, heads, kv_heads, head_dim, page = [1500, 300], [1400, 300], 4, 2, 128, 16
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=15, ramp=ramp)
+    out = torch.full_like(data["q"], float("nan"))
+    attention_bf16.paged_attention(
+        data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
+        head_dim, head_dim**-0.5, 0,
+    )  # fmt: skip
+    assert attention_bf16.take_error() == 0
+    assert torch.isfinite(out).all()
     assert rel_error(out.cpu(), data["want"]) < 1e-2
 
 
