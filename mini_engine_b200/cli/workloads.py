@@ -1,6 +1,6 @@
 """The reference's end-to-end workloads with seeded synthetic tokens and random weights.
 
-    python -m mini_engine_b200.cli.workloads [--layers N]
+    python -m mini_engine_b200.cli.workloads [--size 0.6b|32b] [--layers N]
 
 Shapes follow benchmarks/bench.py:56-62,113-123 of YuvGev00/mini-engine (Qwen3-0.6B layer sizes;
 ``block_size 16, num_blocks 2048, max_num_seqs 64, max_num_batched_tokens 8192, max_model_len
@@ -10,6 +10,12 @@ scheduling):
 * throughput: 64 requests, 256-token prompts, 128 output tokens each;
 * prefix: 64 requests that share a 512-token prefix plus 32 tokens of their own, 64 output tokens,
   one request first and the other 63 together, with the prefix cache on and off.
+
+With ``--size 32b`` (Qwen3-32B layer sizes, 65 GB of random bfloat16 weights) it runs the mixed
+workload instead: steps of 8 prompt portions of 512 tokens beside 32 single decoded tokens at
+4,096-token contexts, device-timed through the step function (the decoding requests' pages hold
+random keys and values rather than computed ones); and the same mix through the scheduler with a
+page pool too small for all requests, so that it has to preempt.
 
 Token ids are uniform random from a fixed seed (the reference draws its prompts the same way,
 benchmarks/bench.py:52-53).
@@ -26,11 +32,107 @@ import time
 import torch
 
 
+def mixed_32b(layers: int) -> int:
+    """8 prompt portions of 512 tokens beside 32 decoded tokens at 4,096-token contexts."""
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.config import Qwen3Config
+    from mini_engine_b200.engine.runner import StepEntry
+
+    cfg = Qwen3Config(
+        vocab_size=151936, hidden_size=5120, intermediate_size=25600, num_hidden_layers=layers,
+        num_attention_heads=64, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
+        max_position_embeddings=40960, tie_word_embeddings=False,
+    )  # fmt: skip
+    rng = random.Random(0)
+
+    def ids(n: int) -> list[int]:
+        return [rng.randrange(100, cfg.vocab_size) for _ in range(n)]
+
+    decodes, prompts, context, portion, steps = 32, 8, 4096, 512, 8
+    engine = LLMEngine.from_random(
+        cfg, 0,
+        EngineConfig(block_size=16, num_blocks=decodes * (context // 16 + 2) + prompts * 64 + 8, max_num_seqs=64,
+                     max_num_batched_tokens=8192, max_model_len=8192, dtype=torch.bfloat16, cuda_graphs=False),
+    )  # fmt: skip
+    runner, manager = engine.runner, engine.block_manager
+    for array in runner.layout.arrays:
+        array.normal_()  # the decoding requests' contexts: random keys and values
+    deep = [manager.new_request() for _ in range(decodes)]
+    fresh = [manager.new_request() for _ in range(prompts)]
+    for cache in deep:
+        assert manager.try_allocate(cache, context + 2 * steps + 2)
+    for cache in fresh:
+        assert manager.try_allocate(cache, 2 * portion)
+    texts = [ids(2 * portion) for _ in range(prompts)]
+    position = context
+
+    def mixed_step(first_half: bool) -> None:
+        nonlocal position
+        lo = 0 if first_half else portion
+        entries = [StepEntry(c, position, ids(1), (0,)) for c in deep]
+        entries += [StepEntry(c, lo, t[lo : lo + portion], (portion - 1,) if not first_half else ()) for c, t in zip(fresh, texts)]
+        runner.execute(entries)
+        position += 1
+
+    for i in range(2):
+        mixed_step(i % 2 == 0)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(2 * steps):
+        mixed_step(i % 2 == 0)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / (2 * steps)
+    tokens = decodes + prompts * portion
+    per_layer = cfg.hidden_size * (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    per_layer += cfg.num_attention_heads * cfg.head_dim * cfg.hidden_size + 3 * cfg.hidden_size * cfg.intermediate_size
+    gemm_tflop = 2.0 * tokens * per_layer * layers / 1e12
+    kv_gb = decodes * (context + steps) * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * layers / 1e9
+    print(json.dumps({
+        "workload": "mixed step, 32B sizes", "layers": layers, "tokens_per_step": tokens, "ms_per_step": round(ms, 3),
+        "tokens_per_second": round(tokens / ms * 1e3, 1), "gemm_tflops": round(gemm_tflop / ms * 1e3, 1),
+        "kv_gb_read_per_step": round(kv_gb, 2),
+    }), flush=True)  # fmt: skip
+    for cache in deep + fresh:
+        manager.free(cache)
+    manager.check_invariants([])
+    del engine, runner, manager, deep, fresh, mixed_step
+    torch.cuda.empty_cache()
+
+    # The same mix through the scheduler, with too few pages for all requests at once.
+    engine = LLMEngine.from_random(
+        cfg, 0,
+        EngineConfig(block_size=16, num_blocks=1400, max_num_seqs=64, max_num_batched_tokens=portion + decodes,
+                     max_model_len=2048, dtype=torch.bfloat16, enable_prefix_caching=False),
+    )  # fmt: skip
+    params = SamplingParams(max_tokens=96, ignore_eos=True)
+    requests = [ids(512) for _ in range(decodes)] + [ids(1024) for _ in range(prompts)]
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    outputs = engine.generate(requests, params)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - began
+    produced = sum(len(o) for o in outputs)
+    engine.block_manager.check_invariants([])
+    print(json.dumps({
+        "workload": "32 x 512 in + 8 x 1,024 in, 96 out each, portions of 512, 1,400 pages", "layers": layers,
+        "output_tokens": produced, "seconds": round(elapsed, 3), "tokens_per_second": round(produced / elapsed, 1),
+        "steps": engine.stats.steps, "graph_steps": engine.stats.graph_steps,
+        "preemptions": engine.scheduler.num_preemptions,
+    }), flush=True)  # fmt: skip
+    return 0
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--layers", type=int, default=28)
+    parser.add_argument("--size", choices=["0.6b", "32b"], default="0.6b")
+    parser.add_argument("--layers", type=int, default=0, help="0: all layers of the size (28 or 64)")
     parser.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
     args = parser.parse_args(argv)
+    if args.size == "32b":
+        return mixed_32b(args.layers or 64)
+    args.layers = args.layers or 28
 
     from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
     from mini_engine_b200.config import Qwen3Config

@@ -82,6 +82,7 @@ class ModelRunner:
         self.last_h2d_bytes = 0
         # What each pinned block holds in its table region: where the region lies and, row by
         # row, whose tables (request, version) were written there last.
+        self._token = object()  # marks the copies of block tables that this runner made (no reference back to it)
         self._row_layout: list[tuple[int, int] | None] = [None, None]
         self._row_owners: list[dict[int, tuple[int, int] | None]] = [{}, {}]
 
@@ -91,13 +92,13 @@ class ModelRunner:
         """The request's block tables as int32 rows of the device table's width, ``NULL_PAGE``
         behind their ends; converted again only when the cache manager has changed them."""
         held = cache.packed
-        if held is None or held[0] is not self or held[1] != cache.version:
+        if held is None or held[0] is not self._token or held[1] != cache.version:
             rows = []
             for table in cache.block_tables:
                 row = np.full(self.table_width, NULL_PAGE, dtype=np.int32)
                 row[: len(table)] = table
                 rows.append(row)
-            held = (self, cache.version, rows, [len(table) for table in cache.block_tables])
+            held = (self._token, cache.version, rows, [len(table) for table in cache.block_tables])
             cache.packed = held
         return held
 
