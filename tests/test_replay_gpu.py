@@ -37,6 +37,7 @@ def requests_for(name: str, vocab: int) -> dict[str, list[int]]:
 
 def expected_logits(folder, dtype_name, requests):
     weights, cfg = load_plain(folder)
+    weights = {k: v.to(torch.float32) for k, v in weights.items()}  # a folder stored in bfloat16 widens exactly
     if dtype_name == "bfloat16":
         weights = {k: v.to(torch.bfloat16).to(torch.float32) for k, v in weights.items()}
     return {name: plain.forward_logits(weights, cfg, toks) for name, toks in requests.items()}
@@ -79,6 +80,37 @@ def test_schedules_match_plain(name, dtype_name, schedule, model_folders):
     steps = getattr(schedules, schedule)(requests)
     got = run_in_process(folder, dtype_name, steps, PAGE_SIZE[name])
     compare(got, expected_logits(folder, dtype_name, requests), requests, TOLERANCE[dtype_name])
+
+
+@pytest.fixture(scope="module")
+def layer_of_8b_folder(tmp_path_factory):
+    from conftest import make_model_folder
+    from tiny_configs import LAYER_OF_8B
+
+    return make_model_folder(tmp_path_factory, "8B", seed=13, dtype=torch.bfloat16, raw=LAYER_OF_8B)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_one_layer_of_real_sizes(dtype_name, layer_of_8b_folder):
+    """Qwen3-8B's layer sizes: a 300-token request whole (the CTA-pair products in bfloat16), a
+    150-token one in changing portions and a 70-token one with its tail decoded one by one
+    (split and stacked products), against the plain implementation; in float32 the cuts give
+    the same bits as the whole."""
+    folder = layer_of_8b_folder
+    _, cfg = load_plain(folder)
+    requests = {"whole": random_ids(401, 300, cfg["vocab"]), "cut": random_ids(402, 150, cfg["vocab"]),
+                "tail": random_ids(403, 70, cfg["vocab"])}  # fmt: skip
+    expected = expected_logits(folder, dtype_name, requests)
+    steps = schedules.whole({"whole": requests["whole"]})
+    got = run_in_process(folder, dtype_name, steps, PAGE_SIZE["8B"])
+    for maker, name in ((schedules.changing_portions, "cut"), (schedules.tail_one_by_one, "tail")):
+        got.update(run_in_process(folder, dtype_name, maker({name: requests[name]}), PAGE_SIZE["8B"]))
+    compare(got, expected, requests, TOLERANCE[dtype_name])
+    if dtype_name == "float32":
+        again = run_in_process(folder, dtype_name, schedules.whole({"cut": requests["cut"], "tail": requests["tail"]}), PAGE_SIZE["8B"])
+        for name in ("cut", "tail"):
+            for position, row in again[name].items():
+                assert torch.equal(row, got[name][position]), f"{name} position {position} differs between cuts"
 
 
 @pytest.mark.parametrize("name", ["A", "B"])

@@ -80,7 +80,27 @@ TINY_D = {
     "max_position_embeddings": 2048,
     "hidden_act": "silu",
 }
-PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32}
+# One layer of Qwen3-8B's sizes (hidden 4096, 32 / 8 heads of 128, intermediate 12288) under a
+# small vocabulary: the products, norms and attention run at the sizes the benchmark runs them,
+# the CTA-pair kernels and their split and stacked relatives included, against the plain
+# implementation.  Not in CONFIGS: only the tests that ask for it by name pay for it.
+LAYER_OF_8B = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "model_type": "qwen3",
+    "num_hidden_layers": 1,
+    "hidden_size": 4096,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "intermediate_size": 12288,
+    "vocab_size": 1000,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False,
+    "max_position_embeddings": 4096,
+    "hidden_act": "silu",
+}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 16, "D": 32, "8B": 16}
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
