@@ -76,6 +76,13 @@ __device__ __forceinline__ bool softmax_barrier_any(bool flag) {
     return any != 0;
 }
 
+// max(a, b, c) in one instruction.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -242,7 +249,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     if (first_key + i <= row_pos) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
+                for (int i = 0; i < 64; i += 2)  // two scores per instruction
+                    best[(i >> 1) & 3] = fmax3(best[(i >> 1) & 3], __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
             }
             float tile_max = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3]));
             // The row's other thread: through shared memory, one named barrier per tile (the buffer
@@ -277,28 +285,36 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
             const float base = row_max == -INFINITY ? 0.0f : row_max;
-            const float negative_base = -base;
-            float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // exp2(score * scale - base) for two scores at a time: the multiply-add and the sum use
+            // the two-wide float32 instructions, so a pair costs one fma, two ex2, one add, one pack.
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(-base, -base);
+            float2 partial[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
+                if (masked_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = first_key + c * 32 + i;
-                    float p0 = fast_exp2(fmaf(__uint_as_float(raw[c * 32 + i]), p.scale_log2, negative_base));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(raw[c * 32 + i + 1]), p.scale_log2, negative_base));
-                    if (masked_tile) {
-                        p0 = key <= row_pos ? p0 : 0.0f;
-                        p1 = key + 1 <= row_pos ? p1 : 0.0f;
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = first_key + c * 32 + i;
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
+                        const float2 pr = make_float2(key <= row_pos ? fast_exp2(x.x) : 0.0f, key + 1 <= row_pos ? fast_exp2(x.y) : 0.0f);
+                        partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
                     }
-                    partial[(i >> 1) & 3] += p0 + p1;
-                    packed[i / 2] = pack_bf16x2(p0, p1);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
+                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                    }
                 }
                 // P columns [16 (2 half + c), +16) hold keys [64 half + 32 c, +32).  Both threads of
                 // the row have read their scores (the barrier above) before either writes P over them.
                 tcgen05_st16(tmem_s + lane_base + (half * 2 + c) * 16, packed);
             }
-            row_sum += (partial[0] + partial[1]) + (partial[2] + partial[3]);
+            row_sum += (partial[0].x + partial[0].y) + (partial[1].x + partial[1].y);
             tcgen05_wait_st();
             tcgen05_fence_before();
             if (ok) mbar_arrive(p_full);
