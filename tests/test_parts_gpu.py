@@ -1,7 +1,7 @@
 """Each part of a layer alone against the plain implementation, at sizes of its own; models
 whose order repeats a layer, reads another entry's cache or uses a window; and a toy mixer
 with state of its own that is registered, built and stepped from here without touching the
-framework's files."""
+framework's files; likewise a toy position encoding and a toy routed feed-forward."""
 
 from __future__ import annotations
 
@@ -370,3 +370,112 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     assert torch.allclose(got[1], torch.cat([want_a[4:5], want_b[:3]]), atol=1e-4, rtol=1e-4)
     assert torch.allclose(got[2], torch.cat([want_b[3:], want_a[5:]]), atol=1e-4, rtol=1e-4)
     assert torch.allclose(got[3], want_b, atol=1e-4, rtol=1e-4)
+
+
+# ------------------------------ a toy position encoding and a toy routed feed-forward
+
+
+def test_toy_position_encoding_is_registered_and_applied():
+    """A position encoding that is no rotation (queries grow and keys shrink with the position, so
+    their product falls with the distance), defined here: the attention mixer then runs its
+    norm, the encoding's own `apply` and the cache write as three steps."""
+    from mini_engine_b200.config.model_spec import PartSpec
+    from mini_engine_b200.parts.base import POSITION_ENCODINGS, PositionEncoding, register
+
+    if "toy_distance_decay" not in POSITION_ENCODINGS:
+
+        @register("position_encoding", "toy_distance_decay")
+        class ToyDistanceDecay(PositionEncoding):
+            def __init__(self, prefix, hidden_size, *, head_dim, rate):
+                self.rates = rate * torch.arange(1, head_dim + 1, dtype=torch.float32, device="cuda") / head_dim
+
+            def apply(self, q, k, positions):
+                grow = torch.exp(positions.float()[:, None, None] * self.rates)
+                q.copy_((q.float() * grow).to(q.dtype))
+                k.copy_((k.float() / grow).to(k.dtype))
+
+    base = one_layer_spec(**SIZES)
+    layer = base.layers[0]
+    params = {**layer.mixer.params, "position_encoding": PartSpec("toy_distance_decay", {"head_dim": 16, "rate": 0.05})}
+    spec = type(base)(**{**base.__dict__, "layers": (type(layer)(**{**layer.__dict__, "mixer": PartSpec(layer.mixer.kind, params)}),)})
+    model, runner, manager, host = make_runner(spec)
+    tokens = [7, 3, 9, 1, 4, 4, 8, 2, 6, 5, 10, 12, 11, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+
+    cfg, w, p = plain_cfg(**SIZES), host, "model.layers.0."
+    t, d, pos = len(tokens), cfg["head_dim"], torch.arange(len(tokens), dtype=torch.float32)
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    normed = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+    q = plain.rms_norm((normed @ w[p + "self_attn.q_proj.weight"].T).view(t, cfg["heads"], d), w[p + "self_attn.q_norm.weight"], cfg["eps"])
+    k = plain.rms_norm((normed @ w[p + "self_attn.k_proj.weight"].T).view(t, cfg["kv_heads"], d), w[p + "self_attn.k_norm.weight"], cfg["eps"])
+    v = (normed @ w[p + "self_attn.v_proj.weight"].T).view(t, cfg["kv_heads"], d)
+    grow = torch.exp(pos[:, None, None] * (0.05 * torch.arange(1, d + 1, dtype=torch.float32) / d))
+    x = x + plain.causal_attention(q * grow, k / grow, v).reshape(t, -1) @ w[p + "self_attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+    want = plain.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
+
+
+def test_toy_routed_feed_forward_is_registered_and_stepped():
+    """A feed-forward with routing, defined here: each token goes to the one of three small
+    experts whose router logit (32-bit, per token) is largest."""
+    from mini_engine_b200.config.model_spec import PartSpec
+    from mini_engine_b200.parts.base import FEED_FORWARDS, FeedForward, register
+    from mini_engine_b200.weights.loader import WeightSpec
+
+    if "toy_top1_experts" not in FEED_FORWARDS:
+
+        @register("feed_forward", "toy_top1_experts")
+        class ToyTop1Experts(FeedForward):
+            def __init__(self, prefix, hidden_size, *, experts, width):
+                self.prefix, self.hidden, self.experts, self.width = prefix + "moe.", hidden_size, experts, width
+
+            def weight_specs(self):
+                specs = [WeightSpec(self.prefix + "router.weight", (self.experts, self.hidden))]
+                for e in range(self.experts):
+                    specs.append(WeightSpec(f"{self.prefix}{e}.in.weight", (self.width, self.hidden)))
+                    specs.append(WeightSpec(f"{self.prefix}{e}.out.weight", (self.hidden, self.width)))
+                return specs
+
+            def load(self, tensors):
+                self.w = {spec.name: tensors[spec.name].float() for spec in self.weight_specs()}
+
+            def forward(self, h, ctx):
+                # token by token, so that a token's result cannot depend on what else is in the
+                # batch (a library product over all rows may add in another order for another
+                # number of rows)
+                x = h.float()
+                out = torch.zeros(1, x.shape[0], self.hidden, device=x.device)
+                for i in range(x.shape[0]):
+                    e = int((self.w[self.prefix + "router.weight"] @ x[i]).argmax())
+                    hidden = torch.relu(self.w[f"{self.prefix}{e}.in.weight"] @ x[i])
+                    out[0, i] = self.w[f"{self.prefix}{e}.out.weight"] @ hidden
+                return out
+
+    base = one_layer_spec(**SIZES, layers=2)
+    routed = PartSpec("toy_top1_experts", {"experts": 3, "width": 20})
+    second = base.layers[1]
+    layers = (base.layers[0], type(second)(**{**second.__dict__, "feed_forward": routed}))  # dense, then routed
+    spec = type(base)(**{**base.__dict__, "layers": layers})
+    model, runner, manager, host = make_runner(spec)
+    tokens = [5, 40, 13, 2, 2, 31, 8, 19, 44, 6, 27, 3, 9, 9, 1]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+
+    cfg, w = plain_cfg(**SIZES, layers=2), host
+    x = w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    x = plain.decoder_layer(x, w, 0, cfg, torch.arange(len(tokens)))
+    p = "model.layers.1."
+    normed = plain.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+    x = x + plain.attention_block(normed, w, p + "self_attn.", cfg, torch.arange(len(tokens)))
+    normed = plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+    choice = (normed @ w[p + "moe.router.weight"].T).argmax(-1)
+    assert len(set(choice.tolist())) > 1, "the test wants tokens on different experts"
+    routed_out = torch.stack([
+        torch.relu(normed[i] @ w[f"{p}moe.{int(e)}.in.weight"].T) @ w[f"{p}moe.{int(e)}.out.weight"].T
+        for i, e in enumerate(choice)
+    ])  # fmt: skip
+    x = x + routed_out
+    want = plain.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
