@@ -18,10 +18,16 @@ from ctypes import c_float, c_int, c_void_p
 
 import torch
 
+from mini_engine_b200.csrc import ops, tensor_core
 from mini_engine_b200.csrc.build import load_library
 
 DECODE_CHUNK = 128
 TENSOR_MEMORY_MIN_TOKENS = 32  # portions at least this long take the tcgen05 kernel
+
+def _ops_stream() -> c_void_p:
+    return ops._stream()
+
+
 _lib = None
 _tc_lib = None
 _page_maps: dict[tuple[int, tuple[int, ...], int], object] = {}
@@ -62,8 +68,6 @@ def take_error() -> int:
 def _page_map(pages: torch.Tensor, box_rows: int | None = None):
     """TMA descriptor of a page array seen as [(pages * kv_heads * page_size), head_dim], with
     boxes of ``box_rows`` rows (a whole page by default)."""
-    from mini_engine_b200.csrc import tensor_core
-
     count, kv_heads, page_size, head_dim = pages.shape
     box_rows = box_rows or page_size
     key = (pages.data_ptr(), tuple(pages.shape), box_rows)
@@ -82,8 +86,6 @@ def tma_decode_kernel_takes(heads: int, kv_heads: int, page_size: int) -> bool:
 
 
 def _query_map(q: torch.Tensor):
-    from mini_engine_b200.csrc import tensor_core
-
     key = (q.data_ptr(), q.shape[0], q.shape[1])
     held = _query_maps.get(key)
     if held is None:
@@ -170,14 +172,12 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     """Attention of the batch's new tokens.  Entries that bring one token take the split decode
     kernel, the others a portions kernel; a step that holds both kinds is two launches, each over
     its own list of entries."""
-    from mini_engine_b200.csrc import ops
-
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ops.KernelError(f"{name} must be contiguous bfloat16")
     if block_table.dtype != torch.int32 or not block_table.is_contiguous():
         raise ops.KernelError("block_table must be contiguous int32")
-    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    stream = _ops_stream()
     page_size, width = k_pages.shape[2], block_table.shape[1]
     common = (q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(), ctx.cu_tokens.data_ptr(),
               ctx.context_lens.data_ptr(), out.data_ptr())  # fmt: skip

@@ -36,8 +36,30 @@ def _ptr(tensor: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+_scoped_stream: c_void_p | None = None
+
+
 def _stream() -> c_void_p:
+    """The stream that launches go to: torch's current one, looked up once per `stream_scope`
+    (the lookup costs about as much as the rest of a launch's Python)."""
+    if _scoped_stream is not None:
+        return _scoped_stream
     return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """While open, every launch of this package goes to the stream that was torch's current one
+    when the scope was opened.  The model's forward pass opens one: nothing inside it changes the
+    current stream (a graph capture changes it around the whole pass)."""
+
+    def __enter__(self) -> None:
+        global _scoped_stream
+        self.previous = _scoped_stream
+        _scoped_stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def __exit__(self, *exc) -> None:
+        global _scoped_stream
+        _scoped_stream = self.previous
 
 
 class _Counter:
@@ -63,8 +85,6 @@ def raise_on_device_error() -> None:
     """Ask the tensor-core and attention libraries that are loaded whether a kernel gave up a
     bounded wait since the last call, and raise if one did: what such a kernel wrote is invalid.
     Reads a flag from the device, so it waits for the work in flight."""
-    from mini_engine_b200.csrc import attention_bf16, tensor_core
-
     for what, code in (("tensor-core product", tensor_core.take_error()), ("attention", attention_bf16.take_error())):
         if code:
             raise KernelError(
@@ -268,32 +288,22 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 def tensor_core_gemm_supports(outs: int, inner: int) -> bool:
     """TMA addresses rows whose pitch is a multiple of 16 bytes: ``inner % 8 == 0`` for
     bfloat16.  Other shapes take the CUDA-core kernel."""
-    from mini_engine_b200.csrc import tensor_core
-
     return tensor_core.supports(outs, inner)
 
 
 def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> int:
-    from mini_engine_b200.csrc import tensor_core
-
     return tensor_core.choose_splits(tokens, outs, inner, max_splits)
 
 
 def GemmPlan(weight: torch.Tensor, dual_rows: int | None = None):  # noqa: N802 - constructs a plan object
-    from mini_engine_b200.csrc import tensor_core
-
     return tensor_core.GemmPlan(weight, dual_rows)
 
 
 def gemm_tensor_core(plan, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
-    from mini_engine_b200.csrc import tensor_core
-
     tensor_core.gemm(plan, x, out, splits)
 
 
 def gemm_tensor_core_swiglu(plan, x: torch.Tensor, act: torch.Tensor) -> None:
-    from mini_engine_b200.csrc import tensor_core
-
     tensor_core.gemm_swiglu(plan, x, act)
 
 
@@ -325,8 +335,6 @@ def paged_attention(
     """Causal attention of the batch's new tokens over their requests' cached keys (the new
     tokens' own keys are already in the cache).  Chooses the kernel by dtype and sizes."""
     if q.dtype == torch.bfloat16:
-        from mini_engine_b200.csrc import attention_bf16
-
         if attention_bf16.supports(head_dim, heads, kv_heads):
             attention_bf16.paged_attention(
                 q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window
@@ -351,3 +359,8 @@ def sample(logits: torch.Tensor, temperatures: torch.Tensor | None, uniforms: to
     fn = _fn("sampling", "me_sample", [c_void_p] * 4 + [c_int, c_int, c_void_p])
     code = fn(_ptr(logits), _ptr(temperatures), _ptr(uniforms), _ptr(out), rows, vocab, _stream())
     _check(code, "sample")
+
+
+# The bindings of the tensor-core and attention libraries use this module's helpers and are used
+# by its wrappers: they are imported last, when everything above exists.
+from mini_engine_b200.csrc import attention_bf16, tensor_core  # noqa: E402

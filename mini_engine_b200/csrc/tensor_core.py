@@ -13,6 +13,7 @@ from ctypes import c_int, c_uint, c_ulonglong, c_void_p
 
 import torch
 
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.csrc.build import load_library
 
 NUM_SMS = 148
@@ -29,6 +30,11 @@ USE_PERSISTENT = os.environ.get("MINI_ENGINE_B200_PERSISTENT", "1") != "0"
 
 STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
 USE_PERSISTENT_GATED = os.environ.get("MINI_ENGINE_B200_PERSISTENT_GATED", "1") != "0"
+
+
+def _ops_stream() -> c_void_p:
+    return ops._stream()
+
 
 _lib = None
 
@@ -138,7 +144,7 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
     if out.dtype != torch.float32 or tuple(out.shape) != (splits, tokens, plan.rows) or not out.is_contiguous():
         raise RuntimeError(f"output {tuple(out.shape)} does not fit [{splits}, {tokens}, {plan.rows}] float32")
     tile = token_tile(tokens)
-    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    stream = _ops_stream()
     if tokens > PAIR_MIN_TOKENS and splits == 1 and USE_PAIRS:
         entry = _library().me_gemm_tcgen05_persistent if USE_PERSISTENT else _library().me_gemm_tcgen05_pair
         code = entry(plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream)
@@ -160,7 +166,7 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
         raise RuntimeError("this plan was not made for a gated product")
     if act.dtype != torch.bfloat16 or tuple(act.shape) != (tokens, plan.dual_rows) or not act.is_contiguous():
         raise RuntimeError(f"activation output {tuple(act.shape)} does not fit [{tokens}, {plan.dual_rows}] bfloat16")
-    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    stream = _ops_stream()
     if tokens <= STACKED_MAX_TOKENS:
         tile = token_tile(tokens)
         code = _library().me_gemm_tcgen05_stacked_swiglu(
@@ -187,8 +193,6 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
 
 
 def _count_launch() -> None:
-    from mini_engine_b200.csrc import ops
-
     ops._Counter.launches += 1
 
 

@@ -12,6 +12,8 @@ import math
 
 import torch
 
+from mini_engine_b200.parts.linear import partial_rows
+
 
 class Workspace:
     def __init__(self, max_tokens: int, device: str | torch.device = "cuda"):
@@ -40,8 +42,6 @@ class Workspace:
 
     def partials(self, name: str, splits: int, tokens: int, width: int) -> torch.Tensor:
         """``[splits, tokens, width]`` float32 for the partial sums of a split product."""
-        from mini_engine_b200.parts.linear import partial_rows
-
         rows = max(partial_rows(self.max_tokens), splits * tokens)
         flat = self._flat(name, rows * width, torch.float32)
         return flat[: splits * tokens * width].view(splits, tokens, width)

@@ -86,6 +86,10 @@ class DecoderModel:
     def forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:
         """Run the batch's tokens through every entry of the order; return float32 logits
         ``[N, vocab]`` at ``logits_rows`` (int32 row numbers among the batch's tokens)."""
+        with ops.stream_scope():
+            return self._forward(ctx, caches, logits_rows)
+
+    def _forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:
         x = ctx.buffer("residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
         ops.embedding(self.embedding, ctx.token_ids, x)
         state = Residual(x)
