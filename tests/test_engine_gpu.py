@@ -142,7 +142,7 @@ def test_eos_stops_generation_and_is_kept(peaked_model_folders):
 
 
 def test_bfloat16_generation_runs_and_mostly_agrees(peaked_model_folders):
-    """bfloat16 is judged by tolerance on logits elsewhere; here generation must run through
+    """bfloat16 is compared by tolerance on logits elsewhere; here generation must run through
     graphs and portions and agree with float32 on peaked logits up to near-ties."""
     from mini_engine_b200 import SamplingParams
 
