@@ -75,6 +75,17 @@ class DecodeGraphs:
                 return bucket
         return None
 
+    def prepare(self, entries: Seq[StepEntry]):
+        """Lay a decode step out ahead of its token ids (placeholders in `entries`)."""
+        bucket = self.bucket_for(len(entries))
+        return self.runner.pack(entries, pad_entries_to=bucket, want_every_entry=True, build_context=False, defer_copy=True)
+
+    def run_prepared(self, prepacked, token_ids: Seq[int]) -> torch.Tensor:
+        """The step that :meth:`prepare` laid out, now that its token ids are known."""
+        self.runner.commit(prepacked, token_ids)
+        self.graphs[prepacked.total_entries].replay()
+        return self.logits[prepacked.total_entries][: prepacked.real]
+
     def run(self, entries: Seq[StepEntry]) -> torch.Tensor:
         """Logits ``[len(entries), vocab]``: one decoded token per entry, the logits of each."""
         real = len(entries)

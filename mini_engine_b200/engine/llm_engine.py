@@ -39,6 +39,7 @@ class EngineStats:
     computed_tokens: int = 0  # tokens actually run through the model
     generated_tokens: int = 0
     graph_steps: int = 0  # steps that replayed a captured graph
+    prepacked_steps: int = 0  # of those, steps whose arrays were laid out while the step before ran
     step_batch_sizes: list[int] = field(default_factory=list)
 
 
@@ -82,6 +83,7 @@ class LLMEngine:
         )
         self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
         self.stats = EngineStats()
+        self._prepacked = None  # the next decode step, laid out while the current one runs
         self.decode_graphs: DecodeGraphs | None = None
         if config.cuda_graphs:
             self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
@@ -131,9 +133,15 @@ class LLMEngine:
             raise RuntimeError("scheduler produced an empty batch with work pending")
         entries = [self._entry(item) for item in batch]
         sampling = [item for item in batch if item.samples]
+        prepacked, self._prepacked = self._prepacked, None
         if self._graph_fits(batch):
-            logits = self.decode_graphs.run(entries)
+            if prepacked is not None and prepacked.matches(entries):
+                logits = self.decode_graphs.run_prepared(prepacked, [e.token_ids[0] for e in entries])
+                self.stats.prepacked_steps += 1
+            else:
+                logits = self.decode_graphs.run(entries)
             self.stats.graph_steps += 1
+            self._prepacked = self._prepack_next(batch)  # host work while the device runs the step
         else:
             logits = self.runner.execute(entries)
         sampled = self.sampler.sample(
@@ -156,6 +164,25 @@ class LLMEngine:
         seq, start = item.seq, item.seq.num_computed_tokens
         want = (item.num_tokens - 1,) if item.samples else ()
         return StepEntry(seq.cache, start, seq.token_ids[start : start + item.num_tokens], want)
+
+    def _prepack_next(self, batch: list[ScheduledSeq]):
+        """Lay out the decode step that follows `batch` if it is certain what it will hold unless
+        a request ends on its next token: nobody waits to be admitted, every request has room for
+        two more tokens and its pages can be had without preempting anyone.  The pages that this
+        takes are the ones the scheduler would take a step later; a request that ends instead
+        gives all its pages back anyway."""
+        if self.scheduler.waiting:
+            return None
+        entries = []
+        for item in batch:
+            seq = item.seq
+            start = seq.num_computed_tokens + 1  # the step in flight computes one token
+            if seq.num_output_tokens + 2 > seq.params.max_tokens or start + 1 > self.config.max_model_len:
+                return None
+            if not self.block_manager.try_allocate(seq.cache, start + 1):
+                return None
+            entries.append(StepEntry(seq.cache, start, [0], (0,)))
+        return self.decode_graphs.prepare(entries)
 
     def _graph_fits(self, batch: list[ScheduledSeq]) -> bool:
         graphs = self.decode_graphs

@@ -39,6 +39,25 @@ class StepEntry:
     want: Seq[int] = field(default_factory=tuple)  # places among these tokens whose logits are returned
 
 
+@dataclass
+class Prepacked:
+    """A decode step laid out in a pinned block ahead of its token ids."""
+
+    flip: int  # which pinned block
+    used: int  # int32 values of the block that belong to the step
+    ids_offset: int
+    real: int  # entries without padding
+    total_entries: int
+    key: tuple  # (request serial, table version, start) of every entry, as laid out
+
+    def matches(self, entries: Seq[StepEntry]) -> bool:
+        """Whether `entries` (one token each) are the step that was laid out: the same requests
+        in the same order at the same positions, their block tables unchanged since."""
+        return len(entries) == self.real and self.key == tuple(
+            (e.cache.serial, e.cache.version, e.start) for e in entries
+        ) and all(len(e.token_ids) == 1 for e in entries)
+
+
 class ModelRunner:
     def __init__(
         self,
@@ -108,13 +127,16 @@ class ModelRunner:
         pad_entries_to: int | None = None,
         want_every_entry: bool = False,
         build_context: bool = True,
-    ) -> tuple[StepContext | None, torch.Tensor | None]:
+        defer_copy: bool = False,
+    ) -> tuple[StepContext | None, torch.Tensor | None] | "Prepacked":
         """Lay the batch out as int32 arrays on the device.  With ``pad_entries_to`` the batch
         is filled up with one-token dummy entries on the spare page (for a captured graph of
         that size); with ``want_every_entry`` the wanted rows are the last token of every entry,
         padding included, whatever the entries ask for.  Returns the context and the int32 row
         numbers of the wanted logits (both ``None`` without ``build_context``: a captured graph
-        reads the arrays where they always lie)."""
+        reads the arrays where they always lie).  With ``defer_copy`` the pinned block is filled
+        but not copied: the :class:`Prepacked` that comes back takes the token ids later
+        (:meth:`commit`), so that a decode step can be laid out while the one before it runs."""
         real = len(entries)
         total_entries = max(real, pad_entries_to or 0)
         counts = [len(e.token_ids) for e in entries]
@@ -258,6 +280,9 @@ class ModelRunner:
         rows_view[:] = wanted_rows
 
         used = offset
+        if defer_copy:
+            key = tuple((e.cache.serial, e.cache.version, e.start) for e in entries)
+            return Prepacked(flip, used, o_ids, real, total_entries, key)
         self._device[:used].copy_(self._host[flip][:used], non_blocking=True)
         self._copied[flip].record()
         self.last_h2d_bytes = used * 4
@@ -296,6 +321,20 @@ class ModelRunner:
             },
         )
         return ctx, at(o_rows, len(wanted_rows))
+
+    def commit(self, prepacked: "Prepacked", token_ids: Seq[int]) -> None:
+        """Put the token ids into a block that :meth:`pack` laid out with ``defer_copy`` and copy
+        it to the device."""
+        if len(token_ids) != prepacked.real:
+            raise ValueError("one token id per entry of the prepacked step")
+        if min(token_ids) < 0 or max(token_ids) >= self.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        host = self._host_np[prepacked.flip]
+        host[prepacked.ids_offset : prepacked.ids_offset + prepacked.real] = token_ids
+        used = prepacked.used
+        self._device[:used].copy_(self._host[prepacked.flip][:used], non_blocking=True)
+        self._copied[prepacked.flip].record()
+        self.last_h2d_bytes = used * 4
 
     # --------------------------------------------------------------------- step
 

@@ -52,6 +52,7 @@ def test_greedy_generation_matches_plain(name, graphs, peaked_model_folders):
     engine.block_manager.check_invariants([])
     if graphs:
         assert engine.stats.graph_steps > 0
+        assert 0 < engine.stats.prepacked_steps < engine.stats.graph_steps  # laid out while the step before ran
 
 
 def test_every_way_of_running_gives_the_same_tokens(peaked_model_folders):
