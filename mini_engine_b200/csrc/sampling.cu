@@ -11,22 +11,23 @@
 
 constexpr int SAMPLE_THREADS = 1024;
 
-// One block per row.  Each thread owns one contiguous chunk of the vocabulary, so the
-// cumulative sums run in index order and ties resolve to the lowest index.
+// One block per row.  Cumulative sums run in index order (a warp per contiguous segment of the
+// vocabulary, then a thread per few consecutive tokens of one segment), and ties resolve to the
+// lowest index.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperatures,
               const float* __restrict__ uniforms, int* __restrict__ out, int vocab) {
     __shared__ float red_value[SAMPLE_THREADS / 32];
     __shared__ int red_index[SAMPLE_THREADS / 32];
-    __shared__ float chunk_sums[SAMPLE_THREADS];
+    __shared__ float segment_sums[SAMPLE_THREADS / 32];
+    __shared__ float warp_totals[SAMPLE_THREADS / 32];
+    __shared__ int first_passing, last_positive;
     __shared__ float row_max_shared;
     __shared__ int best_shared;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_trigger();
     pdl_wait();
     const float* x = logits + static_cast<size_t>(row) * vocab;
-    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int begin = min(tid * chunk, vocab), end = min(begin + chunk, vocab);
 
     // 1. maximum and its lowest index.  Threads stride through the row together (coalesced
     //    loads); a thread meets its indices in ascending order, so "greater than" keeps the lowest.
@@ -51,6 +52,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             if (red_value[w] > b || (red_value[w] == b && red_index[w] < bi)) { b = red_value[w]; bi = red_index[w]; }
         row_max_shared = b;
         best_shared = bi < vocab ? bi : 0;
+        first_passing = SAMPLE_THREADS;
+        last_positive = 0;
     }
     __syncthreads();
     const float temperature = temperatures ? temperatures[row] : 0.0f;
@@ -59,35 +62,70 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         return;
     }
 
-    // 2. unnormalised probabilities, chunk by chunk
-    const float inv_t = 1.0f / fmaxf(temperature, 1e-5f);
+    // 2. unnormalised probabilities: warp w owns the contiguous segment [w * segment, +segment)
+    //    of the vocabulary and adds it up with coalesced loads.
+    const float factor = 1.4426950408889634f / fmaxf(temperature, 1e-5f);  // log2(e) / T
     const float row_max = row_max_shared;
+    const int segment = (vocab + SAMPLE_THREADS / 32 - 1) / (SAMPLE_THREADS / 32);
+    const int seg_begin = min(warp * segment, vocab), seg_end = min(seg_begin + segment, vocab);
     float local = 0.0f;
-    for (int i = begin; i < end; ++i) local += expf((x[i] - row_max) * inv_t);
-    chunk_sums[tid] = local;
+    for (int i = seg_begin + lane; i < seg_end; i += 32) local += exp2f((x[i] - row_max) * factor);
+    local = warp_sum(local);
+    if (lane == 0) segment_sums[warp] = local;
     __syncthreads();
 
-    // 3. the chunk in which the cumulative sum passes uniform * total, then the token in it
-    if (tid == 0) {
-        float total = 0.0f;
-        for (int t = 0; t < SAMPLE_THREADS; ++t) total += chunk_sums[t];
-        const float target = uniforms[row] * total;
-        float before = 0.0f;
-        int owner = 0;
-        for (int t = 0; t < SAMPLE_THREADS; ++t) {
-            if (chunk_sums[t] > 0.0f) owner = t;  // last non-empty chunk so far: fallback for rounding
-            if (before + chunk_sums[t] > target) { owner = t; break; }
-            before += chunk_sums[t];
-        }
-        const int b = min(owner * chunk, vocab), e = min(b + chunk, vocab);
-        int chosen = e - 1;
-        float cumulative = before;
-        for (int i = b; i < e; ++i) {
-            cumulative += expf((x[i] - row_max) * inv_t);
-            if (cumulative > target) { chosen = i; break; }
-        }
-        out[row] = chosen;
+    // 3. the segment in which the cumulative sum passes uniform * total (every thread finds it
+    //    alike).  Then the whole block goes over that one segment, a few consecutive tokens per
+    //    thread: a prefix sum over the threads names the first thread at which the cumulative
+    //    sum exceeds the target, and that thread walks its own tokens.
+    float total = 0.0f;
+    for (int w = 0; w < SAMPLE_THREADS / 32; ++w) total += segment_sums[w];
+    const float target = uniforms[row] * total;
+    int owner = -1, last_nonempty = 0;
+    float before = 0.0f, before_last = 0.0f, running = 0.0f;
+    for (int w = 0; w < SAMPLE_THREADS / 32; ++w) {
+        const float s = segment_sums[w];
+        if (s > 0.0f) { last_nonempty = w; before_last = running; }
+        if (owner < 0 && running + s > target) { owner = w; before = running; }
+        running += s;
     }
+    if (owner < 0) { owner = last_nonempty; before = before_last; }  // rounding at a uniform number near 1
+    const int owner_begin = min(owner * segment, vocab), owner_end = min(owner_begin + segment, vocab);
+    const int per_thread = (segment + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int begin = min(owner_begin + tid * per_thread, owner_end), end = min(begin + per_thread, owner_end);
+    float mine = 0.0f;
+    for (int i = begin; i < end; ++i) mine += exp2f((x[i] - row_max) * factor);
+    float scan = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const float below = __shfl_up_sync(0xffffffffu, scan, offset);
+        if (lane >= offset) scan += below;
+    }
+    if (lane == 31) warp_totals[warp] = scan;
+    __syncthreads();
+    float exclusive = before;
+    for (int w = 0; w < warp; ++w) exclusive += warp_totals[w];
+    exclusive += scan - mine;
+    if (mine > 0.0f) {
+        if (exclusive + mine > target) atomicMin(&first_passing, tid);
+        atomicMax(&last_positive, tid);
+    }
+    __syncthreads();
+    // No thread passes only when rounding left the target at or above the last cumulative sum:
+    // then the last token of the segment that has any probability is the draw.
+    const bool passing = first_passing < SAMPLE_THREADS;
+    if (tid != (passing ? first_passing : last_positive)) return;
+    int chosen = -1, fallback = begin;
+    float cumulative = exclusive;
+    for (int i = begin; i < end && chosen < 0; ++i) {
+        const float p = exp2f((x[i] - row_max) * factor);
+        cumulative += p;
+        if (p > 0.0f) {
+            fallback = i;
+            if (passing && cumulative > target) chosen = i;
+        }
+    }
+    out[row] = chosen >= 0 ? chosen : fallback;
 }
 
 ME_EXPORT int me_sample(const float* logits, const float* temperatures, const float* uniforms, int* out,

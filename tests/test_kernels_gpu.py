@@ -526,6 +526,24 @@ def test_sample_greedy_and_temperature():
         assert below - 1e-4 <= target <= float(cdf[got[r]]) + 1e-4, f"row {r}: token {got[r]} does not hold u={target}"
 
 
+@pytest.mark.parametrize("vocab", [5, 33, 1000, 40961])
+def test_sample_never_draws_a_token_without_probability(vocab):
+    """A few tokens hold all the probability; the rest lie so far below that their exponentials
+    are zero.  Whatever the uniform number (0, the edges between the few, almost 1), the draw is
+    one of the few, and the one that the cumulative sums name."""
+    few = sorted({1, vocab // 3, vocab // 2 + 1, vocab - 2})
+    uniforms = [0.0, 0.1, 0.2499, 0.2501, 0.5, 0.7499, 0.7501, 0.9, 0.99999994]
+    logits = torch.full((len(uniforms), vocab), -1e4, device="cuda")
+    logits[:, few] = 3.0
+    out = torch.empty(len(uniforms), dtype=torch.int32, device="cuda")
+    ops().sample(logits, torch.full((len(uniforms),), 0.9, device="cuda"), torch.tensor(uniforms, device="cuda"), out)
+    share = 1.0 / len(few)
+    for u, token in zip(uniforms, out.tolist()):
+        assert token in few, f"u={u}: token {token} has probability zero"
+        k = few.index(token)
+        assert k * share - 1e-3 <= u <= (k + 1) * share + 1e-3, f"u={u}: token {token} is number {k} of {len(few)}"
+
+
 def test_sample_distribution():
     vocab, draws = 7, 4000
     logits = torch.tensor([[2.0, 0.0, 1.0, -1.0, 0.5, 0.0, -3.0]], device="cuda").repeat(draws, 1)
