@@ -149,17 +149,23 @@ def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int) -> int:
     each request's own tiles evenly among them (two tiles of 128 keys or more per CTA).
 
     Long contexts whose one wave would be lopsided (fewer CTAs than three quarters of the slots,
-    so that some SMs hold two and some one; or a few more than the slots) take three times as
-    many: with several CTAs per slot the SMs that finish early take the next ones, and a CTA of
-    24 tiles and more hides its start-up (batch 32 at 8,192 keys: 199 -> 171 us; batch 64: 382 ->
-    319 us)."""
+    so that some SMs hold two and some one) take three times as many: with several CTAs per slot
+    the SMs that finish early take the next ones, and a CTA of 24 tiles and more hides its
+    start-up (batch 32 at 8,192 keys: 199 -> 171 us).  So do batches with a few more (request, KV
+    head) pairs than slots, from 16 tiles on: whole pairs would leave a last wave that is nearly
+    empty and as long as the first (batch 64 at 2,048 keys: 103 -> 93 us; at 4,096: 194 -> 168 us),
+    while with a last wave that is a third full and more, one CTA per pair is faster (batch 80 at
+    4,096 keys: 202 us against 208 us)."""
     if FORCED_TMA_SPLITS > 0:
         return FORCED_TMA_SPLITS
     tiles = max(1, -(-max_context_len // DECODE_CHUNK))
     pairs = max(1, entries * kv_heads)
-    splits = max(1, min(RESIDENT_DECODE_CTAS // pairs, -(-tiles // 2), 64))
-    ctas = pairs * splits
-    if tiles / splits >= 24 and (ctas > RESIDENT_DECODE_CTAS or ctas < 0.75 * RESIDENT_DECODE_CTAS):
+    slots = RESIDENT_DECODE_CTAS
+    splits = max(1, min(slots // pairs, -(-tiles // 2), 64))
+    if pairs > slots:
+        if tiles >= 16 and pairs % slots < 0.25 * slots:
+            splits = 3
+    elif tiles / splits >= 24 and pairs * splits < 0.75 * slots:
         splits = max(splits, min(3 * splits, tiles // 8, 64))
     return splits
 
