@@ -26,6 +26,10 @@ class EngineConfig:
     # When set (0 < f <= 1), num_blocks is ignored and the pool takes this fraction of the device
     # memory that is free after the weights are loaded.  The reference sizes by num_blocks only.
     kv_memory_fraction: float | None = None
+    # Launch the decode step after the current one before the current one's token ids are read
+    # (needs cuda_graphs).  The tokens are the same either way; off is for comparing.  Not in the
+    # reference, whose steps are strictly one after the other.
+    overlap_steps: bool = True
 
     def __post_init__(self) -> None:
         if self.dtype not in (torch.float32, torch.bfloat16):

@@ -21,12 +21,12 @@ from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.csrc import ops
 from mini_engine_b200.engine.graphs import DecodeGraphs
 from mini_engine_b200.engine.loading import load_model, random_model
-from mini_engine_b200.engine.runner import ModelRunner, StepEntry
+from mini_engine_b200.engine.runner import ModelRunner, Prepacked, StepEntry
 from mini_engine_b200.engine.scheduler import ScheduledSeq, Scheduler, SchedulerConfig
 from mini_engine_b200.engine.sequence import Sequence
 from mini_engine_b200.parts.model import DecoderModel
 from mini_engine_b200.sampling.params import SamplingParams
-from mini_engine_b200.sampling.sampler import Sampler
+from mini_engine_b200.sampling.sampler import Draw, Sampler
 
 
 DEVICE_CHECK_EVERY = 32  # steps between reads of the kernels' error flags (generate() also reads them at its end)
@@ -39,8 +39,17 @@ class EngineStats:
     computed_tokens: int = 0  # tokens actually run through the model
     generated_tokens: int = 0
     graph_steps: int = 0  # steps that replayed a captured graph
-    prepacked_steps: int = 0  # of those, steps whose arrays were laid out while the step before ran
+    prepacked_steps: int = 0  # of those, steps that were launched while the step before ran
+    dropped_steps: int = 0  # steps launched ahead that turned out not to be the next step
     step_batch_sizes: list[int] = field(default_factory=list)
+
+
+@dataclass
+class StepInFlight:
+    """A decode step that was launched before the token ids of the step before it were read."""
+
+    prepacked: Prepacked
+    draw: Draw
 
 
 def kv_cache_bytes_per_token(runner: ModelRunner) -> int:
@@ -83,7 +92,7 @@ class LLMEngine:
         )
         self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
         self.stats = EngineStats()
-        self._prepacked = None  # the next decode step, laid out while the current one runs
+        self._in_flight: StepInFlight | None = None  # the decode step after the current one, already launched
         self.decode_graphs: DecodeGraphs | None = None
         if config.cuda_graphs:
             self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
@@ -127,29 +136,37 @@ class LLMEngine:
 
     @torch.inference_mode()
     def step(self) -> list[Sequence]:
-        """One iteration; returns the requests that finished in it."""
+        """One iteration; returns the requests that finished in it.
+
+        Decode steps overlap: when it is certain what the step after this one holds unless a
+        request ends on the token drawn now, that step is launched before this one's token ids
+        are read, fed on the device with what the sampler drew; scheduling and bookkeeping then
+        run while the device works.  If a request does end (or a new one arrives), the next call
+        finds that the step in flight is not the one the scheduler wants and drops it: it wrote
+        keys and values only to places that the rerun writes again with the same values, or that
+        belonged to the ended request."""
         batch = self.scheduler.schedule()
         if not batch:
             raise RuntimeError("scheduler produced an empty batch with work pending")
         entries = [self._entry(item) for item in batch]
-        sampling = [item for item in batch if item.samples]
-        prepacked, self._prepacked = self._prepacked, None
-        if self._graph_fits(batch):
-            if prepacked is not None and prepacked.matches(entries):
-                logits = self.decode_graphs.run_prepared(prepacked, [e.token_ids[0] for e in entries])
-                self.stats.prepacked_steps += 1
-            else:
-                logits = self.decode_graphs.run(entries)
-            self.stats.graph_steps += 1
-            self._prepacked = self._prepack_next(batch)  # host work while the device runs the step
+        flight, self._in_flight = self._in_flight, None
+        if flight is not None and not flight.prepacked.matches(entries):
+            self.stats.dropped_steps += 1
+            flight = None
+        if flight is not None:
+            draw, graph_step = flight.draw, True
+            self.stats.prepacked_steps += 1
         else:
-            logits = self.runner.execute(entries)
-        sampled = self.sampler.sample(
-            logits,
-            [item.seq.params.temperature for item in sampling],
-            [item.seq.seq_id for item in sampling],
-            [item.seq.num_output_tokens for item in sampling],
-        )
+            graph_step = self._graph_fits(batch)
+            logits = self.decode_graphs.run(entries) if graph_step else self.runner.execute(entries)
+            draw = self._draw(batch, logits, 0)
+        if graph_step:
+            self.stats.graph_steps += 1
+            prepacked = self._prepack_next(batch) if self.config.overlap_steps else None  # host work while the device runs
+            if prepacked is not None:
+                logits = self.decode_graphs.run_prepared(prepacked, draw.tokens)
+                self._in_flight = StepInFlight(prepacked, self._draw(batch, logits, 1))
+        sampled = self.sampler.collect(draw)
         tokens = iter(sampled)
         next_tokens = [next(tokens) if item.samples else None for item in batch]
         self._update_stats(batch)
@@ -164,6 +181,17 @@ class LLMEngine:
         seq, start = item.seq, item.seq.num_computed_tokens
         want = (item.num_tokens - 1,) if item.samples else ()
         return StepEntry(seq.cache, start, seq.token_ids[start : start + item.num_tokens], want)
+
+    def _draw(self, batch: list[ScheduledSeq], logits: torch.Tensor, ahead: int):
+        """Launch the draw of one token for every request of `batch` that samples; `ahead` = 1 for
+        the step after the one that `batch` describes (every request one token further)."""
+        sampling = [item.seq for item in batch if item.samples]
+        return self.sampler.launch(
+            logits,
+            [seq.params.temperature for seq in sampling],
+            [seq.seq_id for seq in sampling],
+            [seq.num_output_tokens + ahead for seq in sampling],
+        )
 
     def _prepack_next(self, batch: list[ScheduledSeq]):
         """Lay out the decode step that follows `batch` if it is certain what it will hold unless

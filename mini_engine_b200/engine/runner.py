@@ -322,18 +322,27 @@ class ModelRunner:
         )
         return ctx, at(o_rows, len(wanted_rows))
 
-    def commit(self, prepacked: "Prepacked", token_ids: Seq[int]) -> None:
+    def commit(self, prepacked: "Prepacked", token_ids: Seq[int] | torch.Tensor) -> None:
         """Put the token ids into a block that :meth:`pack` laid out with ``defer_copy`` and copy
-        it to the device."""
+        it to the device.  Token ids that are still on the device (an int32 tensor, one per entry:
+        what the sampler drew in the step before) are copied there into the device's block, after
+        the block itself, so the host need not know them yet."""
+        used = prepacked.used
+        ids = slice(prepacked.ids_offset, prepacked.ids_offset + prepacked.real)
+        on_device = isinstance(token_ids, torch.Tensor)
         if len(token_ids) != prepacked.real:
             raise ValueError("one token id per entry of the prepacked step")
-        if min(token_ids) < 0 or max(token_ids) >= self.vocab_size:
-            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
-        host = self._host_np[prepacked.flip]
-        host[prepacked.ids_offset : prepacked.ids_offset + prepacked.real] = token_ids
-        used = prepacked.used
+        if on_device:
+            if token_ids.dtype != torch.int32 or not token_ids.is_cuda:
+                raise ValueError("token ids on the device must be int32")
+        else:
+            if min(token_ids) < 0 or max(token_ids) >= self.vocab_size:
+                raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+            self._host_np[prepacked.flip][ids] = token_ids
         self._device[:used].copy_(self._host[prepacked.flip][:used], non_blocking=True)
         self._copied[prepacked.flip].record()
+        if on_device:
+            self._device[ids].copy_(token_ids, non_blocking=True)
         self.last_h2d_bytes = used * 4
 
     # --------------------------------------------------------------------- step

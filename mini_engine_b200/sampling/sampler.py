@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import hashlib
 import struct
+from dataclasses import dataclass
 from typing import Sequence as Seq
 
 import torch
@@ -25,14 +26,64 @@ def uniform_for(seed: int, request_id: int, token_index: int) -> float:
     return (int.from_bytes(digest, "little") >> 40) / float(1 << 24)
 
 
+@dataclass
+class Draw:
+    """A launched draw: the tokens are on the device (``tokens``) and on their way to the host."""
+
+    tokens: torch.Tensor  # int32 [rows] on the device; the next launch of the sampler overwrites it
+    rows: int
+    side: int  # which of the two host buffers the tokens arrive in
+
+
 class Sampler:
+    """Draws are launched and collected separately, so that the caller can queue more device work
+    (the next step, fed with ``Draw.tokens``) before it waits for the token ids.  At most two draws
+    may be outstanding: each launch takes the host buffers that the draw before the last one used."""
+
     def __init__(self, seed: int, max_rows: int, device: str | torch.device = "cuda"):
         self.seed = seed
         self.device = torch.device(device)
-        self._host = torch.empty((2, max_rows), dtype=torch.float32).pin_memory()
-        self._params = torch.empty((2, max_rows), dtype=torch.float32, device=self.device)
+        self._host = torch.empty((2, 2, max_rows), dtype=torch.float32).pin_memory()  # [side][temperature, uniform]
+        self._params = torch.empty((2, 2, max_rows), dtype=torch.float32, device=self.device)
         self._tokens = torch.empty(max_rows, dtype=torch.int32, device=self.device)
-        self._tokens_host = torch.empty(max_rows, dtype=torch.int32).pin_memory()
+        self._tokens_host = torch.empty((2, max_rows), dtype=torch.int32).pin_memory()
+        self._arrived = [torch.cuda.Event(), torch.cuda.Event()]
+        self._side = 0
+
+    def launch(
+        self,
+        logits: torch.Tensor,
+        temperatures: Seq[float],
+        request_ids: Seq[int],
+        token_indices: Seq[int],
+    ) -> Draw:
+        """Start drawing one token per row of ``logits [rows, vocab]`` (float32, on the device)."""
+        rows = logits.shape[0]
+        self._side ^= 1
+        side = self._side
+        out = self._tokens[:rows]
+        if rows == 0:
+            return Draw(out, 0, side)
+        if all(t == 0 for t in temperatures):
+            ops.sample(logits, None, None, out)
+        else:
+            host = self._host[side]
+            for i in range(rows):
+                host[0, i] = temperatures[i]
+                host[1, i] = uniform_for(self.seed, request_ids[i], token_indices[i]) if temperatures[i] else 0.0
+            params = self._params[side]
+            params[:, :rows].copy_(host[:, :rows], non_blocking=True)
+            ops.sample(logits, params[0, :rows], params[1, :rows], out)
+        self._tokens_host[side, :rows].copy_(out, non_blocking=True)
+        self._arrived[side].record()
+        return Draw(out, rows, side)
+
+    def collect(self, draw: Draw) -> list[int]:
+        """Wait for a launched draw and return its token ids."""
+        if draw.rows == 0:
+            return []
+        self._arrived[draw.side].synchronize()
+        return self._tokens_host[draw.side, : draw.rows].tolist()
 
     def sample(
         self,
@@ -42,21 +93,4 @@ class Sampler:
         token_indices: Seq[int],
     ) -> list[int]:
         """One token per row of ``logits [rows, vocab]`` (float32, on the device)."""
-        rows = logits.shape[0]
-        if rows == 0:
-            return []
-        out = self._tokens[:rows]
-        if all(t == 0 for t in temperatures):
-            ops.sample(logits, None, None, out)
-        else:
-            host = self._host
-            for i in range(rows):
-                host[0, i] = temperatures[i]
-                host[1, i] = uniform_for(self.seed, request_ids[i], token_indices[i]) if temperatures[i] else 0.0
-            self._params[:, :rows].copy_(host[:, :rows], non_blocking=True)
-            temps = self._params[0, :rows]
-            uniforms = self._params[1, :rows]
-            ops.sample(logits, temps, uniforms, out)
-        self._tokens_host[:rows].copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._tokens_host[:rows].tolist()
+        return self.collect(self.launch(logits, temperatures, request_ids, token_indices))

@@ -125,6 +125,50 @@ def test_temperature_sampling_is_reproducible_and_batch_independent(model_folder
     assert [s.output_token_ids for s in seqs2] != batched
 
 
+def test_steps_launched_ahead_never_change_the_tokens(peaked_model_folders):
+    """The decode step after the current one is launched before the current one's tokens are
+    read.  When a request then ends on an end-of-sequence token, the step in flight is dropped and
+    run again without it: greedy and sampled tokens equal those of an engine whose steps run strictly
+    one after the other, for requests that end early, at different times, and for those that go on."""
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.engine.loading import load_model
+    from mini_engine_b200.engine.sequence import Sequence
+
+    folder = peaked_model_folders["B"]
+    _, cfg = load_plain(folder)
+    prompts = [random_ids(1200 + i, n, cfg["vocab"]) for i, n in enumerate((9, 30, 2, 17, 44))]
+    _arch, _cfg, model = load_model(folder, torch.float32)
+
+    def generate(engine, params):  # the same request ids in every run: sampled tokens depend on them
+        seqs = [Sequence(p, params, seq_id=7000 + i) for i, p in enumerate(prompts)]
+        for seq in seqs:
+            engine.scheduler.add(seq)
+        while engine.scheduler.has_unfinished():
+            engine.step()
+        return [seq.output_token_ids for seq in seqs]
+
+    for temperature in (0.0, 0.9):
+        params = SamplingParams(max_tokens=24, temperature=temperature)
+        options = dict(block_size=PAGE_SIZE["B"], num_blocks=64, max_model_len=256, max_num_seqs=8, seed=3)
+        free_run = generate(LLMEngine(model, EngineConfig(**options), []), params)
+        # tokens that end some requests early and at different steps, and leave others running
+        eos = [free_run[0][5], free_run[1][11], free_run[3][2]]
+        runs = {}
+        for overlap in (False, True):
+            engine = LLMEngine(model, EngineConfig(overlap_steps=overlap, **options), eos)
+            runs[overlap] = generate(engine, params)
+            engine.block_manager.check_invariants([])
+            assert engine.block_manager.num_free_blocks == 64
+            if overlap:
+                assert engine.stats.prepacked_steps > 0 and engine.stats.dropped_steps > 0
+            else:
+                assert engine.stats.prepacked_steps == 0 and engine.stats.dropped_steps == 0
+        assert runs[True] == runs[False]
+        assert any(len(tokens) < 24 for tokens in runs[True]) and any(len(tokens) == 24 for tokens in runs[True])
+        for tokens, free in zip(runs[True], free_run):
+            assert tokens == free[: len(tokens)]
+
+
 def test_eos_stops_generation_and_is_kept(peaked_model_folders):
     from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
     from mini_engine_b200.engine.loading import load_model
