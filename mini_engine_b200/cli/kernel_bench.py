@@ -100,6 +100,7 @@ def bench_attention(args, decode: bool) -> None:
 
     heads, kv_heads, d, page = args.heads, args.kv_heads, args.head_dim, args.page
     attention_bf16.FORCED_TMA_SPLITS = args.splits
+    attention_bf16.FORCED_TMA_WARPS = args.warps
     entries = args.batch if decode else 1
     context = args.context if decode else args.tokens
     new_tokens = 1 if decode else args.tokens
@@ -138,6 +139,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--page", type=int, default=16)
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--splits", type=int, default=0, help="decode-attention: CTAs per (request, KV head); 0: the engine's rule")
+    parser.add_argument("--warps", type=int, default=0, choices=[0, 6, 8], help="decode-attention: warps of a CTA; 0: the engine's rule")
     parser.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph")
     args = parser.parse_args(argv)
     global GRAPH

@@ -563,8 +563,6 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
 // heads, pages of a power of two >= 8 keys.  Rows of V outside the visible range are zeroed in
 // shared memory before the second product, so what a reused page still holds there cannot leak.
 // With one split the CTA writes the output itself; else partials as in the kernel above.
-constexpr int TMA_DECODE_WARPS = 8;
-constexpr int TMA_DECODE_THREADS = TMA_DECODE_WARPS * 32;
 constexpr int TMA_WARP_KEYS = 16;
 constexpr int TMA_MIN_TILES = 2;  // a CTA takes at least this many tiles: a partial more costs more than a tile
 
@@ -576,23 +574,25 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     return d;
 }
 
-template <int D>
+template <int D, int WARPS>
 constexpr int tma_decode_smem_bytes() {
-    return 1024 + TMA_DECODE_WARPS * 2 * (D / 64) * TMA_WARP_KEYS * 128 + 8 * D * 2 + TMA_DECODE_WARPS * 2 * 8;
+    return 1024 + WARPS * 2 * (D / 64) * TMA_WARP_KEYS * 128 + 8 * D * 2 + WARPS * 2 * 8;
 }
 
-template <int D>
-__global__ void __launch_bounds__(TMA_DECODE_THREADS, 3)
+template <int D, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 3 : 4)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             AttnParams p) {
     extern __shared__ uint8_t raw_smem[];
+    constexpr int TILE_KEYS = WARPS * TMA_WARP_KEYS;       // keys that the CTA takes at a time
+    constexpr int THREADS = WARPS * 32;
     constexpr int HALVES = D / 64;                         // 64-element (128-byte) column blocks of a row
     constexpr int HALF_BYTES = TMA_WARP_KEYS * 128;        // one column block of a warp's 16 keys
     constexpr int OPERAND_BYTES = HALVES * HALF_BYTES;     // a warp's K (or V) tile
     constexpr int STRIDE = D + 2;
     static_assert(8 * STRIDE * 4 <= 2 * OPERAND_BYTES, "a warp's partial must fit its tiles");
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
-    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem + TMA_DECODE_WARPS * 2 * OPERAND_BYTES);  // [8][D]
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem + WARPS * 2 * OPERAND_BYTES);  // [8][D]
     uint64_t* bars = reinterpret_cast<uint64_t*>(q_tile + 8 * D);
 
     const int kv_head = blockIdx.y, split = blockIdx.x, splits = gridDim.x;
@@ -617,7 +617,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int group = p.heads / p.kv_heads;
     // This CTA's tiles [tile, tile_end) among the request's visible ones.
-    const int lowest_tile = lowest / DECODE_CHUNK, tile_count = position / DECODE_CHUNK - lowest_tile + 1;
+    const int lowest_tile = lowest / TILE_KEYS, tile_count = position / TILE_KEYS - lowest_tile + 1;
     const int per_cta = max((tile_count + splits - 1) / splits, TMA_MIN_TILES);
     const int active = (tile_count + per_cta - 1) / per_cta;  // CTAs of this (request, KV head) with work
     int tile = lowest_tile + split * per_cta;
@@ -631,7 +631,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     int run_start = tile, my_page = -1;
     auto load_pages = [&]() {
         const int mine = run_start + lane / boxes;
-        const int index = (mine * DECODE_CHUNK + warp * TMA_WARP_KEYS + (lane % boxes) * box_rows) >> p.page_shift;
+        const int index = (mine * TILE_KEYS + warp * TMA_WARP_KEYS + (lane % boxes) * box_rows) >> p.page_shift;
         my_page = mine < tile_end && index < p.table_width ? table[index] : -1;
     };
     if (split < active) load_pages();
@@ -639,7 +639,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     pdl_wait();
     if (split >= active) return;
 
-    auto first_key_of = [&](int t) { return t * DECODE_CHUNK + warp * TMA_WARP_KEYS; };
+    auto first_key_of = [&](int t) { return t * TILE_KEYS + warp * TMA_WARP_KEYS; };
     auto visible = [&](int t) {  // this warp's 16 keys of tile t hold something the query sees
         const int first = first_key_of(t);
         return t < tile_end && first <= position && first + TMA_WARP_KEYS > lowest;
@@ -669,7 +669,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
 
     // Queries of the group: rows beyond it are zero.
-    for (int idx = threadIdx.x; idx < 8 * (D / 8); idx += TMA_DECODE_THREADS) {
+    for (int idx = threadIdx.x; idx < 8 * (D / 8); idx += THREADS) {
         const int row = idx / (D / 8), chunk = idx % (D / 8);
         uint4 value = make_uint4(0u, 0u, 0u, 0u);
         if (row < group)
@@ -807,17 +807,17 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 
     // Merge the eight warps (ascending keys): the CTA's partial, or with one split the output.
     const bool direct = splits == 1;
-    for (int idx = threadIdx.x; idx < group * STRIDE; idx += TMA_DECODE_THREADS) {
+    for (int idx = threadIdx.x; idx < group * STRIDE; idx += THREADS) {
         const int row = idx / STRIDE, col = idx % STRIDE;
-        float weight[TMA_DECODE_WARPS], total_max = -INFINITY;
+        float weight[WARPS], total_max = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < TMA_DECODE_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             weight[w] = reinterpret_cast<const float*>(smem + w * 2 * OPERAND_BYTES)[row * STRIDE + D];
             total_max = fmaxf(total_max, weight[w]);
         }
         float value = 0.0f, denom = 0.0f;
 #pragma unroll
-        for (int w = 0; w < TMA_DECODE_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             if (weight[w] == -INFINITY) continue;
             const float* part = reinterpret_cast<const float*>(smem + w * 2 * OPERAND_BYTES);
             const float scale = exp2f(weight[w] - total_max);
@@ -845,12 +845,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int row = warp; row < group; row += TMA_DECODE_WARPS) merge_head<D>(p, entry, kv_head * group + row, 0, active - 1, lane);
+    for (int row = warp; row < group; row += WARPS) merge_head<D>(p, entry, kv_head * group + row, 0, active - 1, lane);
 }
 
 // One warp per (entry, head) merges the partials of the kernel above when it got no counters.
-template <int D>
+template <int D, int WARPS>
 __global__ void __launch_bounds__(128) attention_decode_tma_merge_kernel(AttnParams p, int items) {
+    constexpr int TILE_KEYS = WARPS * TMA_WARP_KEYS;
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_trigger();
     pdl_wait();
@@ -859,7 +860,7 @@ __global__ void __launch_bounds__(128) attention_decode_tma_merge_kernel(AttnPar
     const int entry = p.entry_ids ? p.entry_ids[listed] : listed;
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
-    const int tile_count = position / DECODE_CHUNK - lowest / DECODE_CHUNK + 1;
+    const int tile_count = position / TILE_KEYS - lowest / TILE_KEYS + 1;
     const int per_cta = max((tile_count + p.max_splits - 1) / p.max_splits, TMA_MIN_TILES);
     merge_head<D>(p, entry, head, 0, (tile_count + per_cta - 1) / per_cta - 1, lane);
 }
@@ -897,11 +898,11 @@ static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) 
     return launch_kernel(attention_decode_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
 }
 
-template <int D>
+template <int D, int WARPS>
 static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map, const AttnParams& p, int entries,
                              cudaStream_t stream) {
-    constexpr int SMEM = tma_decode_smem_bytes<D>();
-    auto kernel = attention_decode_tma_kernel<D>;
+    constexpr int SMEM = tma_decode_smem_bytes<D, WARPS>();
+    auto kernel = attention_decode_tma_kernel<D, WARPS>;
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -909,10 +910,10 @@ static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map,
         configured = true;
     }
     dim3 grid(p.max_splits, p.kv_heads, entries);
-    const int status = launch_kernel(kernel, grid, TMA_DECODE_THREADS, SMEM, stream, k_map, v_map, p);
+    const int status = launch_kernel(kernel, grid, WARPS * 32, SMEM, stream, k_map, v_map, p);
     if (status != 0 || p.counters != nullptr || p.max_splits == 1) return status;
     const int items = entries * p.heads;
-    return launch_kernel(attention_decode_tma_merge_kernel<D>, (items + 3) / 4, 128, 0, stream, p, items);
+    return launch_kernel(attention_decode_tma_merge_kernel<D, WARPS>, (items + 3) / 4, 128, 0, stream, p, items);
 }
 
 static int shift_of(int page_size) {
@@ -970,23 +971,28 @@ ME_EXPORT int me_attention_decode_bf16_tiled(const void* q, const void* k_pages,
 // of one (request, KV head); `partials` holds entries * heads * splits * (head_dim + 2) floats and
 // `counters` entries * kv_heads zeros (both unused with one split).  Groups of up to 8 query
 // heads, pages of a power of two of at least 8 keys; other sizes are refused.
+// `warps`: 8 (tiles of 128 keys, three CTAs to an SM) or 6 (tiles of 96 keys, four to an SM).
 ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map, const void* q, const int* block_table,
                                            const int* cu_tokens, const int* context_lens, void* out, float* partials,
-                                           int* counters, float scale, int entries, int splits, int heads,
+                                           int* counters, float scale, int entries, int splits, int warps, int heads,
                                            int kv_heads, int head_dim, int page_size, int table_width, int window,
                                            const int* entry_ids, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (!sizes_ok(head_dim, heads, kv_heads) || heads / kv_heads > 8) return ME_ERR_UNSUPPORTED;
     if (shift_of(page_size) < 3) return ME_ERR_UNSUPPORTED;
     if (splits < 1 || splits > 65535 || (splits > 1 && partials == nullptr)) return ME_ERR_ARGUMENT;
+    if (warps != 8 && warps != 6) return ME_ERR_ARGUMENT;
     AttnParams p{static_cast<const __nv_bfloat16*>(q), nullptr, nullptr, block_table, cu_tokens, context_lens,
                  static_cast<__nv_bfloat16*>(out), partials, counters, entry_ids, scale * LOG2E, heads, kv_heads,
                  page_size, table_width, window, splits, shift_of(page_size), 0};
     CUtensorMap maps[2];
     memcpy(&maps[0], k_map, sizeof(CUtensorMap));
     memcpy(&maps[1], v_map, sizeof(CUtensorMap));
-    return head_dim == 128 ? launch_decode_tma<128>(maps[0], maps[1], p, entries, stream)
-                           : launch_decode_tma<64>(maps[0], maps[1], p, entries, stream);
+    if (warps == 8)
+        return head_dim == 128 ? launch_decode_tma<128, 8>(maps[0], maps[1], p, entries, stream)
+                               : launch_decode_tma<64, 8>(maps[0], maps[1], p, entries, stream);
+    return head_dim == 128 ? launch_decode_tma<128, 6>(maps[0], maps[1], p, entries, stream)
+                           : launch_decode_tma<64, 6>(maps[0], maps[1], p, entries, stream);
 }
 
 // First failure that a decode kernel recorded since the last call (a wait that ran out), or 0.

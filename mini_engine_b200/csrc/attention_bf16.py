@@ -116,7 +116,7 @@ def _library():
         lib.me_attention_portions_bf16.restype = c_int
         lib.me_attention_decode_bf16_tiled.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tiled.restype = c_int
-        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 8 + [c_void_p, c_void_p]
+        lib.me_attention_decode_bf16_tma.argtypes = [c_void_p] * 9 + [c_float] + [c_int] * 9 + [c_void_p, c_void_p]
         lib.me_attention_decode_bf16_tma.restype = c_int
         lib.me_attention_bf16_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_attention_bf16_take_error.restype = c_int
@@ -141,12 +141,29 @@ def decode_tiles_per_cta(entries: int, kv_heads: int, max_context_len: int) -> i
 
 
 FORCED_TMA_SPLITS = 0  # > 0: what kernel_bench's --splits asks for
+FORCED_TMA_WARPS = 0  # 6 or 8: what kernel_bench's --warps asks for
+RESIDENT_DECODE_CTAS_OF_SIX_WARPS = 4 * 148  # four CTAs of six warps fit an SM
 
 
-def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int) -> int:
+def tma_decode_warps(entries: int, kv_heads: int) -> int:
+    """Warps of a CTA of the TMA decode kernel: eight (128 keys at a time, three CTAs to an SM,
+    444 resident) or six (96 keys at a time, four CTAs to an SM, 592 resident).  Six when one CTA
+    per (request, KV head) then needs fewer waves: batch 64 with 8 KV heads is 512 pairs, one wave
+    of six-warp CTAs but a full and a nearly empty one of eight-warp CTAs (2,048 keys: 88.7 us
+    against 93.2 us with three CTAs per pair; 320 keys: 17.9 us against 22.0 us).  With as many
+    waves either way, eight warps are faster (batch 96: 122 us against 137 us)."""
+    if FORCED_TMA_WARPS:
+        return FORCED_TMA_WARPS
+    pairs = max(1, entries * kv_heads)
+    waves_of_eight = -(-pairs // RESIDENT_DECODE_CTAS)
+    waves_of_six = -(-pairs // RESIDENT_DECODE_CTAS_OF_SIX_WARPS)
+    return 6 if waves_of_six < waves_of_eight else 8
+
+
+def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int, warps: int = 8) -> int:
     """CTAs that share the keys of one (request, KV head) in the TMA decode kernel: as many as
-    fill one resident wave, at most one per 256 keys of the longest context.  The kernel divides
-    each request's own tiles evenly among them (two tiles of 128 keys or more per CTA).
+    fill one resident wave, at most one per two tiles of the longest context.  The kernel divides
+    each request's own tiles evenly among them (two tiles or more per CTA).
 
     Long contexts whose one wave would be lopsided (fewer CTAs than three quarters of the slots,
     so that some SMs hold two and some one) take three times as many: with several CTAs per slot
@@ -158,9 +175,9 @@ def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int) -> int:
     4,096 keys: 202 us against 208 us)."""
     if FORCED_TMA_SPLITS > 0:
         return FORCED_TMA_SPLITS
-    tiles = max(1, -(-max_context_len // DECODE_CHUNK))
+    tiles = max(1, -(-max_context_len // (warps * TMA_DECODE_KEYS)))
     pairs = max(1, entries * kv_heads)
-    slots = RESIDENT_DECODE_CTAS
+    slots = RESIDENT_DECODE_CTAS if warps == 8 else RESIDENT_DECODE_CTAS_OF_SIX_WARPS
     splits = max(1, min(slots // pairs, -(-tiles // 2), 64))
     if pairs > slots:
         if tiles >= 16 and pairs % slots < 0.25 * slots:
@@ -202,7 +219,8 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     for kind, entries, ids, longest in launches:
         ids_ptr = None if ids is None else ids.data_ptr()
         if kind == "decode" and tma_decode_kernel_takes(heads, kv_heads, page_size):
-            splits = tma_decode_splits(entries, kv_heads, ctx.max_context_len)
+            warps = tma_decode_warps(entries, kv_heads)
+            splits = tma_decode_splits(entries, kv_heads, ctx.max_context_len, warps)
             partials = counters = None
             if splits > 1:
                 partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32).data_ptr()
@@ -210,7 +228,7 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
             rows = min(page_size, TMA_DECODE_KEYS)
             code = _library().me_attention_decode_bf16_tma(
                 _page_map(k_pages, rows), _page_map(v_pages, rows), common[0], *common[3:], partials, counters, scale,
-                entries, splits, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, stream,
+                entries, splits, warps, heads, kv_heads, head_dim, page_size, width, window, ids_ptr, stream,
             )  # fmt: skip
             ops._check(code, "attention_decode_bf16_tma")
         elif kind == "decode":

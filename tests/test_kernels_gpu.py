@@ -377,6 +377,15 @@ BF16_ATTENTION_CASES = [
 ]
 
 
+@pytest.fixture(params=[0, 6, 8])
+def decode_warps(request, monkeypatch):
+    """Warps of a CTA of the TMA decode kernel: by the engine's rule, six (tiles of 96 keys) or eight."""
+    from mini_engine_b200.csrc import attention_bf16
+
+    monkeypatch.setattr(attention_bf16, "FORCED_TMA_WARPS", request.param)
+    return request.param
+
+
 def fake_context(data):
     """What the attention binding reads of a step context."""
     from types import SimpleNamespace
@@ -400,7 +409,7 @@ def fake_context(data):
 
 
 @pytest.mark.parametrize("case", BF16_ATTENTION_CASES)
-def test_paged_attention_bf16_tensor_core(case):
+def test_paged_attention_bf16_tensor_core(case, decode_warps):
     from mini_engine_b200.csrc import attention_bf16
 
     lengths, news, heads, kv_heads, head_dim, page = case
@@ -416,7 +425,7 @@ def test_paged_attention_bf16_tensor_core(case):
 
 
 @pytest.mark.parametrize("page", [8, 16, 64])
-def test_decode_ignores_what_reused_pages_still_hold(page):
+def test_decode_ignores_what_reused_pages_still_hold(page, decode_warps):
     """Slots behind a request's last token (and pages it does not own) hold infinities: none of it
     may reach the output, not even multiplied by a probability of zero."""
     from mini_engine_b200.csrc import attention_bf16
@@ -481,7 +490,7 @@ def test_paged_attention_tcgen05_growing_maximum(ramp):
 
 
 @pytest.mark.parametrize("news", [[1, 1], [90, 5]])
-def test_paged_attention_bf16_window(news):
+def test_paged_attention_bf16_window(news, decode_warps):
     from mini_engine_b200.csrc import attention_bf16
 
     heads, kv_heads, head_dim, page, window = 4, 2, 64, 8, 70
