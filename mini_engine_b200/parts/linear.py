@@ -32,6 +32,11 @@ DECODE_TOKENS = 64
 # followed by the activation kernel stream it a little faster than 192 long ones (measured at
 # batch 1: 3.24 against 3.31 ms a step; at batch 8: 3.61 against 3.58).
 GATED_FUSED_MIN_TOKENS = 5
+# The stacked kernel (5 to 64 tokens) has one CTA per 64 gated features and does not split the
+# reduction: with few features it leaves most SMs idle, and the split product with the activation
+# kernel behind it is faster (intermediate size 3,072, 48 CTAs: a decode step of 28 layers at batch
+# 32 takes 1.13 ms that way against 1.20 ms; at 12,288, 192 CTAs, the stacked kernel wins).
+GATED_STACKED_MIN_FEATURES = 128 * 64
 
 
 def partial_rows(max_tokens: int) -> int:
@@ -84,7 +89,8 @@ class GatedLinear:
         """``x [T, in]`` -> activated ``[T, inter]`` in the compute dtype."""
         tokens = x.shape[0]
         act = ctx.buffer(name + ".act", (tokens, self.inter), x.dtype)
-        if self.tensor_core and tokens >= GATED_FUSED_MIN_TOKENS:
+        fused = tokens >= GATED_FUSED_MIN_TOKENS and (tokens > DECODE_TOKENS or self.inter >= GATED_STACKED_MIN_FEATURES)
+        if self.tensor_core and fused:
             ops.gemm_tensor_core_swiglu(self.plan, x, act)
             return act
         both = self.linear.forward(x, ctx, name + ".gate_up")
