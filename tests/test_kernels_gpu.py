@@ -374,6 +374,8 @@ BF16_ATTENTION_CASES = [
     # many (request, KV head) pairs: a decode CTA walks two, then four tiles of 128 keys
     ([1 + (37 * i) % 700 for i in range(40)], [1] * 40, 8, 4, 64, 16),
     ([1 + (53 * i) % 900 for i in range(70)], [1] * 70, 8, 4, 128, 16),
+    # 480 (request, KV head) pairs: more than three CTAs of eight warps per SM hold, so six warps by the rule
+    ([1 + (29 * i) % 500 for i in range(60)], [1] * 60, 16, 8, 128, 16),
 ]
 
 
