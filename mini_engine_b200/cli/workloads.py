@@ -168,11 +168,13 @@ def main(argv: list[str] | None = None) -> int:
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - began
         tokens = sum(len(o) for o in outputs)
+        engine.block_manager.check_invariants([])  # every page is back and none is held twice
         row = {
             "workload": name, "output_tokens": tokens, "seconds": round(elapsed, 4),
             "tokens_per_second": round(tokens / elapsed, 1), "steps": engine.stats.steps,
             "graph_steps": engine.stats.graph_steps, "prompt_tokens_from_cache": engine.scheduler.num_cached_tokens,
-            "preemptions": engine.scheduler.num_preemptions,
+            "preemptions": engine.scheduler.num_preemptions, "steps_launched_ahead": engine.stats.prepacked_steps,
+            "steps_dropped": engine.stats.dropped_steps,
         }  # fmt: skip
         print(json.dumps(row), flush=True)
         return row
