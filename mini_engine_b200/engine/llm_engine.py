@@ -93,6 +93,8 @@ class LLMEngine:
         self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
         self.stats = EngineStats()
         self._in_flight: StepInFlight | None = None  # the decode step after the current one, already launched
+        self._rows_host = torch.empty((2, max(config.max_num_seqs, 1)), dtype=torch.int64).pin_memory()
+        self._rows = torch.empty(max(config.max_num_seqs, 1), dtype=torch.int64, device="cuda")
         self.decode_graphs: DecodeGraphs | None = None
         if config.cuda_graphs:
             self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
@@ -162,10 +164,18 @@ class LLMEngine:
             draw = self._draw(batch, logits, 0)
         if graph_step:
             self.stats.graph_steps += 1
-            prepacked = self._prepack_next(batch) if self.config.overlap_steps else None  # host work while the device runs
-            if prepacked is not None:
-                logits = self.decode_graphs.run_prepared(prepacked, draw.tokens)
-                self._in_flight = StepInFlight(prepacked, self._draw(batch, logits, 1))
+            ahead = self._prepack_next(batch) if self.config.overlap_steps else None  # host work while the device runs
+            if ahead is not None:
+                prepacked, staying = ahead
+                tokens = draw.tokens
+                if len(staying) < len(batch):  # the tokens of the requests that go on, picked on the device
+                    rows = len(staying)
+                    host = self._rows_host[self.stats.steps & 1]  # its copy of two steps ago has run by now
+                    host[:rows] = torch.tensor([i for i, _ in staying], dtype=torch.int64)
+                    self._rows[:rows].copy_(host[:rows], non_blocking=True)
+                    tokens = draw.tokens.index_select(0, self._rows[:rows])
+                logits = self.decode_graphs.run_prepared(prepacked, tokens)
+                self._in_flight = StepInFlight(prepacked, self._draw([item for _, item in staying], logits, 1))
         sampled = self.sampler.collect(draw)
         tokens = iter(sampled)
         next_tokens = [next(tokens) if item.samples else None for item in batch]
@@ -195,22 +205,28 @@ class LLMEngine:
 
     def _prepack_next(self, batch: list[ScheduledSeq]):
         """Lay out the decode step that follows `batch` if it is certain what it will hold unless
-        a request ends on its next token: nobody waits to be admitted, every request has room for
-        two more tokens and its pages can be had without preempting anyone.  The pages that this
-        takes are the ones the scheduler would take a step later; a request that ends instead
-        gives all its pages back anyway."""
+        a request ends on an end-of-sequence token: nobody waits to be admitted, and every request
+        that does not reach its `max_tokens` with the token drawn now can have the pages of one
+        more token without preempting anyone.  Returns the layout and the (row, item) pairs of
+        `batch` that go on, or None.  The pages that this takes are the ones the scheduler would
+        take a step later; a request that ends instead gives all its pages back anyway."""
         if self.scheduler.waiting:
             return None
-        entries = []
-        for item in batch:
+        entries, staying = [], []
+        for row, item in enumerate(batch):
             seq = item.seq
+            if seq.num_output_tokens + 1 >= seq.params.max_tokens:
+                continue  # ends on the token that the step in flight draws
             start = seq.num_computed_tokens + 1  # the step in flight computes one token
-            if seq.num_output_tokens + 2 > seq.params.max_tokens or start + 1 > self.config.max_model_len:
+            if start + 1 > self.config.max_model_len:
                 return None
             if not self.block_manager.try_allocate(seq.cache, start + 1):
                 return None
             entries.append(StepEntry(seq.cache, start, [0], (0,)))
-        return self.decode_graphs.prepare(entries)
+            staying.append((row, item))
+        if not entries:
+            return None
+        return self.decode_graphs.prepare(entries), staying
 
     def _graph_fits(self, batch: list[ScheduledSeq]) -> bool:
         graphs = self.decode_graphs

@@ -139,10 +139,12 @@ def test_steps_launched_ahead_never_change_the_tokens(peaked_model_folders):
     prompts = [random_ids(1200 + i, n, cfg["vocab"]) for i, n in enumerate((9, 30, 2, 17, 44))]
     _arch, _cfg, model = load_model(folder, torch.float32)
 
-    def generate(engine, params):  # the same request ids in every run: sampled tokens depend on them
-        seqs = [Sequence(p, params, seq_id=7000 + i) for i, p in enumerate(prompts)]
-        for seq in seqs:
-            engine.scheduler.add(seq)
+    def generate(engine, params, lengths=None):  # the same request ids in every run: sampled tokens depend on them
+        seqs = []
+        for i, prompt in enumerate(prompts):
+            mine = params if lengths is None else SamplingParams(max_tokens=lengths[i], temperature=params.temperature)
+            seqs.append(Sequence(prompt, mine, seq_id=7000 + i))
+            engine.scheduler.add(seqs[-1])
         while engine.scheduler.has_unfinished():
             engine.step()
         return [seq.output_token_ids for seq in seqs]
@@ -167,6 +169,17 @@ def test_steps_launched_ahead_never_change_the_tokens(peaked_model_folders):
         assert any(len(tokens) < 24 for tokens in runs[True]) and any(len(tokens) == 24 for tokens in runs[True])
         for tokens, free in zip(runs[True], free_run):
             assert tokens == free[: len(tokens)]
+        # Requests that end at their own max_tokens: known ahead, so the step after goes on without
+        # them, launched ahead like any other, and none is dropped.
+        lengths = [24, 7, 15, 24, 3]
+        engine = LLMEngine(model, EngineConfig(**options), [])
+        limited = generate(engine, params, lengths)
+        assert [len(tokens) for tokens in limited] == lengths
+        for tokens, free in zip(limited, free_run):
+            assert tokens == free[: len(tokens)]
+        assert engine.stats.dropped_steps == 0
+        assert engine.stats.prepacked_steps == engine.stats.graph_steps - 1  # all but the first decode step
+        engine.block_manager.check_invariants([])
 
 
 def test_eos_stops_generation_and_is_kept(peaked_model_folders):
