@@ -234,7 +234,9 @@ def run_ours(args) -> dict:
 
     # ------------------------------------------------- decode through the Python entry point
     def time_e2e(batch: int, steps: int, warmup: int) -> tuple[float, int, int]:
-        params = SamplingParams(max_tokens=steps + warmup + 2, ignore_eos=True)
+        # The first requests already decode while the later ones' prompts run (one step per prompt
+        # under this token budget): room for those tokens too, so that nobody ends inside the timed steps.
+        params = SamplingParams(max_tokens=steps + warmup + batch + 2, ignore_eos=True)
         seqs = [engine.add_request(random_prompt(CONTEXT), params) for _ in range(batch)]
         while any(s.num_computed_tokens < s.num_prompt_tokens for s in seqs):
             engine.step()  # prompts, in portions under the token budget

@@ -636,8 +636,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     };
     if (split < active) load_pages();
     __syncwarp();  // the warp's barriers are initialised
-    pdl_wait();
-    if (split >= active) return;
 
     auto first_key_of = [&](int t) { return t * TILE_KEYS + warp * TMA_WARP_KEYS; };
     auto visible = [&](int t) {  // this warp's 16 keys of tile t hold something the query sees
@@ -662,8 +660,21 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             tma_load_2d(dst + half * HALF_BYTES + box * box_rows * 128, map, half * 64, row, bar);
         }
     };
-    while (tile < tile_end && !visible(tile)) ++tile;  // a window may start inside the first tile
-    if (tile < tile_end) {
+    // The keys and values of a tile that does not hold the query's own position were written in
+    // earlier steps, which are complete: the CTA's first tile is then on its way before the wait
+    // for the previous kernel (which writes the newest key and value, and the queries).
+    bool fetching = false;
+    if (split < active) {
+        while (tile < tile_end && !visible(tile)) ++tile;  // a window may start inside the first tile
+        if (tile < tile_end && tile != position / TILE_KEYS) {
+            issue(tile, k_tile, &k_map, k_bar);
+            issue(tile, v_tile, &v_map, v_bar);
+            fetching = true;
+        }
+    }
+    pdl_wait();
+    if (split >= active) return;
+    if (!fetching && tile < tile_end) {
         issue(tile, k_tile, &k_map, k_bar);
         issue(tile, v_tile, &v_map, v_bar);
     }

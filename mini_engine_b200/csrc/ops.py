@@ -146,6 +146,15 @@ def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -
     _check(code, "embedding")
 
 
+def pick_tokens(tokens: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[i] = tokens[rows[i]]``, all int32 on the device."""
+    _need(tokens, torch.int32, "tokens"), _need(rows, torch.int32, "rows"), _need(out, torch.int32, "out")
+    if rows.shape[0] != out.shape[0]:
+        raise KernelError("one row index per output")
+    fn = _fn("sampling", "me_pick_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(tokens), _ptr(rows), _ptr(out), out.shape[0], _stream()), "pick_tokens")
+
+
 def add_rmsnorm(
     x: torch.Tensor,
     pending: torch.Tensor | None,

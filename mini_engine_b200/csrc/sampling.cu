@@ -133,3 +133,17 @@ ME_EXPORT int me_sample(const float* logits, const float* temperatures, const fl
     if (rows <= 0) return 0;
     return launch_kernel(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, temperatures, uniforms, out, vocab);
 }
+
+// out[i] = tokens[rows[i]]: the drawn tokens of the requests that go on, in the order of the next
+// step, without a round trip to the host.
+__global__ void pick_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ rows, int* __restrict__ out, int count) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = tokens[rows[i]];
+}
+
+ME_EXPORT int me_pick_tokens(const int* tokens, const int* rows, int* out, int count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    return launch_kernel(pick_tokens_kernel, (count + 127) / 128, 128, 0, stream, tokens, rows, out, count);
+}

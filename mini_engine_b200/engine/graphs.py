@@ -80,10 +80,11 @@ class DecodeGraphs:
         bucket = self.bucket_for(len(entries))
         return self.runner.pack(entries, pad_entries_to=bucket, want_every_entry=True, build_context=False, defer_copy=True)
 
-    def run_prepared(self, prepacked, token_ids: Seq[int] | torch.Tensor) -> torch.Tensor:
+    def run_prepared(self, prepacked, token_ids: Seq[int] | torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         """The step that :meth:`prepare` laid out, now that its token ids are known: to the host,
-        or only to the device (an int32 tensor that the sampler wrote)."""
-        self.runner.commit(prepacked, token_ids)
+        or only to the device (an int32 tensor that the sampler wrote, of which ``rows`` picks the
+        entries' tokens if given)."""
+        self.runner.commit(prepacked, token_ids, rows)
         self.graphs[prepacked.total_entries].replay()
         return self.logits[prepacked.total_entries][: prepacked.real]
 

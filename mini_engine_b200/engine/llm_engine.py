@@ -93,8 +93,8 @@ class LLMEngine:
         self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
         self.stats = EngineStats()
         self._in_flight: StepInFlight | None = None  # the decode step after the current one, already launched
-        self._rows_host = torch.empty((2, max(config.max_num_seqs, 1)), dtype=torch.int64).pin_memory()
-        self._rows = torch.empty(max(config.max_num_seqs, 1), dtype=torch.int64, device="cuda")
+        self._rows_host = torch.empty((2, max(config.max_num_seqs, 1)), dtype=torch.int32).pin_memory()
+        self._rows = torch.empty(max(config.max_num_seqs, 1), dtype=torch.int32, device="cuda")
         self.decode_graphs: DecodeGraphs | None = None
         if config.cuda_graphs:
             self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
@@ -167,14 +167,14 @@ class LLMEngine:
             ahead = self._prepack_next(batch) if self.config.overlap_steps else None  # host work while the device runs
             if ahead is not None:
                 prepacked, staying = ahead
-                tokens = draw.tokens
-                if len(staying) < len(batch):  # the tokens of the requests that go on, picked on the device
-                    rows = len(staying)
+                rows = None
+                if len(staying) < len(batch):  # the tokens of the requests that go on are picked on the device
+                    count = len(staying)
                     host = self._rows_host[self.stats.steps & 1]  # its copy of two steps ago has run by now
-                    host[:rows] = torch.tensor([i for i, _ in staying], dtype=torch.int64)
-                    self._rows[:rows].copy_(host[:rows], non_blocking=True)
-                    tokens = draw.tokens.index_select(0, self._rows[:rows])
-                logits = self.decode_graphs.run_prepared(prepacked, tokens)
+                    host[:count] = torch.tensor([row for row, _ in staying], dtype=torch.int32)
+                    rows = self._rows[:count]
+                    rows.copy_(host[:count], non_blocking=True)
+                logits = self.decode_graphs.run_prepared(prepacked, draw.tokens, rows)
                 self._in_flight = StepInFlight(prepacked, self._draw([item for _, item in staying], logits, 1))
         sampled = self.sampler.collect(draw)
         tokens = iter(sampled)

@@ -24,6 +24,7 @@ import torch
 
 from mini_engine_b200.cache.manager import NULL_PAGE, RequestCache
 from mini_engine_b200.cache.storage import CacheLayout, allocate_cache
+from mini_engine_b200.csrc import ops
 from mini_engine_b200.engine.workspace import Workspace
 from mini_engine_b200.parts.base import StepContext
 from mini_engine_b200.parts.model import DecoderModel
@@ -322,26 +323,31 @@ class ModelRunner:
         )
         return ctx, at(o_rows, len(wanted_rows))
 
-    def commit(self, prepacked: "Prepacked", token_ids: Seq[int] | torch.Tensor) -> None:
+    def commit(self, prepacked: "Prepacked", token_ids: Seq[int] | torch.Tensor, rows: torch.Tensor | None = None) -> None:
         """Put the token ids into a block that :meth:`pack` laid out with ``defer_copy`` and copy
-        it to the device.  Token ids that are still on the device (an int32 tensor, one per entry:
-        what the sampler drew in the step before) are copied there into the device's block, after
-        the block itself, so the host need not know them yet."""
+        it to the device.  Token ids that are still on the device (an int32 tensor: what the
+        sampler drew in the step before) are copied there into the device's block, after the
+        block itself, so the host need not know them yet; entry i takes ``token_ids[rows[i]]``
+        when ``rows`` (int32, on the device) is given, else ``token_ids[i]``."""
         used = prepacked.used
         ids = slice(prepacked.ids_offset, prepacked.ids_offset + prepacked.real)
         on_device = isinstance(token_ids, torch.Tensor)
-        if len(token_ids) != prepacked.real:
+        if (len(token_ids) if rows is None else len(rows)) != prepacked.real:
             raise ValueError("one token id per entry of the prepacked step")
         if on_device:
             if token_ids.dtype != torch.int32 or not token_ids.is_cuda:
                 raise ValueError("token ids on the device must be int32")
         else:
+            if rows is not None:
+                raise ValueError("rows pick among token ids on the device")
             if min(token_ids) < 0 or max(token_ids) >= self.vocab_size:
                 raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
             self._host_np[prepacked.flip][ids] = token_ids
         self._device[:used].copy_(self._host[prepacked.flip][:used], non_blocking=True)
         self._copied[prepacked.flip].record()
-        if on_device:
+        if on_device and rows is not None:
+            ops.pick_tokens(token_ids, rows, self._device[ids])
+        elif on_device:
             self._device[ids].copy_(token_ids, non_blocking=True)
         self.last_h2d_bytes = used * 4
 
