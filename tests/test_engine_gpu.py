@@ -182,6 +182,55 @@ def test_steps_launched_ahead_never_change_the_tokens(peaked_model_folders):
         engine.block_manager.check_invariants([])
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_overlapped_steps_with_arrivals_small_pools_and_early_ends(seed, peaked_model_folders):
+    """Random workloads (requests that arrive while others decode, pools that force preemption,
+    shared prefixes, end-of-sequence tokens, own max_tokens and temperatures): steps launched
+    ahead give the tokens of strictly serial steps, and every page comes back."""
+    import random
+
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.engine.loading import load_model
+    from mini_engine_b200.engine.sequence import Sequence
+
+    folder = peaked_model_folders["B"]
+    _, cfg = load_plain(folder)
+    _arch, _cfg, model = load_model(folder, torch.float32)
+    rng = random.Random(seed)
+    page, vocab = PAGE_SIZE["B"], cfg["vocab"]
+    count = rng.randint(3, 10)
+    shared = [rng.randrange(vocab) for _ in range(rng.choice([0, 2 * page, 5 * page]))]
+    prompts = [shared + [rng.randrange(vocab) for _ in range(rng.randint(1, 50))] for _ in range(count)]
+    lengths = [rng.randint(1, 30) for _ in range(count)]
+    temperatures = [rng.choice([0.0, 0.0, 0.7, 1.3]) for _ in range(count)]
+    arrivals = sorted(rng.randint(0, 12) for _ in range(count))  # the step before which each request is added
+    blocks = rng.choice([24, 40])
+    eos = [rng.randrange(vocab) for _ in range(rng.choice([0, 3, 40]))]
+    options = dict(
+        block_size=page, num_blocks=blocks, max_model_len=128, max_num_seqs=rng.choice([3, 8]),
+        max_num_batched_tokens=rng.choice([16, 64, 512]), seed=seed, enable_prefix_caching=rng.random() < 0.7,
+    )  # fmt: skip
+    runs = {}
+    for overlap in (False, True):
+        engine = LLMEngine(model, EngineConfig(overlap_steps=overlap, **options), eos)
+        seqs = [
+            Sequence(p, SamplingParams(max_tokens=m, temperature=t), seq_id=9000 + i)
+            for i, (p, m, t) in enumerate(zip(prompts, lengths, temperatures))
+        ]
+        step = added = 0
+        while added < count or engine.scheduler.has_unfinished():
+            while added < count and arrivals[added] <= step:
+                engine.scheduler.add(seqs[added])
+                added += 1
+            if engine.scheduler.has_unfinished():
+                engine.step()
+            step += 1
+        engine.block_manager.check_invariants([])
+        assert engine.block_manager.num_free_blocks == blocks
+        runs[overlap] = [seq.output_token_ids for seq in seqs]
+    assert runs[True] == runs[False]
+
+
 def test_eos_stops_generation_and_is_kept(peaked_model_folders):
     from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
     from mini_engine_b200.engine.loading import load_model
