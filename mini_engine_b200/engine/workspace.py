@@ -21,6 +21,10 @@ class Workspace:
         self.device = torch.device(device)
         self._buffers: dict[tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False  # set while a graph is captured: no new allocation may happen
+        # Buffers that were replaced by larger ones.  A captured graph keeps the address of the
+        # buffer it was captured with and goes on writing and reading there, so the memory must
+        # neither be freed nor given to anyone else.
+        self._retired: list[torch.Tensor] = []
 
     def _flat(self, name: str, elements: int, dtype: torch.dtype) -> torch.Tensor:
         key = (name, dtype)
@@ -28,6 +32,8 @@ class Workspace:
         if held is None or held.numel() < elements:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow during graph capture")
+            if held is not None:
+                self._retired.append(held)
             held = torch.empty(elements, dtype=dtype, device=self.device)
             self._buffers[key] = held
         return held
@@ -60,9 +66,11 @@ class Workspace:
         if held is None or held.numel() < count:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow during graph capture")
+            if held is not None:
+                self._retired.append(held)
             held = torch.zeros(max(count, 1024), dtype=torch.int32, device=self.device)
             self._buffers[key] = held
         return held[:count]
 
     def bytes_held(self) -> int:
-        return sum(t.numel() * t.element_size() for t in self._buffers.values())
+        return sum(t.numel() * t.element_size() for t in [*self._buffers.values(), *self._retired])

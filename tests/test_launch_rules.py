@@ -80,3 +80,25 @@ def test_partial_sum_buffer_holds_every_split_of_a_decode_step():
         for tokens in range(1, min(max_tokens, linear.DECODE_TOKENS) + 1):
             assert rows >= linear.MAX_SPLITS * tokens
         assert rows >= max_tokens
+
+
+def test_a_buffer_that_grows_leaves_the_old_one_alive():
+    """A captured graph holds the address of the buffer it was captured with: when a later step
+    needs a larger one, the old memory stays with the workspace instead of going back to the
+    allocator, where someone else could be given it."""
+    import torch
+
+    from mini_engine_b200.engine.workspace import Workspace
+
+    workspace = Workspace(8, device="cpu")
+    small = workspace.growing("attn.partials", (4, 2, 3), torch.float32)
+    counters = workspace.zeroed("attn.counters", 10)
+    addresses = {small.data_ptr(), counters.data_ptr()}
+    del small, counters
+    large = workspace.growing("attn.partials", (40, 2, 30), torch.float32)
+    more = workspace.zeroed("attn.counters", 5000)
+    assert {t.data_ptr() for t in workspace._retired} == addresses
+    assert large.data_ptr() not in addresses and more.data_ptr() not in addresses
+    assert int(more.sum()) == 0
+    again = workspace.growing("attn.partials", (40, 2, 30), torch.float32)
+    assert again.data_ptr() == large.data_ptr() and len(workspace._retired) == 2  # the same size: no new buffer
