@@ -7,7 +7,6 @@ from __future__ import annotations
 import json
 import subprocess
 import sys
-from pathlib import Path
 
 import numpy as np
 import pytest

@@ -11,7 +11,6 @@ failure has run everything else before.
 
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_void_p
 
 import pytest
