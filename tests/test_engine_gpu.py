@@ -301,3 +301,19 @@ def test_pool_sized_from_free_memory(peaked_model_folders):
     _, cfg = load_plain(folder)
     prompts = [random_ids(900, 21, cfg["vocab"])]
     assert_same_tokens(engine.generate(prompts, SamplingParams(max_tokens=4)), plain_greedy(folder, prompts, 4))
+
+
+def test_engine_profiler_reports_phases(capsys):
+    """The phase profiler runs the engine's own step both ways and prints one JSON line each."""
+    import json
+
+    from mini_engine_b200.cli import profile_engine
+
+    assert profile_engine.main(["--steps", "4", "--requests", "3", "--prompt-len", "20", "--num-blocks", "64"]) == 0
+    rows = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    assert len(rows) == 2
+    running, isolated = rows
+    assert running["steps_launched_ahead"] > 0 and isolated["steps_launched_ahead"] == 0
+    assert running["kernel_launches_per_step"] > 100  # 28 layers of eight kernels and more
+    assert "wait for the token ids" in running["phases_us_per_step"]
+    assert "lay out + H2D + graph launch" in isolated["phases_us_per_step"]
