@@ -205,18 +205,21 @@ class LLMEngine:
 
     def _prepack_next(self, batch: list[ScheduledSeq]):
         """Lay out the decode step that follows `batch` if it is certain what it will hold unless
-        a request ends on an end-of-sequence token: nobody waits to be admitted, and every request
-        that does not reach its `max_tokens` with the token drawn now can have the pages of one
-        more token without preempting anyone.  Returns the layout and the (row, item) pairs of
+        a request ends on an end-of-sequence token: nobody can be admitted (no request waits, or every
+        place stays taken), and every request that does not reach its `max_tokens` with the token
+        drawn now can have the pages of one more token without preempting anyone.  Returns the layout and the (row, item) pairs of
         `batch` that go on, or None.  The pages that this takes are the ones the scheduler would
         take a step later; a request that ends instead gives all its pages back anyway."""
-        if self.scheduler.waiting:
-            return None
+        ends = [item.seq.num_output_tokens + 1 >= item.seq.params.max_tokens for item in batch]  # on the token being drawn
+        if len(batch) != len(self.scheduler.running):
+            return None  # the token budget left someone out: the next batch is another
+        if self.scheduler.waiting and len(batch) - sum(ends) < self.config.max_num_seqs:
+            return None  # a place is free: the next step admits a request
         entries, staying = [], []
         for row, item in enumerate(batch):
             seq = item.seq
-            if seq.num_output_tokens + 1 >= seq.params.max_tokens:
-                continue  # ends on the token that the step in flight draws
+            if ends[row]:
+                continue
             start = seq.num_computed_tokens + 1  # the step in flight computes one token
             if start + 1 > self.config.max_model_len:
                 return None
