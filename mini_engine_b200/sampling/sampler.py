@@ -44,6 +44,7 @@ class Sampler:
         self.seed = seed
         self.device = torch.device(device)
         self._host = torch.empty((2, 2, max_rows), dtype=torch.float32).pin_memory()  # [side][temperature, uniform]
+        self._host_np = self._host.numpy()
         self._params = torch.empty((2, 2, max_rows), dtype=torch.float32, device=self.device)
         self._tokens = torch.empty(max_rows, dtype=torch.int32, device=self.device)
         self._tokens_host = torch.empty((2, max_rows), dtype=torch.int32).pin_memory()
@@ -67,12 +68,13 @@ class Sampler:
         if all(t == 0 for t in temperatures):
             ops.sample(logits, None, None, out)
         else:
-            host = self._host[side]
-            for i in range(rows):
-                host[0, i] = temperatures[i]
-                host[1, i] = uniform_for(self.seed, request_ids[i], token_indices[i]) if temperatures[i] else 0.0
+            host = self._host_np[side]  # written through numpy: one assignment per row of the block
+            host[0, :rows] = temperatures
+            host[1, :rows] = [
+                uniform_for(self.seed, request_ids[i], token_indices[i]) if temperatures[i] else 0.0 for i in range(rows)
+            ]
             params = self._params[side]
-            params[:, :rows].copy_(host[:, :rows], non_blocking=True)
+            params[:, :rows].copy_(self._host[side][:, :rows], non_blocking=True)
             ops.sample(logits, params[0, :rows], params[1, :rows], out)
         self._tokens_host[side, :rows].copy_(out, non_blocking=True)
         self._arrived[side].record()
