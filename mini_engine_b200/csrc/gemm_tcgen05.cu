@@ -418,7 +418,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const int t0 = (tile % p.token_tiles) * PAIR_T + token_offset;
     const int n0 = ((tile / p.token_tiles) * 2 + rank) * BLOCK_N;
     const int b_row = t0 + rank * (width / 2);  // this CTA's half of the tile's tokens
-    const int iterations = p.k_blocks;
+    // grid.y cuts the reduction (a plain product only): split s takes k blocks [kb_begin, +iterations)
+    // and writes slice s of the output.
+    const int split = blockIdx.y;
+    const int kb_begin = split * p.k_blocks_per_split;
+    const int iterations = min(p.k_blocks_per_split, p.k_blocks - kb_begin);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -439,20 +443,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             for (int i = 0; i < early; ++i) {
                 uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
                 if (rank == 0) mbar_expect_tx(&full[i], 2 * C::STAGE_BYTES);  // the bytes of both CTAs
-                tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[i]);
-                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[i]);
+                tma_load_2d_pair(a_tile, &map_w, (kb_begin + i) * BLOCK_K, n0, &full[i]);
+                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, (kb_begin + i) * BLOCK_K, p.dual_row_offset + n0, &full[i]);
             }
             pdl_wait();
             for (int i = 0; i < early; ++i)
-                tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, b_row, &full[i]);
+                tma_load_2d_pair(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb_begin + i) * BLOCK_K, b_row, &full[i]);
             for (int i = early; i < iterations; ++i) {
                 const int stage = i % C::STAGES;
                 if (!mbar_wait(&empty[stage], ((i / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (10 << 8) | stage); break; }
                 uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
                 if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
-                tma_load_2d_pair(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
-                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
-                tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, b_row, &full[stage]);
+                tma_load_2d_pair(a_tile, &map_w, (kb_begin + i) * BLOCK_K, n0, &full[stage]);
+                if (DUAL) tma_load_2d_pair(a_tile + BLOCK_N * BLOCK_K * 2, &map_w, (kb_begin + i) * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d_pair(a_tile + C::A_BYTES, &map_x, (kb_begin + i) * BLOCK_K, b_row, &full[stage]);
             }
         }
     } else if (warp == 1) {
@@ -497,7 +501,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     float v[16];
                     tcgen05_ld16(lane_base + c0, v);
                     if (n < p.outs) {
-                        float* out = static_cast<float*>(p.out);
+                        float* out = static_cast<float*>(p.out) + static_cast<size_t>(split) * p.tokens * p.outs;
 #pragma unroll
                         for (int c = 0; c < 16; ++c)
                             if (t0 + c0 + c < p.tokens) out[static_cast<size_t>(t0 + c0 + c) * p.outs + n] = v[c];
@@ -806,7 +810,7 @@ ME_EXPORT int me_gemm_tcgen05(const void* map_w, const void* map_x, float* out, 
 
 
 template <bool DUAL>
-static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream, int splits = 1) {
     using C = PairConfig<DUAL>;
     auto kernel = gemm_tcgen05_pair_kernel<DUAL>;
     static bool configured = false;
@@ -819,6 +823,7 @@ static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     GemmParams q = p;
+    q.k_blocks_per_split = (p.k_blocks + splits - 1) / splits;
     q.token_tiles = (p.tokens + PAIR_T - 1) / PAIR_T;
     const int tiles = q.token_tiles * ((p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N));
     const int pairs = sms / 2 > 0 ? sms / 2 : 1;
@@ -829,10 +834,10 @@ static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const
     // cutting a half-full wave in three or four made the products 20-60 % slower).
     q.tail_parts = 1;
     while (q.tail_parts < 4 && (tiles - q.full_tiles) * q.tail_parts * 2 <= pairs) q.tail_parts *= 2;
-    if (tiles < pairs) { q.full_tiles = tiles; q.tail_parts = 1; }  // a single, partly filled wave: nothing to gain
+    if (tiles < pairs || splits > 1) { q.full_tiles = tiles; q.tail_parts = 1; }  // a single, partly filled wave: nothing to gain
     const int clusters = q.full_tiles + (tiles - q.full_tiles) * q.tail_parts;
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(2 * clusters, 1, 1);
+    config.gridDim = dim3(2 * clusters, splits, 1);
     config.blockDim = dim3(GEMM_THREADS);
     config.dynamicSmemBytes = C::SMEM_BYTES;
     config.stream = stream;
@@ -858,6 +863,21 @@ ME_EXPORT int me_gemm_tcgen05_pair(const void* map_w, const void* map_x, float* 
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1};
     return launch_pair<false>(w, x, p, stream);
+}
+
+// out[s][t][n] (float32) = the part of x[t] . w[n] over the k blocks of split s, by CTA pairs: for
+// products of a few hundred tokens, whose tiles alone do not fill the GPU.  A pair takes a third
+// less out of L2 per flop than two lone CTAs, which is what bounds those products.
+ME_EXPORT int me_gemm_tcgen05_pair_split(const void* map_w, const void* map_x, float* out, int tokens, int outs, int inner,
+                                         int splits, cudaStream_t stream) {
+    if (tokens <= 0 || outs <= 0) return 0;
+    alignas(64) CUtensorMap w, x;
+    memcpy(&w, map_w, sizeof(w));
+    memcpy(&x, map_x, sizeof(x));
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1};
+    if (splits < 1 || splits > p.k_blocks) return ME_ERR_ARGUMENT;
+    if ((splits - 1) * ((p.k_blocks + splits - 1) / splits) >= p.k_blocks) return ME_ERR_ARGUMENT;  // an empty split
+    return launch_pair<false>(w, x, p, stream, splits);
 }
 
 ME_EXPORT int me_gemm_tcgen05_pair_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,

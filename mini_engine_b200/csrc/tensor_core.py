@@ -27,6 +27,12 @@ USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
 # The persistent pair kernel (two accumulator buffers, epilogue under the next tile's MMAs);
 # "0" falls back to one tile per pair of CTAs.
 USE_PERSISTENT = os.environ.get("MINI_ENGINE_B200_PERSISTENT", "1") != "0"
+# Products of 129 to 1,024 tokens whose reduction is split run on CTA pairs too (each split its own
+# pairs) when a split is long: 48 k blocks and more (the down projection of Qwen3-8B: 256 tokens
+# 33.1 -> 31.3 us, 512 tokens 48.9 -> 44.2 us); with 16 to 32 k blocks per split the lone CTAs are as
+# fast or 2 % faster.
+USE_PAIR_SPLITS = os.environ.get("MINI_ENGINE_B200_PAIR_SPLITS", "1") != "0"
+PAIR_SPLIT_MIN_K_BLOCKS = 48
 
 STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
 USE_PERSISTENT_GATED = os.environ.get("MINI_ENGINE_B200_PERSISTENT_GATED", "1") != "0"
@@ -50,6 +56,8 @@ def _library():
         lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_swiglu.restype = c_int
         lib.me_gemm_tcgen05_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_pair_split.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_pair_split.restype = c_int
         lib.me_gemm_tcgen05_pair.restype = c_int
         lib.me_gemm_tcgen05_pair_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_swiglu.restype = c_int
@@ -148,6 +156,10 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
     if tokens > PAIR_MIN_TOKENS and splits == 1 and USE_PAIRS:
         entry = _library().me_gemm_tcgen05_persistent if USE_PERSISTENT else _library().me_gemm_tcgen05_pair
         code = entry(plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream)
+    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PAIR_SPLITS and -(-plan.inner // BLOCK_K) >= PAIR_SPLIT_MIN_K_BLOCKS * splits:
+        code = _library().me_gemm_tcgen05_pair_split(
+            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, splits, stream
+        )
     else:
         code = _library().me_gemm_tcgen05(
             plan.map, _activation_map(x, tile), out.data_ptr(), tokens, plan.rows, plan.inner, tile, splits, stream

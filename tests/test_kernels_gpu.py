@@ -59,6 +59,9 @@ TC_SHAPES = [
     # CTA pairs with a partly filled last wave: its tiles are cut in two (88 tiles) and in four (82)
     (2048, 2600, 128),
     (512, 10496, 72),
+    # a few hundred tokens and a long reduction: each split of it runs on CTA pairs
+    (300, 4000, 12352),
+    (640, 2100, 6200),
 ]
 
 
@@ -75,7 +78,9 @@ def test_gemm_tensor_core(tokens, outs, inner):
         out = torch.full((splits, tokens, outs), float("nan"), device="cuda")
         tensor_core.gemm(plan, x, out, splits)
         assert tensor_core.take_error() == 0
-        assert rel_error(out.sum(0), want) < 1e-5, f"splits={splits}"
+        # float32 accumulation: the error grows with the square root of the reduction's length
+        # (as in test_gemm_simt); 1e-5 is the bound up to 4,096, the engine's usual length.
+        assert rel_error(out.sum(0), want) < 1e-5 * max(1.0, math.sqrt(inner / 4096)), f"splits={splits}"
 
 
 def test_gemm_tensor_core_finds_one_large_product():
