@@ -102,3 +102,17 @@ def test_a_buffer_that_grows_leaves_the_old_one_alive():
     assert int(more.sum()) == 0
     again = workspace.growing("attn.partials", (40, 2, 30), torch.float32)
     assert again.data_ptr() == large.data_ptr() and len(workspace._retired) == 2  # the same size: no new buffer
+
+
+@pytest.mark.parametrize("max_batch", [1, 2, 3, 8, 9, 16, 17, 64, 100, 256])
+def test_graph_buckets_cover_every_batch_up_to_the_cap(max_batch):
+    """Buckets 1, 2, 4, 8, then multiples of 16 up to the request cap (the reference's,
+    src/mini_engine/cuda_graphs.py:28-40): ascending, the last one the cap itself, and every batch
+    size has a bucket that is at least as large and wastes less than 16 rows (or half the bucket)."""
+    from mini_engine_b200.engine.graphs import batch_buckets
+
+    buckets = batch_buckets(max_batch)
+    assert buckets == sorted(set(buckets)) and buckets[-1] == max_batch and buckets[0] >= 1
+    for batch in range(1, max_batch + 1):
+        bucket = next(b for b in buckets if b >= batch)
+        assert bucket - batch < max(16, bucket // 2 + 1)
