@@ -37,10 +37,11 @@ QWEN3_8B = dict(
     max_position_embeddings=40960, tie_word_embeddings=False,
 )  # fmt: skip
 CONTEXT = 2048  # tokens each request holds when decode is timed
+REPEATS = 3  # the timed decode region is run this often; the median counts, the spread is printed
 PREFILL_TOKENS = 2048
 MAX_MODEL_LEN = 4096  # benchmark context length of the configuration
 BLOCK_SIZE = 16
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_kind": "burst", "source": "fallback"}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def load_peaks() -> dict:
@@ -48,14 +49,13 @@ def load_peaks() -> dict:
     if path.is_file():
         try:
             raw = json.loads(path.read_text())
-            peaks = {
+            return {
                 "hbm_gbs": float(raw["hbm_gbs"]),
-                # the prefill is a long step under the power cap: the sustained figure where there is one
-                "bf16_tflops": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
-                "bf16_kind": "sustained" if raw.get("bf16_tflops_sustained") else "burst",
+                "bf16_tflops": float(raw["bf16_tflops"]),  # best single product (burst)
+                # a product repeated for seconds under the power cap; the prefill is such a step
+                "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"]),
                 "source": "measured",
             }
-            return peaks
         except (KeyError, ValueError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -145,7 +145,7 @@ def run_ours(args) -> dict:
     layers = cfg.num_hidden_layers
     peaks = load_peaks()
     max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
-    steps_total = args.steps + args.warmup + 8
+    steps_total = REPEATS * args.steps + args.warmup + 8
     pages_per_request = -(-(CONTEXT + steps_total + 1) // BLOCK_SIZE)
     engine_config = EngineConfig(
         block_size=BLOCK_SIZE, num_blocks=max_batch * pages_per_request + 8, max_num_seqs=max_batch,
@@ -191,7 +191,9 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         return caches
 
-    def time_decode(batch: int, steps: int, warmup: int) -> tuple[float, int]:
+    def time_decode(batch: int, steps: int, warmup: int, repeats: int) -> tuple[list[float], int]:
+        """Times ``repeats`` regions of ``steps`` decode steps each, one after the other (the
+        contexts go on growing); returns the milliseconds per step of every region."""
         caches = fill_contexts(batch)
         tokens = random_prompt(batch)
         position = CONTEXT
@@ -207,28 +209,31 @@ def run_ours(args) -> dict:
         for _ in range(warmup):
             one_step()
         torch.cuda.synchronize()
-        launches_before = ops.launch_count()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(steps):
-            one_step()
-        end.record()
-        torch.cuda.synchronize()
-        eager_launches = ops.launch_count() - launches_before
-        in_graph = graphs.launches[graphs.bucket_for(batch)] * steps
+        regions, launches = [], 0
+        for _ in range(repeats):
+            launches_before = ops.launch_count()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(steps):
+                one_step()
+            end.record()
+            torch.cuda.synchronize()
+            regions.append(start.elapsed_time(end) / steps)
+            launches = ops.launch_count() - launches_before + graphs.launches[graphs.bucket_for(batch)] * steps
         for cache in caches:
             engine.block_manager.free(cache)
-        return start.elapsed_time(end) / steps, eager_launches + in_graph
+        return regions, launches
 
     with ClockSampler() as clocks:
-        ms_per_step, launches = time_decode(args.batch, args.steps, args.warmup)
+        regions, launches = time_decode(args.batch, args.steps, args.warmup, REPEATS)
     clock_summary = clocks.summary()
+    ms_per_step = statistics.median(regions)
     value = args.batch / (ms_per_step / 1e3)
 
     points = {}
     if not args.skip_points:
         for batch in (1, 64):
-            ms, _ = time_decode(batch, max(args.steps // 2, 5), args.warmup)
+            ms = statistics.median(time_decode(batch, max(args.steps // 2, 5), args.warmup, REPEATS)[0])
             points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 1)
             points[f"decode_b{batch}_ms"] = round(ms, 4)
 
@@ -260,22 +265,36 @@ def run_ours(args) -> dict:
     if args.fp32_check:
         fp32_check = check_against_fp32(engine, cfg, random_prompt(args.fp32_check))
 
-    achieved_gbs = decode_bytes(cfg, layers, args.batch, CONTEXT + args.warmup + args.steps // 2) / (ms_per_step / 1e3) / 1e9
-    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    return result_line(
+        "ours", cfg, layers, full_layers, args, peaks, regions, e2e_value, h2d_bytes, d2h_bytes, prefill_ms, points,
+        clock_summary, "captured CUDA graph per step + sampling kernel",
+        gpu_launches=launches, device_error=device_error, **({"fp32_check": fp32_check} if fp32_check else {}),
+    )  # fmt: skip
+
+
+def result_line(impl, cfg, layers, full_layers, args, peaks, regions, e2e_value, h2d_bytes, d2h_bytes, prefill_ms,
+                points, clock_summary, decode_path, **more) -> dict:  # fmt: skip
+    """The one JSON line of a run; both arms print the same keys from the same formulas."""
+    ms_per_step = statistics.median(regions)
+    middle = CONTEXT + args.warmup + len(regions) * args.steps // 2  # mean context length of the timed steps
+    achieved_gbs = decode_bytes(cfg, layers, args.batch, middle) / (ms_per_step / 1e3) / 1e9
+    tflops = prefill_flops(cfg, layers, PREFILL_TOKENS) / (prefill_ms / 1e3) / 1e12
     return {
         "metric": "decode tok/s at batch 8, 2,048-token contexts (Qwen3-8B layer sizes)",
-        "value": round(value, 1),
+        "value": round(args.batch / (ms_per_step / 1e3), 1),
         "unit": "tokens/s",
         "n_gpus": 1,
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": round(ms_per_step, 4),
+        "ms_per_step_regions": [round(r, 4) for r in regions],
+        "spread": round((max(regions) - min(regions)) / ms_per_step, 4),
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic: seeded random token ids, random-init weights N(0, 0.02)",
-        "impl": "ours",
+        "impl": impl,
         "config": {
             "model": "Qwen3-8B layer sizes",
             "layers": layers,
@@ -290,25 +309,28 @@ def run_ours(args) -> dict:
             "seq_len": CONTEXT,
             "max_model_len": MAX_MODEL_LEN,
             "kv_block_size": BLOCK_SIZE,
+            "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "single GPU",
-            "decode": "captured CUDA graph per step + sampling kernel",
             "l2": "inputs larger than L2: each step reads all weights",
             "peaks": peaks["source"],
         },
+        "decode_path": decode_path,
         "e2e": {
             "value": round(e2e_value, 1),
             "unit": "tokens/s",
             "h2d_bytes_per_step": h2d_bytes,
             "d2h_bytes_per_step": d2h_bytes,
         },
-        "gpu_launches": launches,
         "prefill": {
             "value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1),
             "tokens": PREFILL_TOKENS,
             "ms": round(prefill_ms, 3),
-            "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
-            "peak_tflops": peaks["bf16_tflops"],
-            "peak_kind": peaks["bf16_kind"],
+            "tflops": round(tflops, 1),
+            # a 2,048-token step lasts tens of milliseconds under the power cap: the sustained peak
+            "frac": round(tflops / peaks["bf16_tflops_sustained"], 4),
+            "frac_of_burst": round(tflops / peaks["bf16_tflops"], 4),
+            "peak_tflops_sustained": peaks["bf16_tflops_sustained"],
+            "peak_tflops_burst": peaks["bf16_tflops"],
         },
         "roofline": {
             "bound": "hbm",
@@ -319,8 +341,7 @@ def run_ours(args) -> dict:
         },
         "points": points,
         "clocks": clock_summary,
-        "device_error": device_error,
-        **({"fp32_check": fp32_check} if fp32_check else {}),
+        **more,
     }
 
 
@@ -360,6 +381,166 @@ def check_against_fp32(engine, cfg, prompt: list[int]) -> dict:
     }
 
 
+REFERENCE_DIR = ROOT / "baseline" / "_ref"
+
+
+def locate_reference() -> str | None:
+    """Puts the reference's package on the path and returns None, or says why it cannot.
+
+    The package is pure Python; its offline ``pip install`` fails only because its build backend
+    is not in the image, so ``baseline/_ref/mini_engine`` is an unmodified file copy of its
+    ``src/mini_engine`` (made here from ``$MINI_ENGINE_REF`` when the folder is not there yet)."""
+    import os
+    import shutil
+
+    package = REFERENCE_DIR / "mini_engine"
+    if not (package / "engine.py").is_file():
+        source = os.environ.get("MINI_ENGINE_REF", "")
+        if not (source and (Path(source) / "mini_engine" / "engine.py").is_file()):
+            return "no copy of YuvGev00/mini-engine under baseline/_ref and MINI_ENGINE_REF does not name its src folder"
+        REFERENCE_DIR.mkdir(parents=True, exist_ok=True)
+        shutil.copytree(Path(source) / "mini_engine", package)
+    sys.path.insert(0, str(REFERENCE_DIR))
+    return None
+
+
+def run_reference(args) -> dict:
+    """The same measurement through YuvGev00/mini-engine's own engine, unmodified.
+
+    Its ``Qwen3ForCausalLM(ModelConfig(...))`` is built from the same numbers with N(0, 0.02)
+    weights, wrapped in its ``LLMEngine`` with its stock CUDA options (Triton paged attention,
+    captured decode graphs, ``engine.py:59-108``), and driven through ``add_request`` and
+    ``step`` (``engine.py:145-196``) only.  Nothing of this repository's package is imported."""
+    import types
+
+    why = locate_reference()
+    if why:
+        return {"impl": "reference", "unavailable": why}
+    import torch
+
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device in this process"}
+    from mini_engine.engine import EngineConfig, LLMEngine
+    from mini_engine.model import ModelConfig, Qwen3ForCausalLM
+    from mini_engine.sequence import SamplingParams
+
+    sizes = dict(QWEN3_8B)
+    full_layers = sizes["num_hidden_layers"]
+    if args.layers:
+        sizes["num_hidden_layers"] = args.layers
+    cfg = types.SimpleNamespace(**sizes)
+    layers = cfg.num_hidden_layers
+    peaks = load_peaks()
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = Qwen3ForCausalLM(ModelConfig(
+            vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+            num_layers=layers, num_heads=cfg.num_attention_heads, num_kv_heads=cfg.num_key_value_heads,
+            head_dim=cfg.head_dim, rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta,
+            max_position_embeddings=cfg.max_position_embeddings, tie_word_embeddings=cfg.tie_word_embeddings,
+        ))  # fmt: skip
+    with torch.no_grad():
+        for name, parameter in model.named_parameters():
+            if parameter.dim() == 2:  # linear and embedding weights; the norms keep their ones
+                parameter.normal_(0.0, 0.02)
+    model = model.to(dtype=torch.bfloat16)
+    generator = torch.Generator().manual_seed(1)
+
+    def random_prompt(n: int) -> list[int]:
+        return torch.randint(0, cfg.vocab_size, (n,), generator=generator).tolist()
+
+    def new_engine(batch: int, budget: int, tokens_per_request: int) -> "LLMEngine":
+        pages = -(-tokens_per_request // BLOCK_SIZE)
+        return LLMEngine(model, EngineConfig(
+            block_size=BLOCK_SIZE, num_blocks=batch * pages + 8, max_num_seqs=batch, max_num_batched_tokens=budget,
+            max_model_len=MAX_MODEL_LEN, enable_prefix_caching=False, device="cuda", dtype=torch.bfloat16, seed=0,
+            cuda_graphs=True,
+        ))  # fmt: skip
+
+    def timed(function) -> float:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        function()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    # ------------------------------------------------------------------ prefill: one whole prompt per step
+    engine = new_engine(1, PREFILL_TOKENS, PREFILL_TOKENS + 16)
+    prefill_times = []
+    for i in range(3 + 3):
+        engine.add_request(random_prompt(PREFILL_TOKENS), SamplingParams(max_tokens=1, ignore_eos=True))
+        torch.cuda.synchronize()
+        ms = timed(engine.step)  # the prompt, its one sampled token, finished
+        if i >= 3:
+            prefill_times.append(ms)
+    prefill_ms = statistics.median(prefill_times)
+    del engine
+
+    # ------------------------------------------------------------------ decode
+    def decode_engine(batch: int, steps_needed: int):
+        """An engine whose ``batch`` requests all hold CONTEXT tokens and decode.  Prompts run in
+        portions of 512 tokens: its padded prompt attention (``attention.py:128-157``) makes
+        scores of batch x longest-portion x context, which a 2,048-token portion beside 63
+        decoding requests would not fit."""
+        engine = new_engine(batch, 512 if batch > 8 else PREFILL_TOKENS, CONTEXT + steps_needed + batch * 4 + 16)
+        params = SamplingParams(max_tokens=min(steps_needed + batch * 4 + 8, MAX_MODEL_LEN - CONTEXT), ignore_eos=True)
+        seqs = [engine.add_request(random_prompt(CONTEXT), params) for _ in range(batch)]
+        while any(s.num_computed_tokens < s.num_prompt_tokens for s in seqs):
+            engine.step()
+        return engine
+
+    def time_decode(batch: int, steps: int, warmup: int, repeats: int, e2e: bool):
+        engine = decode_engine(batch, warmup + (repeats + int(e2e)) * steps)
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        regions = [timed(lambda: [engine.step() for _ in range(steps)]) / steps for _ in range(repeats)]
+        wall = None
+        if e2e:
+            torch.cuda.synchronize()
+            began = time.perf_counter()
+            for _ in range(steps):
+                engine.step()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - began
+        return regions, wall, engine
+
+    with ClockSampler() as clocks:
+        regions, wall, engine = time_decode(args.batch, args.steps, args.warmup, REPEATS, True)
+    clock_summary = clocks.summary()
+    e2e_value = args.batch * args.steps / wall
+    # what its graph path copies per step (cuda_graphs.py:124-136): int64 ids, positions, slots;
+    # context and query lengths; the block-table rows of the batch.  Back: the sampled ids.
+    backend, graphs = engine.attention_backend, engine.decode_graphs
+    bucket = next(b for b in graphs.buckets if b >= args.batch) if graphs else args.batch
+    width = -(-(CONTEXT + args.warmup + (REPEATS + 1) * args.steps) // BLOCK_SIZE)
+    h2d_bytes = 8 * (3 * bucket + 2 * bucket + bucket * width)
+    d2h_bytes = 8 * args.batch
+    decode_path = (
+        f"its attention backend {backend!r}, "
+        + ("its captured CUDA graph per step" if graphs else "eager launches (it captured no graphs)")
+        + ", library matrix products, torch argmax"
+    )
+    del engine, graphs
+
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            try:
+                ms = statistics.median(time_decode(batch, max(args.steps // 2, 5), args.warmup, REPEATS, False)[0])
+                points[f"decode_b{batch}"] = round(batch / (ms / 1e3), 1)
+                points[f"decode_b{batch}_ms"] = round(ms, 4)
+            except (RuntimeError, AssertionError) as error:  # e.g. out of memory in its padded attention
+                points[f"decode_b{batch}_error"] = str(error).splitlines()[0][:200]
+                torch.cuda.empty_cache()
+
+    return result_line(
+        "reference", cfg, layers, full_layers, args, peaks, regions, e2e_value, h2d_bytes, d2h_bytes, prefill_ms,
+        points, clock_summary, decode_path,
+    )  # fmt: skip
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -372,18 +553,14 @@ def main() -> int:
     parser.add_argument("--fp32-check", type=int, default=0, metavar="TOKENS",
                         help="also run a prompt of this many tokens through the float32 path and compare logits")
     args = parser.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({
-            "impl": "reference",
-            "unavailable": "YuvGev00/mini-engine does not install offline: its build backend uv_build is not in "
-                           "the image or the wheelhouse (pip install --no-index --no-build-isolation fails)",
-        }))  # fmt: skip
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
     print(json.dumps(run_ours(args)))
     return 0
 
