@@ -173,6 +173,106 @@ def test_weight_dtypes_by_role(tmp_path):
     assert loaded["lm_head.weight"].data_ptr() == loaded["model.embed_tokens.weight"].data_ptr()  # tied
 
 
+def _split_into_shards(folder, parts: int) -> dict[str, str]:
+    """Rewrites ``model.safetensors`` of a folder as ``parts`` shard files with the usual names;
+    returns tensor name -> file name."""
+    from safetensors.torch import load_file, save_file
+
+    state = {name: tensor.clone() for name, tensor in load_file(str(folder / "model.safetensors")).items()}
+    (folder / "model.safetensors").unlink()
+    names = sorted(state)
+    weight_map = {}
+    for part in range(parts):
+        file_name = f"model-{part + 1:05d}-of-{parts:05d}.safetensors"
+        mine = names[part::parts]  # interleaved: a layer's tensors lie in different files
+        save_file({name: state[name] for name in mine}, str(folder / file_name))
+        weight_map.update({name: file_name for name in mine})
+    return weight_map
+
+
+@pytest.mark.parametrize("with_index", [False, True])
+def test_a_model_in_several_shards_loads_tensor_by_tensor(tmp_path, with_index):
+    """A real checkpoint is several files, with or without ``model.safetensors.index.json``; the
+    reference reads every file of the folder in sorted order
+    (src/mini_engine/engine.py:126-128 of YuvGev00/mini-engine)."""
+    from mini_engine_b200.config import Qwen3Config, architecture_for
+    from mini_engine_b200.parts.model import declared_weights
+    from mini_engine_b200.weights import load_weights, write_random_model
+
+    cfg = Qwen3Config.from_dict(CONFIGS["B"])
+    specs = declared_weights(architecture_for(cfg.architecture).build_spec(cfg))
+    whole = load_weights(write_random_model(tmp_path / "whole", cfg, 5, torch.float32), specs, torch.float32, "cpu")
+    folder = write_random_model(tmp_path / "sharded", cfg, 5, torch.float32)
+    weight_map = _split_into_shards(folder, 3)
+    if with_index:
+        index = {"metadata": {"total_size": 0}, "weight_map": weight_map}
+        (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+        # a file that the index does not name is not part of the model
+        from safetensors.torch import save_file
+
+        save_file({"model.layers.0.stray.weight": torch.zeros(3)}, str(folder / "stray.safetensors"))
+    assert len(list(folder.glob("model-*.safetensors"))) == 3
+    sharded = load_weights(folder, specs, torch.float32, "cpu")
+    assert sorted(sharded) == sorted(whole)
+    for name, tensor in whole.items():
+        assert torch.equal(sharded[name], tensor), name
+
+
+def test_a_shard_that_is_missing_is_reported_by_its_tensors(tmp_path):
+    from mini_engine_b200.config import Qwen3Config, architecture_for
+    from mini_engine_b200.parts.model import declared_weights
+    from mini_engine_b200.weights import WeightError, load_weights, write_random_model
+
+    cfg = Qwen3Config.from_dict(CONFIGS["A"])
+    specs = declared_weights(architecture_for(cfg.architecture).build_spec(cfg))
+    folder = write_random_model(tmp_path / "m", cfg, 5, torch.float32)
+    weight_map = _split_into_shards(folder, 3)
+    (folder / "model-00002-of-00003.safetensors").unlink()
+    with pytest.raises(WeightError) as raised:
+        load_weights(folder, specs, torch.float32, "cpu")
+    gone = sorted(name for name, file_name in weight_map.items() if file_name.startswith("model-00002"))
+    assert raised.value.missing == gone and not raised.value.unexpected
+
+
+def test_a_tied_checkpoint_that_also_stores_its_head(tmp_path):
+    """With tied embeddings a stored ``lm_head.weight`` is dropped and the head is the embedding's
+    own storage (src/mini_engine/model.py:192-194 of YuvGev00/mini-engine)."""
+    from safetensors.torch import load_file, save_file
+
+    from mini_engine_b200.config import Qwen3Config, architecture_for
+    from mini_engine_b200.parts.model import declared_weights
+    from mini_engine_b200.weights import load_weights, write_random_model
+
+    cfg = Qwen3Config.from_dict(CONFIGS["A"])
+    assert cfg.tie_word_embeddings
+    specs = declared_weights(architecture_for(cfg.architecture).build_spec(cfg))
+    folder = write_random_model(tmp_path / "m", cfg, 6, torch.float32)
+    state = {name: tensor.clone() for name, tensor in load_file(str(folder / "model.safetensors")).items()}
+    state["lm_head.weight"] = torch.full_like(state["model.embed_tokens.weight"], 9.0)  # a stale copy
+    save_file(state, str(folder / "model.safetensors"))
+    loaded = load_weights(folder, specs, torch.float32, "cpu")
+    assert loaded["lm_head.weight"].data_ptr() == loaded["model.embed_tokens.weight"].data_ptr()
+    assert torch.equal(loaded["lm_head.weight"], state["model.embed_tokens.weight"])
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator is counter-based: any element can be made alone, in any chunking, and a
+    matrix made in pieces equals the matrix made at once."""
+    from mini_engine_b200.weights import random_init
+
+    key = random_init._seed_for(3, "some.weight")
+    whole = random_init.standard_normal(5000, key)
+    assert torch.equal(random_init.standard_normal(100, key, first=4100), whole[4100:4200])
+    old = random_init._CHUNK
+    try:
+        random_init._CHUNK = 777  # chunk edges must not show
+        assert torch.equal(random_init.standard_normal(5000, key), whole)
+    finally:
+        random_init._CHUNK = old
+    assert abs(float(whole.mean())) < 0.05 and abs(float(whole.std()) - 1.0) < 0.05
+    assert not torch.equal(random_init.standard_normal(5000, random_init._seed_for(3, "other.weight")), whole)
+
+
 def test_engine_config_validation():
     from mini_engine_b200 import EngineConfig, SamplingParams
 
