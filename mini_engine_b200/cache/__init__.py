@@ -6,8 +6,9 @@ from mini_engine_b200.cache.manager import (
     GroupSpec,
     PagePool,
     RequestCache,
+    SlotGroupSpec,
     SlotPool,
     hash_page,
 )
 
-__all__ = ["NULL_PAGE", "CacheManager", "GroupSpec", "PagePool", "RequestCache", "SlotPool", "hash_page"]
+__all__ = ["NULL_PAGE", "CacheManager", "GroupSpec", "PagePool", "RequestCache", "SlotGroupSpec", "SlotPool", "hash_page"]

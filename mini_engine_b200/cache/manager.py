@@ -38,10 +38,27 @@ def hash_page(parent: bytes, token_ids: Seq[int]) -> bytes:
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """What the manager needs to know of a cache group."""
+    """What the manager needs to know of a cache group.
+
+    ``num_blocks`` is the size of the group's own page pool (``None``: the manager's default); a
+    group with a window needs far fewer pages than one that keeps every key.  ``shareable`` says
+    whether what the group holds for a prefix can be found again by content hash; a group that
+    cannot offer that (per-request state without snapshots, for one) says so here, and because a
+    prefix hit skips the shared tokens in *every* layer, one such group means that requests of
+    this model are always computed from their first token."""
 
     name: str
     window: int | None = None  # None: every key is kept
+    num_blocks: int | None = None
+    shareable: bool = True
+
+
+@dataclass(frozen=True)
+class SlotGroupSpec:
+    """Per-request state of fixed size, kept in one slot per live request."""
+
+    name: str
+    shareable: bool = False  # no snapshot of the state exists at page boundaries
 
 
 @dataclass
@@ -142,19 +159,21 @@ class CacheManager:
         block_size: int,
         max_num_seqs: int,
         enable_prefix_caching: bool = True,
-        has_state: bool = False,
+        slot_groups: Seq[SlotGroupSpec] = (),
     ):
         if num_blocks < 1 or block_size < 1 or max_num_seqs < 1:
             raise ValueError("num_blocks, block_size and max_num_seqs must be positive")
         self.groups = list(groups)
+        self.slot_groups = list(slot_groups)
         self.num_blocks = num_blocks
         self.block_size = block_size
-        self.pools = [PagePool(num_blocks) for _ in self.groups]
+        self.pools = [PagePool(g.num_blocks or num_blocks) for g in self.groups]
         self.slots = SlotPool(max_num_seqs)
-        # A prefix hit skips the computation of the shared tokens.  That is only sound when
-        # everything those tokens left behind is in shareable pages: no window has dropped
-        # some of them and no mixer carries a state that the skipped tokens would have fed.
-        shareable = all(g.window is None for g in self.groups) and not has_state
+        # A prefix hit skips the computation of the shared tokens in every layer.  That is only
+        # sound when each group can supply what those tokens left behind: a group that keeps every
+        # key, all their pages; a group with a window, the pages that the window still reaches at
+        # the end of the shared prefix; a group that says it is not shareable, nothing.
+        shareable = all(g.shareable for g in [*self.groups, *self.slot_groups])
         self.enable_prefix_caching = enable_prefix_caching and shareable and bool(self.groups)
 
     # ------------------------------------------------------------------ queries
@@ -171,6 +190,12 @@ class CacheManager:
         return min((p.num_free for p in self.pools), default=self.num_blocks)
 
     @property
+    def smallest_pool(self) -> int:
+        """Pages that a single request could ever hold in a group that keeps every key (a group
+        with a window never holds a whole request, so its pool does not bound a request)."""
+        return min((p.num_pages for g, p in zip(self.groups, self.pools) if g.window is None), default=self.num_blocks)
+
+    @property
     def num_evictions(self) -> int:
         return sum(p.num_evictions for p in self.pools)
 
@@ -183,22 +208,38 @@ class CacheManager:
         return max(0, num_computed - group.window + 1) // self.block_size
 
     def match_prefix(self, token_ids: Seq[int]) -> list[list[int]]:
-        """Per group, the longest run of cached full pages that prefix ``token_ids`` (the
-        same length in every group).  Only the first ``len - 1`` tokens are eligible: at
-        least one token must be computed to have logits for the next
-        (src/mini_engine/block_manager.py:62-79)."""
+        """Per group, the block table of the longest prefix of ``token_ids`` that the cache still
+        holds, in whole pages (the same length in every group).  Only the first ``len - 1`` tokens
+        are eligible: at least one token must be computed to have logits for the next
+        (src/mini_engine/block_manager.py:62-79).  A group that keeps every key must hold every
+        page of the prefix; a group with a window only those that the window still reaches from
+        the prefix's end, and its table has ``NULL_PAGE`` before them."""
         if not self.enable_prefix_caching:
             return [[] for _ in self.groups]
-        hits: list[list[int]] = [[] for _ in self.groups]
-        parent = ROOT_HASH
         bs = self.block_size
+        found: list[list[int | None]] = [[] for _ in self.groups]
+        parent = ROOT_HASH
+        best = 0
         for i in range((len(token_ids) - 1) // bs):
             parent = hash_page(parent, token_ids[i * bs : (i + 1) * bs])
-            pages = [pool.hash_to_page.get(parent) for pool in self.pools]
-            if any(page is None for page in pages):
+            stop = False
+            for group, pool, pages in zip(self.groups, self.pools, found):
+                page = pool.hash_to_page.get(parent)
+                pages.append(page)
+                if page is None and group.window is None:
+                    stop = True  # a full group has a gap: nothing longer can be whole
+            if stop:
                 break
-            for table, page in zip(hits, pages):
-                table.append(page)
+            length = i + 1
+            if all(
+                None not in pages[self._first_needed_page(group, length * bs) : length]
+                for group, pages in zip(self.groups, found)
+            ):
+                best = length
+        hits: list[list[int]] = []
+        for group, pages in zip(self.groups, found):
+            first = self._first_needed_page(group, best * bs)
+            hits.append([NULL_PAGE if i < first else pages[i] for i in range(best)])
         return hits
 
     # ---------------------------------------------------------------- mutations
@@ -216,7 +257,7 @@ class CacheManager:
             if seed and table:
                 raise ValueError("cached pages can only seed an empty block table")
             fresh = max(target - len(table) - len(seed), 0)
-            revived = sum(1 for page in seed if pool.ref_counts[page] == 0)
+            revived = sum(1 for page in seed if page != NULL_PAGE and pool.ref_counts[page] == 0)
             if fresh + revived > pool.num_free:
                 return False
         if req.state_slot < 0:
@@ -226,7 +267,8 @@ class CacheManager:
             req.state_slot = slot
         for pool, table, seed in zip(self.pools, req.block_tables, cached):
             for page in seed:
-                pool.share(page)
+                if page != NULL_PAGE:
+                    pool.share(page)
                 table.append(page)
                 req.version += 1
             while len(table) < target:
@@ -273,7 +315,8 @@ class CacheManager:
             value = hash_page(parent, token_ids[i * bs : (i + 1) * bs])
             req.page_hashes.append(value)
             for pool, table in zip(self.pools, req.block_tables):
-                pool.set_hash(table[i], value)
+                if table[i] != NULL_PAGE:  # a page behind a window that a prefix hit never held
+                    pool.set_hash(table[i], value)
 
     def reset_prefix_cache(self) -> None:
         for pool in self.pools:

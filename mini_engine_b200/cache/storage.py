@@ -16,7 +16,7 @@ from dataclasses import dataclass
 
 import torch
 
-from mini_engine_b200.cache.manager import GroupSpec
+from mini_engine_b200.cache.manager import GroupSpec, SlotGroupSpec
 from mini_engine_b200.parts.base import LayerCache, PagedCacheSpec, StateSpec
 
 
@@ -26,8 +26,17 @@ class CacheLayout:
     group_specs: list[PagedCacheSpec]
     views: list[LayerCache]  # one per execution entry
     arrays: list[torch.Tensor]  # per group [entries, 2, pages + 1, kv_heads, block_size, head_dim]
-    has_state: bool
+    slot_groups: list[SlotGroupSpec]  # one per execution entry whose mixer keeps per-request state
     bytes_per_token: int
+
+    @property
+    def has_state(self) -> bool:
+        return bool(self.slot_groups)
+
+    @property
+    def spare_pages(self) -> list[int]:
+        """Per group, the page that no request owns (the last of its array)."""
+        return [g.num_blocks for g in self.groups]
 
 
 def plan_groups(needs) -> tuple[list[PagedCacheSpec], list[int | None]]:
@@ -51,10 +60,22 @@ def plan_groups(needs) -> tuple[list[PagedCacheSpec], list[int | None]]:
     return specs, group_of
 
 
-def group_names(specs: list[PagedCacheSpec]) -> list[GroupSpec]:
+def pages_of_group(spec: PagedCacheSpec, num_blocks: int, block_size: int, max_num_seqs: int, max_step_tokens: int) -> int:
+    """Pages of a group's pool.  A group that keeps every key gets ``num_blocks``.  A group with a
+    window never holds more of a request than the window, the tokens of the step that is being
+    computed (their pages are taken before the step and the pages behind the window go back after
+    it) and the two pages that the ends of that range may share with their neighbours; so that
+    much for every request that can be live is all it can ever use."""
+    if spec.window is None:
+        return num_blocks
+    per_request = -(-(spec.window + max_step_tokens) // block_size) + 2
+    return max(1, min(num_blocks, max_num_seqs * per_request))
+
+
+def group_names(specs: list[PagedCacheSpec], pages: list[int]) -> list[GroupSpec]:
     return [
-        GroupSpec(f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f":w{s.window}" if s.window else ""), s.window)
-        for i, s in enumerate(specs)
+        GroupSpec(f"kv{i}:{s.kv_heads}x{s.head_dim}" + (f":w{s.window}" if s.window else ""), s.window, count)
+        for i, (s, count) in enumerate(zip(specs, pages))
     ]
 
 
@@ -97,8 +118,15 @@ def allocate_cache(
     max_num_seqs: int,
     dtype: torch.dtype,
     device: str | torch.device = "cuda",
+    max_step_tokens: int | None = None,
 ) -> CacheLayout:
+    """``max_step_tokens`` (the token budget of a step) bounds what a group with a window can
+    hold; without it such a group is sized like one that keeps every key."""
     specs, group_of = plan_groups(needs)
+    pages = [
+        pages_of_group(s, num_blocks, block_size, max_num_seqs, max_step_tokens) if max_step_tokens else num_blocks
+        for s in specs
+    ]
     owners: list[list[int]] = [[] for _ in specs]
     for entry, (paged, _state, cache_of) in enumerate(needs):
         if paged is not None and cache_of is None:
@@ -106,12 +134,12 @@ def allocate_cache(
     element = torch.empty((), dtype=dtype).element_size()
     arrays = [
         torch.zeros(
-            (len(entries), 2, num_blocks + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device
+            (len(entries), 2, count + 1, s.kv_heads, block_size, s.head_dim), dtype=dtype, device=device
         )
-        for s, entries in zip(specs, owners)
+        for s, entries, count in zip(specs, owners, pages)
     ]
     views: list[LayerCache] = []
-    has_state = False
+    slot_groups: list[SlotGroupSpec] = []
     for entry, (paged, state, cache_of) in enumerate(needs):
         view = LayerCache()
         if paged is not None:
@@ -121,8 +149,8 @@ def allocate_cache(
             view.group, view.k, view.v = g, arrays[g][index, 0], arrays[g][index, 1]
             view.writes = cache_of is None
         if state is not None:
-            has_state = True
+            slot_groups.append(SlotGroupSpec(f"state{entry}:{'x'.join(map(str, state.shape))}"))
             view.state = torch.zeros((max_num_seqs + 1, *state.shape), dtype=state.dtype, device=device)
         views.append(view)
     per_token = sum(2 * len(e) * s.kv_heads * s.head_dim * element for s, e in zip(specs, owners))
-    return CacheLayout(group_names(specs), specs, views, arrays, has_state, per_token)
+    return CacheLayout(group_names(specs, pages), specs, views, arrays, slot_groups, per_token)

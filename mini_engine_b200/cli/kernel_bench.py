@@ -99,8 +99,6 @@ def bench_attention(args, decode: bool) -> None:
     from mini_engine_b200.csrc import attention_bf16
 
     heads, kv_heads, d, page = args.heads, args.kv_heads, args.head_dim, args.page
-    attention_bf16.FORCED_TMA_SPLITS = args.splits
-    attention_bf16.FORCED_TMA_WARPS = args.warps
     entries = args.batch if decode else 1
     context = args.context if decode else args.tokens
     new_tokens = 1 if decode else args.tokens
@@ -114,7 +112,8 @@ def bench_attention(args, decode: bool) -> None:
     ctx = attention_context(entries, new_tokens, context)
 
     def run(i: int) -> None:
-        attention_bf16.paged_attention(q, k[i % layers], v[i % layers], table, ctx, out, heads, kv_heads, d, d**-0.5, 0)
+        attention_bf16.paged_attention(q, k[i % layers], v[i % layers], table, ctx, out, heads, kv_heads, d, d**-0.5, 0,
+                                       decode_warps=args.warps or None, decode_splits_per_pair=args.splits or None)  # fmt: skip
 
     ms = timed(run, args.iters)
     if decode:

@@ -76,10 +76,11 @@ def profile(args: argparse.Namespace, isolated: bool) -> dict:
     for _ in range(5):
         engine.step()
     totals: dict[str, float] = defaultdict(float)
-    timed(engine.scheduler, "schedule", "schedule", totals, isolated)
+    timed(engine.scheduler, "plan", "schedule", totals, isolated)
     timed(engine.decode_graphs, "run", "lay out + H2D + graph launch", totals, isolated)
     timed(engine.decode_graphs, "run_prepared", "token ids + H2D + graph launch (laid out ahead)", totals, isolated)
-    timed(engine, "_prepack_next", "lay out the next step", totals, isolated)
+    timed(engine.scheduler, "plan_ahead", "plan the next step", totals, isolated)
+    timed(engine.decode_graphs, "prepare", "lay out the next step", totals, isolated)
     timed(engine.sampler, "launch", "sampling kernel + D2H", totals, isolated)
     timed(engine.sampler, "collect", "wait for the token ids", totals, isolated)
     timed(engine.scheduler, "postprocess", "postprocess", totals, isolated)

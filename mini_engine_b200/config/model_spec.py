@@ -30,16 +30,31 @@ class LayerSpec:
     """One set of layer weights.
 
     ``prefix`` is the checkpoint name prefix of the layer's tensors (for example
-    ``model.layers.3.``).  ``block`` names the arrangement of the four parts (for example
-    pre-norm residual).  Different layers may name different mixers and feed-forwards.
+    ``model.layers.3.``).  ``block`` names the arrangement of the parts (for example pre-norm
+    residual).  Different layers may name different mixers and feed-forwards.  ``norms`` maps the
+    names that the block's class asks for to norm parts: a pre-norm block asks for ``"mixer"``
+    and ``"feed_forward"`` (the norm in front of each); another arrangement may ask for more
+    (norms behind the mixer and the feed-forward, say).  ``mixer_norm`` and
+    ``feed_forward_norm`` are those two entries under their old names.
     """
 
     prefix: str
     block: str
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer_norm: PartSpec | None = None
+    feed_forward_norm: PartSpec | None = None
+    norms: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def named_norms(self) -> dict[str, PartSpec]:
+        """Every norm of the layer by the name its block knows it under."""
+        named = dict(self.norms)
+        for name, spec in (("mixer", self.mixer_norm), ("feed_forward", self.feed_forward_norm)):
+            if spec is not None:
+                if name in named:
+                    raise ValueError(f"layer {self.prefix!r} names its {name!r} norm twice")
+                named[name] = spec
+        return named
 
 
 @dataclass(frozen=True)

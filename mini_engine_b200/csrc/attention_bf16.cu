@@ -314,6 +314,23 @@ constexpr int MAX_DECODE_TILES = 8;
 template <int D>
 __device__ __forceinline__ void merge_head(const AttnParams& p, int entry, int head, int first, int last, int lane);
 
+// First failure that a decode kernel recorded: 1 = a bounded wait ran out, 2 = a context needed
+// more partial-result slots than the launch was given (its last keys were left out).
+__device__ int g_decode_error = 0;
+
+// The range of partial-result slots of one (entry, head) in the kernel below: one per span of
+// keys that the query can see, clamped to the slots that exist.  A context that needs more was
+// given too few splits by the caller: its keys beyond are not read, which is recorded.
+__device__ __forceinline__ void decode_slot_range(const AttnParams& p, int position, int lowest, int span, int& first,
+                                                  int& last) {
+    last = position / span;
+    if (last >= p.max_splits) {
+        atomicCAS(&g_decode_error, 0, 2);
+        last = p.max_splits - 1;
+    }
+    first = min(lowest / span, last);
+}
+
 template <int D>
 __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -464,8 +481,10 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
     __shared__ int is_last;
     __threadfence();
     __syncthreads();
+    int first_slot, last_slot;
+    decode_slot_range(p, position, lowest, span, first_slot, last_slot);
     if (threadIdx.x == 0) {
-        const int active = position / span - lowest / span + 1;
+        const int active = last_slot - first_slot + 1;  // the CTAs of this (request, KV head) that got here
         int* counter = p.counters + entry * p.kv_heads + kv_head;
         const int ticket = atomicAdd(counter, 1);
         is_last = ticket == active - 1;
@@ -474,8 +493,7 @@ __global__ void __launch_bounds__(ATTN_THREADS, 3) attention_decode_kernel(AttnP
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int row = warp; row < group; row += 4)
-        merge_head<D>(p, entry, kv_head * group + row, lowest / span, position / span, lane);
+    for (int row = warp; row < group; row += 4) merge_head<D>(p, entry, kv_head * group + row, first_slot, last_slot, lane);
 }
 
 // One warp merges the partials of one (entry, head) in ascending order of their keys and writes
@@ -544,7 +562,9 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
     const int position = p.context_lens[entry] - 1;
     const int lowest = p.window > 0 ? max(position - p.window + 1, 0) : 0;
     const int span = p.tiles_per_cta * DECODE_CHUNK;
-    merge_head<D>(p, entry, head, lowest / span, position / span, lane);
+    int first_slot, last_slot;
+    decode_slot_range(p, position, lowest, span, first_slot, last_slot);
+    merge_head<D>(p, entry, head, first_slot, last_slot, lane);
 }
 
 // ------------------------------------------------- decode kernel with TMA page loads
@@ -565,8 +585,6 @@ __global__ void __launch_bounds__(128) attention_decode_merge_kernel(AttnParams 
 // With one split the CTA writes the output itself; else partials as in the kernel above.
 constexpr int TMA_WARP_KEYS = 16;
 constexpr int TMA_MIN_TILES = 2;  // a CTA takes at least this many tiles: a partial more costs more than a tile
-
-__device__ int g_decode_error = 0;
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
     uint32_t d;
@@ -882,12 +900,8 @@ template <int D>
 static int launch_portions(const AttnParams& p, int entries, int max_new_tokens, cudaStream_t stream) {
     constexpr int SMEM = (BLOCK_M * D + 4 * BLOCK_KEYS * D) * 2;
     auto kernel = attention_portions_kernel<D>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, SMEM)) return e;
     dim3 grid((max_new_tokens + BLOCK_M - 1) / BLOCK_M, p.heads, entries);
     return launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
 }
@@ -896,12 +910,8 @@ template <int D>
 static int launch_decode(const AttnParams& p, int entries, cudaStream_t stream) {
     constexpr int SMEM = (16 * D + 8 * DECODE_WARP_KEYS * D) * 2;
     auto kernel = attention_decode_kernel<D>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, SMEM)) return e;
     dim3 grid(p.max_splits, p.kv_heads, entries);
     const int status = launch_kernel(kernel, grid, ATTN_THREADS, SMEM, stream, p);
     if (status != 0 || p.counters != nullptr) return status;
@@ -914,12 +924,8 @@ static int launch_decode_tma(const CUtensorMap& k_map, const CUtensorMap& v_map,
                              cudaStream_t stream) {
     constexpr int SMEM = tma_decode_smem_bytes<D, WARPS>();
     auto kernel = attention_decode_tma_kernel<D, WARPS>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, SMEM)) return e;
     dim3 grid(p.max_splits, p.kv_heads, entries);
     const int status = launch_kernel(kernel, grid, WARPS * 32, SMEM, stream, k_map, v_map, p);
     if (status != 0 || p.counters != nullptr || p.max_splits == 1) return status;
@@ -1006,7 +1012,8 @@ ME_EXPORT int me_attention_decode_bf16_tma(const void* k_map, const void* v_map,
                            : launch_decode_tma<64, 6>(maps[0], maps[1], p, entries, stream);
 }
 
-// First failure that a decode kernel recorded since the last call (a wait that ran out), or 0.
+// First failure that a decode kernel recorded since the last call, or 0: 1 = a wait that ran out,
+// 2 = `max_splits` did not cover a context (its output lacks the keys beyond).
 ME_EXPORT int me_attention_bf16_take_error(int* code) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(code, g_decode_error, sizeof(int));

@@ -140,8 +140,6 @@ def decode_tiles_per_cta(entries: int, kv_heads: int, max_context_len: int) -> i
     return max(1, min(8, -(-tiles // RESIDENT_DECODE_CTAS)))
 
 
-FORCED_TMA_SPLITS = 0  # > 0: what kernel_bench's --splits asks for
-FORCED_TMA_WARPS = 0  # 6 or 8: what kernel_bench's --warps asks for
 RESIDENT_DECODE_CTAS_OF_SIX_WARPS = 4 * 148  # four CTAs of six warps fit an SM
 
 
@@ -152,8 +150,6 @@ def tma_decode_warps(entries: int, kv_heads: int) -> int:
     of six-warp CTAs but a full and a nearly empty one of eight-warp CTAs (2,048 keys: 88.7 us
     against 93.2 us with three CTAs per pair; 320 keys: 17.9 us against 22.0 us).  With as many
     waves either way, eight warps are faster (batch 96: 122 us against 137 us)."""
-    if FORCED_TMA_WARPS:
-        return FORCED_TMA_WARPS
     pairs = max(1, entries * kv_heads)
     waves_of_eight = -(-pairs // RESIDENT_DECODE_CTAS)
     waves_of_six = -(-pairs // RESIDENT_DECODE_CTAS_OF_SIX_WARPS)
@@ -173,8 +169,6 @@ def tma_decode_splits(entries: int, kv_heads: int, max_context_len: int, warps: 
     empty and as long as the first (batch 64 at 2,048 keys: 103 -> 93 us; at 4,096: 194 -> 168 us),
     while with a last wave that is a third full and more, one CTA per pair is faster (batch 80 at
     4,096 keys: 202 us against 208 us)."""
-    if FORCED_TMA_SPLITS > 0:
-        return FORCED_TMA_SPLITS
     tiles = max(1, -(-max_context_len // (warps * TMA_DECODE_KEYS)))
     pairs = max(1, entries * kv_heads)
     slots = RESIDENT_DECODE_CTAS if warps == 8 else RESIDENT_DECODE_CTAS_OF_SIX_WARPS
@@ -191,10 +185,13 @@ def decode_splits(max_context_len: int, tiles_per_cta: int = 1) -> int:
     return max(1, -(-max_context_len // (DECODE_CHUNK * tiles_per_cta)))
 
 
-def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window) -> None:
+def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads, head_dim, scale, window,
+                    decode_warps: int | None = None, decode_splits_per_pair: int | None = None) -> None:
     """Attention of the batch's new tokens.  Entries that bring one token take the split decode
     kernel, the others a portions kernel; a step that holds both kinds is two launches, each over
-    its own list of entries."""
+    its own list of entries.  ``decode_warps`` (6 or 8) and ``decode_splits_per_pair`` pin the form
+    of the TMA decode kernel that the rules above would otherwise choose from the batch: the kernel
+    tests run every case in both forms, and the kernel bench times one form against the other."""
     for name, t in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
         if t.dtype != torch.bfloat16 or not t.is_contiguous():
             raise ops.KernelError(f"{name} must be contiguous bfloat16")
@@ -219,8 +216,8 @@ def paged_attention(q, k_pages, v_pages, block_table, ctx, out, heads, kv_heads,
     for kind, entries, ids, longest in launches:
         ids_ptr = None if ids is None else ids.data_ptr()
         if kind == "decode" and tma_decode_kernel_takes(heads, kv_heads, page_size):
-            warps = tma_decode_warps(entries, kv_heads)
-            splits = tma_decode_splits(entries, kv_heads, ctx.max_context_len, warps)
+            warps = decode_warps or tma_decode_warps(entries, kv_heads)
+            splits = decode_splits_per_pair or tma_decode_splits(entries, kv_heads, ctx.max_context_len, warps)
             partials = counters = None
             if splits > 1:
                 partials = ctx.workspace.growing("attn.partials", (ctx.num_entries, heads, splits, head_dim + 2), torch.float32).data_ptr()

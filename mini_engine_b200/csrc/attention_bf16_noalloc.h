@@ -20,7 +20,10 @@
  *  - entries * heads * max_splits * (head_dim + 2) must not exceed
  *    ME_NOALLOC_MAX_PARTIAL_FLOATS (2,097,152 floats = 8 MiB); otherwise the call returns
  *    ME_ERR_NOALLOC_TOO_LARGE and launches nothing.  max_splits must cover the longest
- *    context of the call: ceil(context / 128).  Example: 16 requests x 32 heads x 30 splits
+ *    context of the call: ceil(context / 128).  The host cannot check that (the context
+ *    lengths are on the device); a context that needs more is computed without its keys
+ *    beyond 128 * max_splits, never reads or writes outside its own slots, and makes
+ *    me_attention_bf16_take_error report 2.  Example: 16 requests x 32 heads x 30 splits
  *    (3,840 tokens of context) x head_dim 128 = 1,996,800 floats.
  *  - Every GPU on which the library is loaded holds the 8 MiB until the process exits.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress,

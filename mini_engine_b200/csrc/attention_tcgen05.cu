@@ -373,12 +373,8 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
                    heads, kv_heads, page_size, table_width};
     constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(attention_tcgen05_kernel, SMEM)) return e;
     dim3 grid(heads, (max_new_tokens + TC_ROWS - 1) / TC_ROWS, entries);
     return launch_kernel(attention_tcgen05_kernel, grid, TC_THREADS, SMEM, stream, q, k, v, p);
 }

@@ -127,6 +127,9 @@ def compile_library(name: str, verbose: bool = True) -> Path:
         scratch.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed for {source.name}:\n{output}")
     os.replace(scratch, target)  # atomic: a concurrent builder never sees half a file
+    for stale in target.parent.glob(f"{name}-*.so"):  # builds of older sources: never loaded again
+        if stale != target and ".tmp" not in stale.name:
+            stale.unlink(missing_ok=True)
     if verbose:
         print(f"[mini_engine_b200] built {target.name} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
     return target

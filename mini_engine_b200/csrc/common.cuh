@@ -4,7 +4,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
 #define ME_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -45,18 +44,26 @@ static inline int launch_status() { return static_cast<int>(cudaGetLastError());
 // or writes anything that another kernel writes or reads it calls pdl_wait(), which returns once
 // the preceding kernel has completed and its memory is visible.  pdl_trigger() tells the
 // scheduler that the next kernel's CTAs may be made resident as far as this CTA is concerned.
-// Without the attribute (MINI_ENGINE_B200_PDL=0) both are no-ops and kernels run back to back.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-static inline bool pdl_enabled() {
-    static int enabled = -1;
-    if (enabled < 0) {
-        const char* value = getenv("MINI_ENGINE_B200_PDL");
-        enabled = (value && value[0] == '0') ? 0 : 1;
+// A kernel's opt-in to more than 48 KB of dynamic shared memory holds for one device only, so it
+// is remembered per device ordinal (the device that is current when the kernel is launched).
+struct SharedMemoryOptIn {
+    bool done[64] = {};
+    template <typename Kernel>
+    int operator()(Kernel kernel, int bytes) {
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        const bool remembered = device >= 0 && device < 64;
+        if (remembered && done[device]) return 0;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        if (remembered) done[device] = true;
+        return 0;
     }
-    return enabled == 1;
-}
+};
 
 template <typename... KernelArgs, typename... Args>
 static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -70,6 +77,6 @@ static inline int launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 b
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
-    config.numAttrs = pdl_enabled() ? 1 : 0;
+    config.numAttrs = 1;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...));
 }

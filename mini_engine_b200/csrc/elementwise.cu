@@ -15,7 +15,7 @@
 // a thread then moves eight elements per step.
 template <typename T, bool VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, float multiplier) {
     const int token = blockIdx.x;
     pdl_trigger();
     pdl_wait();
@@ -41,27 +41,56 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[j] = to_float(row[i + j]);
             }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] *= multiplier;  // 1 for a model without embedding scaling: exact
             *reinterpret_cast<float4*>(row_out + i) = make_float4(v[0], v[1], v[2], v[3]);
             *reinterpret_cast<float4*>(row_out + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
         }
     } else {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = to_float(row[i]);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) row_out[i] = to_float(row[i]) * multiplier;
     }
 }
 
+// out[t][:] = table[ids[t]][:] * multiplier, widened to float32.
 ME_EXPORT int me_embedding(const void* table, int table_type, const int* ids, float* out, int tokens,
-                           int hidden, int vocab, cudaStream_t stream) {
+                           int hidden, int vocab, float multiplier, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const bool vec = hidden % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
     const int threads = vec ? std::min(512, std::max(32, (hidden / 8 + 31) / 32 * 32)) : (hidden >= 1024 ? 256 : 128);
     if (table_type == ME_BF16) {
         const auto* t = static_cast<const __nv_bfloat16*>(table);
-        return vec ? launch_kernel(embedding_kernel<__nv_bfloat16, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab)
-                   : launch_kernel(embedding_kernel<__nv_bfloat16, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab);
+        return vec ? launch_kernel(embedding_kernel<__nv_bfloat16, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab, multiplier)
+                   : launch_kernel(embedding_kernel<__nv_bfloat16, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab, multiplier);
     }
     const auto* t = static_cast<const float*>(table);
-    return vec ? launch_kernel(embedding_kernel<float, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab)
-               : launch_kernel(embedding_kernel<float, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab);
+    return vec ? launch_kernel(embedding_kernel<float, true>, tokens, threads, 0, stream, t, ids, out, hidden, vocab, multiplier)
+               : launch_kernel(embedding_kernel<float, false>, tokens, threads, 0, stream, t, ids, out, hidden, vocab, multiplier);
+}
+
+// ------------------------------------------------------------- what a head may do to logits
+
+// logits[r][v] = cap(logits[r][v] * scale + bias[v]) with cap(y) = soft_cap * tanh(y / soft_cap) when
+// soft_cap > 0, in place; `bias` may be null.  For heads that have a bias, a logit scale or a
+// soft cap; a plain head never launches this.
+__global__ void logits_finish_kernel(float* __restrict__ logits, const float* __restrict__ bias, float scale,
+                                     float soft_cap, int vocab) {
+    pdl_trigger();
+    pdl_wait();
+    float* row = logits + static_cast<size_t>(blockIdx.y) * vocab;
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < vocab; v += gridDim.x * blockDim.x) {
+        float y = row[v] * scale;
+        if (bias != nullptr) y += bias[v];
+        if (soft_cap > 0.0f) y = soft_cap * tanhf(y / soft_cap);
+        row[v] = y;
+    }
+}
+
+ME_EXPORT int me_logits_finish(float* logits, const float* bias, float scale, float soft_cap, int rows, int vocab,
+                               cudaStream_t stream) {
+    if (rows <= 0 || vocab <= 0) return 0;
+    if (rows > 65535) return ME_ERR_ARGUMENT;
+    const int blocks = std::min((vocab + 255) / 256, 1024);
+    return launch_kernel(logits_finish_kernel, dim3(blocks, rows), 256, 0, stream, logits, bias, scale, soft_cap, vocab);
 }
 
 // --------------------------------------------------------------- residual sum + RMSNorm

@@ -777,12 +777,8 @@ template <int BLOCK_T, bool DUAL>
 static int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, int splits, cudaStream_t stream) {
     using C = Config<BLOCK_T, DUAL>;
     auto kernel = gemm_tcgen05_kernel<BLOCK_T, DUAL>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
     dim3 grid((p.tokens + BLOCK_T - 1) / BLOCK_T, (p.outs + BLOCK_N - 1) / BLOCK_N, splits);
     return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
 }
@@ -813,12 +809,8 @@ template <bool DUAL>
 static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream, int splits = 1) {
     using C = PairConfig<DUAL>;
     auto kernel = gemm_tcgen05_pair_kernel<DUAL>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -849,20 +841,8 @@ static int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, const
     attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
-    config.numAttrs = pdl_enabled() ? 2 : 1;
+    config.numAttrs = 2;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, q));
-}
-
-// out[t][n] (float32) = x[t] . w[n] by CTA pairs.  The weight map has boxes of 128 rows, the
-// activation map boxes of 128 rows too (each CTA of a pair loads half of the 256 tokens).
-ME_EXPORT int me_gemm_tcgen05_pair(const void* map_w, const void* map_x, float* out, int tokens, int outs, int inner,
-                                   cudaStream_t stream) {
-    if (tokens <= 0 || outs <= 0) return 0;
-    alignas(64) CUtensorMap w, x;
-    memcpy(&w, map_w, sizeof(w));
-    memcpy(&x, map_x, sizeof(x));
-    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1};
-    return launch_pair<false>(w, x, p, stream);
 }
 
 // out[s][t][n] (float32) = the part of x[t] . w[n] over the k blocks of split s, by CTA pairs: for
@@ -880,26 +860,12 @@ ME_EXPORT int me_gemm_tcgen05_pair_split(const void* map_w, const void* map_x, f
     return launch_pair<false>(w, x, p, stream, splits);
 }
 
-ME_EXPORT int me_gemm_tcgen05_pair_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs, int inner,
-                                          int dual_row_offset, cudaStream_t stream) {
-    if (tokens <= 0 || outs <= 0) return 0;
-    alignas(64) CUtensorMap w, x;
-    memcpy(&w, map_w, sizeof(w));
-    memcpy(&x, map_x, sizeof(x));
-    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1};
-    return launch_pair<true>(w, x, p, stream);
-}
-
 template <bool DUAL>
 static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
     using C = PersistentConfig<DUAL>;
     auto kernel = gemm_tcgen05_persistent_kernel<DUAL>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
     int device = 0, sms = 0;
     cudaGetDevice(&device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
@@ -928,7 +894,7 @@ static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x,
     attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
-    config.numAttrs = pdl_enabled() ? 2 : 1;
+    config.numAttrs = 2;
     return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, q));
 }
 
@@ -974,12 +940,8 @@ template <int BLOCK_T>
 static int launch_stacked(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
     using C = StackedConfig<BLOCK_T>;
     auto kernel = gemm_tcgen05_stacked_swiglu_kernel<BLOCK_T>;
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return static_cast<int>(e);
-        configured = true;
-    }
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
     dim3 grid((p.tokens + BLOCK_T - 1) / BLOCK_T, (p.outs + STACK_ROWS - 1) / STACK_ROWS, 1);
     return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
 }
@@ -999,6 +961,48 @@ ME_EXPORT int me_gemm_tcgen05_stacked_swiglu(const void* map_w, const void* map_
         case 64: return launch_stacked<64>(w, x, p, stream);
         default: return ME_ERR_ARGUMENT;
     }
+}
+
+// ------------------------------------------------------------- the give-up path, exercised
+//
+// A CTA with the warp roles of the product kernels whose copies never arrive: no TMA is issued, so
+// the MMA warp's wait for its first stage runs out after `polls` polls, it records the failure and
+// commits nothing; the epilogue warps' wait for the accumulator runs out in turn; all warps meet,
+// the tensor memory is given back, and the CTA returns normally.  Nothing faults, traps or hangs:
+// a test calls this to see that a wait that runs out leaves the error word set, the context usable
+// and tensor memory free for the next product.  `returned` (one int) is set to 1 at the very end.
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_wait_probe_kernel(uint32_t polls, int* returned) {
+    __shared__ uint64_t full, accum;
+    __shared__ uint32_t tmem_holder;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(&full, 1);
+        mbar_init(&accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(&tmem_holder, 32);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_holder;
+    if (warp == 0) {
+        // the producer: its copy is never issued
+    } else if (warp == 1) {
+        if (lane == 0 && !mbar_wait(&full, 0, polls)) atomicCAS(&g_gemm_error, 0, (40 << 8));
+        // no MMA was issued, so nothing is committed to `accum`
+    } else {
+        bool ok = mbar_wait(&accum, 0, polls);
+        if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (41 << 8));
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem_base, 32);
+    if (threadIdx.x == 0) *returned = 1;
+}
+
+ME_EXPORT int me_gemm_wait_probe(int polls, int* returned, cudaStream_t stream) {
+    if (polls < 1 || polls > (1 << 20) || returned == nullptr) return ME_ERR_ARGUMENT;
+    return launch_kernel(gemm_wait_probe_kernel, 1, GEMM_THREADS, 0, stream, static_cast<uint32_t>(polls), returned);
 }
 
 // The first failure a kernel of this library recorded since the last call (0: none); clears it.

@@ -137,13 +137,28 @@ def check_attention_sizes(head_dim: int, heads: int, kv_heads: int) -> None:
 # ------------------------------------------------------------------------------ elementwise
 
 
-def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t] = table[token_ids[t]]`` widened to float32."""
+def embedding(table: torch.Tensor, token_ids: torch.Tensor, out: torch.Tensor, multiplier: float = 1.0) -> None:
+    """``out[t] = table[token_ids[t]] * multiplier`` widened to float32."""
     _need(table, None, "table"), _need(token_ids, torch.int32, "token_ids"), _need(out, torch.float32, "out")
-    fn = _fn("elementwise", "me_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    fn = _fn("elementwise", "me_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     vocab, hidden = table.shape
-    code = fn(_ptr(table), _type_code(table.dtype), _ptr(token_ids), _ptr(out), out.shape[0], hidden, vocab, _stream())
+    code = fn(_ptr(table), _type_code(table.dtype), _ptr(token_ids), _ptr(out), out.shape[0], hidden, vocab,
+              float(multiplier), _stream())  # fmt: skip
     _check(code, "embedding")
+
+
+def logits_finish(logits: torch.Tensor, bias: torch.Tensor | None, scale: float = 1.0, soft_cap: float = 0.0) -> None:
+    """In place on float32 ``logits [N, vocab]``: ``y = x * scale + bias``, then ``soft_cap *
+    tanh(y / soft_cap)`` when ``soft_cap > 0``."""
+    _need(logits, torch.float32, "logits")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.shape != (logits.shape[1],):
+            raise KernelError("the bias must have one value per logit")
+    fn = _fn("elementwise", "me_logits_finish", [c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
+    code = fn(_ptr(logits), _ptr(bias) if bias is not None else None, float(scale), float(soft_cap),
+              logits.shape[0], logits.shape[1], _stream())  # fmt: skip
+    _check(code, "logits_finish")
 
 
 def pick_tokens(tokens: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

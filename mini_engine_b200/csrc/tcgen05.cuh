@@ -29,10 +29,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// Bounded wait; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait; false when the limit ran out (`limit` polls, or the clock bound, whichever first).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = WAIT_LIMIT) {
     const long long started = clock64();
-    for (uint32_t spin = 0; spin < WAIT_LIMIT; ++spin) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 1023u) == 1023u && clock64() - started > WAIT_CYCLES) break;
     }

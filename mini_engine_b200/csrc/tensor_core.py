@@ -8,7 +8,6 @@ live in the engine's persistent workspace.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_int, c_uint, c_ulonglong, c_void_p
 
 import torch
@@ -22,20 +21,13 @@ BLOCK_K = 64
 TOKEN_TILES = (16, 32, 64, 128, 256)
 SPLIT_MAX_TOKENS = 1024  # products of more tokens have enough tiles without splitting
 MIN_K_BLOCKS_PER_SPLIT = 4
-PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles)
-USE_PAIRS = os.environ.get("MINI_ENGINE_B200_PAIRS", "1") != "0"
-# The persistent pair kernel (two accumulator buffers, epilogue under the next tile's MMAs);
-# "0" falls back to one tile per pair of CTAs.
-USE_PERSISTENT = os.environ.get("MINI_ENGINE_B200_PERSISTENT", "1") != "0"
+PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles), unsplit ones in the persistent kernel
 # Products of 129 to 1,024 tokens whose reduction is split run on CTA pairs too (each split its own
 # pairs) when a split is long: 48 k blocks and more (the down projection of Qwen3-8B: 256 tokens
 # 33.1 -> 31.3 us, 512 tokens 48.9 -> 44.2 us); with 16 to 32 k blocks per split the lone CTAs are as
 # fast or 2 % faster.
-USE_PAIR_SPLITS = os.environ.get("MINI_ENGINE_B200_PAIR_SPLITS", "1") != "0"
 PAIR_SPLIT_MIN_K_BLOCKS = 48
-
 STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
-USE_PERSISTENT_GATED = os.environ.get("MINI_ENGINE_B200_PERSISTENT_GATED", "1") != "0"
 
 
 def _ops_stream() -> c_void_p:
@@ -55,18 +47,16 @@ def _library():
         lib.me_gemm_tcgen05.restype = c_int
         lib.me_gemm_tcgen05_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_swiglu.restype = c_int
-        lib.me_gemm_tcgen05_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_split.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_split.restype = c_int
-        lib.me_gemm_tcgen05_pair.restype = c_int
-        lib.me_gemm_tcgen05_pair_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
-        lib.me_gemm_tcgen05_pair_swiglu.restype = c_int
         lib.me_gemm_tcgen05_persistent.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent.restype = c_int
         lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
         lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
+        lib.me_gemm_wait_probe.argtypes = [c_int, c_void_p, c_void_p]
+        lib.me_gemm_wait_probe.restype = c_int
         lib.me_gemm_take_error.argtypes = [ctypes.POINTER(c_int)]
         lib.me_gemm_take_error.restype = c_int
         _lib = lib
@@ -153,10 +143,11 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
         raise RuntimeError(f"output {tuple(out.shape)} does not fit [{splits}, {tokens}, {plan.rows}] float32")
     tile = token_tile(tokens)
     stream = _ops_stream()
-    if tokens > PAIR_MIN_TOKENS and splits == 1 and USE_PAIRS:
-        entry = _library().me_gemm_tcgen05_persistent if USE_PERSISTENT else _library().me_gemm_tcgen05_pair
-        code = entry(plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream)
-    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PAIR_SPLITS and -(-plan.inner // BLOCK_K) >= PAIR_SPLIT_MIN_K_BLOCKS * splits:
+    if tokens > PAIR_MIN_TOKENS and splits == 1:
+        code = _library().me_gemm_tcgen05_persistent(
+            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream
+        )
+    elif tokens > PAIR_MIN_TOKENS and -(-plan.inner // BLOCK_K) >= PAIR_SPLIT_MIN_K_BLOCKS * splits:
         code = _library().me_gemm_tcgen05_pair_split(
             plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, splits, stream
         )
@@ -185,16 +176,12 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
             plan.map_half, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
             tile, stream,
         )  # fmt: skip
-    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS and USE_PERSISTENT_GATED:
+    elif tokens > PAIR_MIN_TOKENS:
         code = _library().me_gemm_tcgen05_persistent_swiglu(
             plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
         )
-    elif tokens > PAIR_MIN_TOKENS and USE_PAIRS:
-        code = _library().me_gemm_tcgen05_pair_swiglu(
-            plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
-        )
     else:
-        tile = 256 if tokens > 128 else 128
+        tile = 128  # 65 to 128 tokens: lone CTAs with gate and up sums side by side in tensor memory
         code = _library().me_gemm_tcgen05_swiglu(
             plan.map, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
             tile, stream,
@@ -206,6 +193,20 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
 
 def _count_launch() -> None:
     ops._Counter.launches += 1
+
+
+def wait_probe(polls: int = 4096) -> bool:
+    """Launch a CTA whose barrier waits run out after ``polls`` polls because nothing ever arrives
+    at them (no fault, trap or endless loop): it records the failure as the product kernels do,
+    gives its tensor memory back and returns.  True when it returned; :func:`take_error` then
+    reports the recorded code.  Exists so that the give-up path can be tested."""
+    lib = _library()
+    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    code = lib.me_gemm_wait_probe(polls, returned.data_ptr(), _ops_stream())
+    _count_launch()
+    if code != 0:
+        raise RuntimeError(f"the wait probe failed to launch (code {code})")
+    return bool(returned.item())
 
 
 def take_error() -> int:

@@ -39,7 +39,7 @@ class DecodeGraphs:
 
     def _dummy_entries(self, count: int) -> list[StepEntry]:
         caches = [
-            RequestCache(block_tables=[[self.runner.spare_page] for _ in range(self.runner.num_groups)])
+            RequestCache(block_tables=[[page] for page in self.runner.spare_pages])
             for _ in range(count)
         ]
         return [StepEntry(c, 0, [0], (0,)) for c in caches]

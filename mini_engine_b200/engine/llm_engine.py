@@ -21,7 +21,7 @@ from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.csrc import ops
 from mini_engine_b200.engine.graphs import DecodeGraphs
 from mini_engine_b200.engine.loading import load_model, random_model
-from mini_engine_b200.engine.runner import ModelRunner, Prepacked, StepEntry
+from mini_engine_b200.engine.runner import ModelRunner, Prepacked
 from mini_engine_b200.engine.scheduler import ScheduledSeq, Scheduler, SchedulerConfig
 from mini_engine_b200.engine.sequence import Sequence
 from mini_engine_b200.parts.model import DecoderModel
@@ -83,12 +83,15 @@ class LLMEngine:
             config.block_size,
             config.max_num_seqs,
             config.enable_prefix_caching,
-            has_state=self.runner.layout.has_state,
+            slot_groups=self.runner.layout.slot_groups,
         )
         self.scheduler = Scheduler(
             SchedulerConfig(config.max_num_seqs, config.max_num_batched_tokens, config.max_model_len),
             self.block_manager,
             set(eos_token_ids),
+            # A step launched ahead may have to be dropped and run again; that is only harmless when
+            # a step leaves nothing behind but keys and values (a mixer's own state would advance twice).
+            rerun_safe=not self.runner.layout.has_state,
         )
         self.sampler = Sampler(config.seed, max(config.max_num_seqs, 1))
         self.stats = EngineStats()
@@ -147,10 +150,10 @@ class LLMEngine:
         finds that the step in flight is not the one the scheduler wants and drops it: it wrote
         keys and values only to places that the rerun writes again with the same values, or that
         belonged to the ended request."""
-        batch = self.scheduler.schedule()
+        plan = self.scheduler.plan()
+        batch, entries = plan.items, plan.entries
         if not batch:
             raise RuntimeError("scheduler produced an empty batch with work pending")
-        entries = [self._entry(item) for item in batch]
         flight, self._in_flight = self._in_flight, None
         if flight is not None and not flight.prepacked.matches(entries):
             self.stats.dropped_steps += 1
@@ -164,18 +167,19 @@ class LLMEngine:
             draw = self._draw(batch, logits, 0)
         if graph_step:
             self.stats.graph_steps += 1
-            ahead = self._prepack_next(batch) if self.config.overlap_steps else None  # host work while the device runs
+            # host work while the device runs: the scheduler says whether the step after is certain
+            ahead = self.scheduler.plan_ahead(plan) if self.config.overlap_steps else None
             if ahead is not None:
-                prepacked, staying = ahead
+                prepacked = self.decode_graphs.prepare(ahead.entries)
                 rows = None
-                if len(staying) < len(batch):  # the tokens of the requests that go on are picked on the device
-                    count = len(staying)
+                if len(ahead.staying) < len(batch):  # the tokens of the requests that go on are picked on the device
+                    count = len(ahead.staying)
                     host = self._rows_host[self.stats.steps & 1]  # its copy of two steps ago has run by now
-                    host[:count] = torch.tensor([row for row, _ in staying], dtype=torch.int32)
+                    host[:count] = torch.tensor([row for row, _ in ahead.staying], dtype=torch.int32)
                     rows = self._rows[:count]
                     rows.copy_(host[:count], non_blocking=True)
                 logits = self.decode_graphs.run_prepared(prepacked, draw.tokens, rows)
-                self._in_flight = StepInFlight(prepacked, self._draw([item for _, item in staying], logits, 1))
+                self._in_flight = StepInFlight(prepacked, self._draw([item for _, item in ahead.staying], logits, 1))
         sampled = self.sampler.collect(draw)
         tokens = iter(sampled)
         next_tokens = [next(tokens) if item.samples else None for item in batch]
@@ -185,12 +189,6 @@ class LLMEngine:
         return self.scheduler.postprocess(batch, next_tokens)
 
     # ---------------------------------------------------------------- private
-
-    @staticmethod
-    def _entry(item: ScheduledSeq) -> StepEntry:
-        seq, start = item.seq, item.seq.num_computed_tokens
-        want = (item.num_tokens - 1,) if item.samples else ()
-        return StepEntry(seq.cache, start, seq.token_ids[start : start + item.num_tokens], want)
 
     def _draw(self, batch: list[ScheduledSeq], logits: torch.Tensor, ahead: int):
         """Launch the draw of one token for every request of `batch` that samples; `ahead` = 1 for
@@ -202,34 +200,6 @@ class LLMEngine:
             [seq.seq_id for seq in sampling],
             [seq.num_output_tokens + ahead for seq in sampling],
         )
-
-    def _prepack_next(self, batch: list[ScheduledSeq]):
-        """Lay out the decode step that follows `batch` if it is certain what it will hold unless
-        a request ends on an end-of-sequence token: nobody can be admitted (no request waits, or every
-        place stays taken), and every request that does not reach its `max_tokens` with the token
-        drawn now can have the pages of one more token without preempting anyone.  Returns the layout and the (row, item) pairs of
-        `batch` that go on, or None.  The pages that this takes are the ones the scheduler would
-        take a step later; a request that ends instead gives all its pages back anyway."""
-        ends = [item.seq.num_output_tokens + 1 >= item.seq.params.max_tokens for item in batch]  # on the token being drawn
-        if len(batch) != len(self.scheduler.running):
-            return None  # the token budget left someone out: the next batch is another
-        if self.scheduler.waiting and len(batch) - sum(ends) < self.config.max_num_seqs:
-            return None  # a place is free: the next step admits a request
-        entries, staying = [], []
-        for row, item in enumerate(batch):
-            seq = item.seq
-            if ends[row]:
-                continue
-            start = seq.num_computed_tokens + 1  # the step in flight computes one token
-            if start + 1 > self.config.max_model_len:
-                return None
-            if not self.block_manager.try_allocate(seq.cache, start + 1):
-                return None
-            entries.append(StepEntry(seq.cache, start, [0], (0,)))
-            staying.append((row, item))
-        if not entries:
-            return None
-        return self.decode_graphs.prepare(entries), staying
 
     def _graph_fits(self, batch: list[ScheduledSeq]) -> bool:
         graphs = self.decode_graphs

@@ -58,7 +58,7 @@ class Replayer:
             block_size,
             max_num_seqs=MAX_LIVE * 2,
             enable_prefix_caching=False,
-            has_state=self.runner.layout.has_state,
+            slot_groups=self.runner.layout.slot_groups,
         )
         self.live: dict[str, list] = {}  # id -> [RequestCache, tokens held]
 

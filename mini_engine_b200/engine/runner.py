@@ -16,7 +16,7 @@ token; here it is one int32 block in pinned memory and one host-to-device copy.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence as Seq
 
 import numpy as np
@@ -25,19 +25,10 @@ import torch
 from mini_engine_b200.cache.manager import NULL_PAGE, RequestCache
 from mini_engine_b200.cache.storage import CacheLayout, allocate_cache
 from mini_engine_b200.csrc import ops
+from mini_engine_b200.engine.batch import StepEntry  # noqa: F401  (re-exported: the step function's input)
 from mini_engine_b200.engine.workspace import Workspace
 from mini_engine_b200.parts.base import StepContext
 from mini_engine_b200.parts.model import DecoderModel
-
-
-@dataclass
-class StepEntry:
-    """Tokens ``[start, start + len(token_ids))`` of one request."""
-
-    cache: RequestCache
-    start: int
-    token_ids: Seq[int]
-    want: Seq[int] = field(default_factory=tuple)  # places among these tokens whose logits are returned
 
 
 @dataclass
@@ -84,11 +75,12 @@ class ModelRunner:
         self.table_width = -(-max_model_len // block_size)
         self.vocab_size = model.spec.vocab_size
         self.layout: CacheLayout = allocate_cache(
-            model.cache_needs(), num_blocks, block_size, max_num_seqs, dtype, self.device
-        )
+            model.cache_needs(), num_blocks, block_size, max_num_seqs, dtype, self.device,
+            max_step_tokens=max_num_batched_tokens,
+        )  # fmt: skip
         self.num_groups = len(self.layout.groups)
         self.workspace = Workspace(max_num_batched_tokens, self.device)
-        self.spare_page = num_blocks  # owned by no request: padding rows write and read here
+        self.spare_pages = self.layout.spare_pages  # per group, owned by no request: padding rows write and read here
         self.spare_slot = max_num_seqs
         # One int32 block holds every index array of a step; two pinned copies alternate so a
         # step never overwrites what an earlier copy may still be reading.
@@ -188,7 +180,7 @@ class ModelRunner:
             owners[b] = key
             for gi in range(g):
                 if rows is None:
-                    table_rows[gi][b] = self.spare_page
+                    table_rows[gi][b] = self.spare_pages[gi]
                 else:
                     table_rows[gi][b] = rows[gi]
 
@@ -262,7 +254,7 @@ class ModelRunner:
         for b in range(real, total_entries):  # padding: one token at position 0 of the spare page
             ids[cursor], pos[cursor], ent[cursor] = 0, 0, b
             for gi in range(g):
-                slots[gi][0][cursor] = self.spare_page * bs
+                slots[gi][0][cursor] = self.spare_pages[gi] * bs
             put_row(b, None, None)
             cu[b + 1] = cursor + 1
             ctx_len[b], state[b], fresh[b] = 1, self.spare_slot, 1

@@ -1,14 +1,15 @@
 """Interfaces and registries of the parts a layer is made of.
 
-A layer is assembled from four parts and an arrangement:
+A layer is assembled from parts and an arrangement:
 
 * a **mixer** (token mixing: attention here) that may keep per-token pages and/or a
   fixed-size per-request state in the cache manager,
 * a **feed-forward**,
-* two **norms**,
-* a **block** that says how the four are wired (pre-norm residual here),
+* **norms**, by the names that the arrangement asks for (two in a pre-norm layer),
+* a **block** that says how they are wired (pre-norm residual here),
 
-and a mixer may own a **position encoding**.  Each kind has one registry from a name to a
+and a mixer may own a **position encoding**.  The model's two ends are parts as well: an
+**embedding** and a **head**.  Each kind has one registry from a name to a
 class; a :class:`~mini_engine_b200.config.model_spec.PartSpec` names the class and carries
 its constants.  No part reads a model configuration or knows which model it is in.
 
@@ -189,15 +190,48 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block(Part):
-    """Arrangement of mixer, feed-forward and norms around the residual stream."""
+class Embedding(Part):
+    """The model's first part: token ids to rows of the residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    def forward(self, token_ids: torch.Tensor, ctx: StepContext, out: torch.Tensor) -> None:
+        """Fill ``out [T, hidden]`` (float32, the residual stream) for ``token_ids [T]`` (int32)."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The model's last part: normalised rows to logits."""
+
+    def forward(self, rows: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """``rows [N, hidden]`` (compute dtype) -> float32 logits ``[N, vocab]``."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of mixer, feed-forward and norms around the residual stream.
+
+    ``NORMS`` lists the names of the norms that the arrangement uses; the layer's spec must give
+    exactly those (``LayerSpec.named_norms``), and they arrive as ``self.norms[name]``."""
+
+    NORMS: tuple[str, ...] = ("mixer", "feed_forward")
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Mapping[str, Norm]):
+        if set(norms) != set(self.NORMS):
+            raise ValueError(
+                f"{type(self).__name__} wants the norms {sorted(self.NORMS)}, the layer names {sorted(norms)}"
+            )
         self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.norms = dict(norms)
+
+    @property
+    def mixer_norm(self) -> Norm:
+        return self.norms["mixer"]
+
+    @property
+    def feed_forward_norm(self) -> Norm:
+        return self.norms["feed_forward"]
 
     def parts(self) -> list[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [self.mixer, self.feed_forward, *(self.norms[name] for name in self.NORMS)]
 
     def weight_specs(self) -> list[WeightSpec]:
         return [spec for part in self.parts() for spec in part.weight_specs()]
@@ -219,6 +253,8 @@ FEED_FORWARDS: dict[str, Factory] = {}
 NORMS: dict[str, Factory] = {}
 POSITION_ENCODINGS: dict[str, Factory] = {}
 BLOCKS: dict[str, Factory] = {}
+EMBEDDINGS: dict[str, Factory] = {}
+HEADS: dict[str, Factory] = {}
 
 _REGISTRIES = {
     "mixer": MIXERS,
@@ -226,6 +262,8 @@ _REGISTRIES = {
     "norm": NORMS,
     "position_encoding": POSITION_ENCODINGS,
     "block": BLOCKS,
+    "embedding": EMBEDDINGS,
+    "head": HEADS,
 }
 
 
@@ -234,7 +272,8 @@ def register(kind: str, name: str, replace: bool = False) -> Callable[[Factory],
 
     A mixer, feed-forward, norm or position encoding is built as ``cls(prefix, hidden_size,
     **PartSpec.params)`` where ``prefix`` is the checkpoint prefix of the layer; a block as
-    ``cls(mixer, feed_forward, mixer_norm, feed_forward_norm)``.
+    ``cls(mixer, feed_forward, norms)`` with ``norms`` a mapping from the names in its ``NORMS``
+    to norm parts; an embedding or a head as ``cls(vocab_size, hidden_size, **PartSpec.params)``.
     """
     registry = _REGISTRIES[kind]
 
@@ -245,6 +284,14 @@ def register(kind: str, name: str, replace: bool = False) -> Callable[[Factory],
         return cls
 
     return decorate
+
+
+def build_end(kind: str, spec: PartSpec, vocab_size: int, hidden_size: int) -> Any:
+    """An ``"embedding"`` or a ``"head"``: ``cls(vocab_size, hidden_size, **PartSpec.params)``."""
+    registry = _REGISTRIES[kind]
+    if spec.kind not in registry:
+        raise KeyError(f"no {kind} named {spec.kind!r}; registered: {', '.join(sorted(registry))}")
+    return registry[spec.kind](vocab_size, hidden_size, **dict(spec.params))
 
 
 def build_part(kind: str, spec: PartSpec, prefix: str, hidden_size: int) -> Any:

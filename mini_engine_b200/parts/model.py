@@ -1,8 +1,9 @@
 """A decoder assembled from a :class:`~mini_engine_b200.config.model_spec.ModelSpec`.
 
-Embedding lookup without scaling, the layers in the order that the spec lists, the final
-norm on the wanted rows only, then the head without bias; the head may be the embedding
-matrix itself (src/mini_engine/model.py:163-188 of YuvGev00/mini-engine).
+The embedding part, the layers in the order that the spec lists, the final norm on the wanted
+rows only, then the head part (src/mini_engine/model.py:163-188 of YuvGev00/mini-engine: a
+lookup without scaling and a head without bias that may be the embedding matrix itself).
+Every one of them is looked up in a registry by the kind its spec names.
 """
 
 from __future__ import annotations
@@ -21,48 +22,46 @@ from mini_engine_b200.parts.base import (
     Residual,
     StateSpec,
     StepContext,
+    build_end,
     build_part,
 )
-from mini_engine_b200.parts.linear import Linear
 from mini_engine_b200.weights.loader import WeightSpec
 
 # Importing the built-in parts registers them.
-from mini_engine_b200.parts import attention, block, mlp, norms, rotary  # noqa: F401,E402
+from mini_engine_b200.parts import attention, block, ends, mlp, norms, rotary  # noqa: F401,E402
 
 
 def build_block(spec: ModelSpec, index: int) -> Block:
+    """The layer's block with the parts its spec names; the block's class says which norms it
+    wants (``Block.NORMS``) and the spec must name exactly those."""
     layer = spec.layers[index]
     if layer.block not in BLOCKS:
         raise KeyError(f"no block named {layer.block!r}; registered: {', '.join(sorted(BLOCKS))}")
     hidden = spec.hidden_size
+    norms = {name: build_part("norm", part, layer.prefix, hidden) for name, part in layer.named_norms().items()}
     return BLOCKS[layer.block](
         build_part("mixer", layer.mixer, layer.prefix, hidden),
         build_part("feed_forward", layer.feed_forward, layer.prefix, hidden),
-        build_part("norm", layer.mixer_norm, layer.prefix, hidden),
-        build_part("norm", layer.feed_forward_norm, layer.prefix, hidden),
+        norms,
     )
 
 
 class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
+        self.embedding = build_end("embedding", spec.embedding, spec.vocab_size, spec.hidden_size)
         self.blocks = [build_block(spec, i) for i in range(len(spec.layers))]
         self.final_norm = build_part("norm", spec.final_norm, "", spec.hidden_size)
-        self.embedding_name: str = spec.embedding["weight"]
-        self.head_name: str = spec.head["weight"]
-        self.head_tied_to: str | None = spec.head.get("tied_to")
-        self.embedding: torch.Tensor | None = None
-        self.head: Linear | None = None
+        self.head = build_end("head", spec.head, spec.vocab_size, spec.hidden_size)
 
     # ------------------------------------------------------------------ declarations
 
     def weight_specs(self) -> list[WeightSpec]:
-        shape = (self.spec.vocab_size, self.spec.hidden_size)
-        specs = [WeightSpec(self.embedding_name, shape)]
+        specs = list(self.embedding.weight_specs())
         for blk in self.blocks:
             specs += blk.weight_specs()
         specs += self.final_norm.weight_specs()
-        specs.append(WeightSpec(self.head_name, shape, alias_of=self.head_tied_to))
+        specs += self.head.weight_specs()
         return specs
 
     def cache_needs(self) -> list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]]:
@@ -75,11 +74,11 @@ class DecoderModel:
         return needs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.embedding = tensors[self.embedding_name]
+        self.embedding.load(tensors)
         for blk in self.blocks:
             blk.load(tensors)
         self.final_norm.load(tensors)
-        self.head = Linear(tensors[self.head_name])
+        self.head.load(tensors)
 
     # ------------------------------------------------------------------------ step
 
@@ -91,7 +90,7 @@ class DecoderModel:
 
     def _forward(self, ctx: StepContext, caches: list[LayerCache], logits_rows: torch.Tensor) -> torch.Tensor:
         x = ctx.buffer("residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
-        ops.embedding(self.embedding, ctx.token_ids, x)
+        self.embedding.forward(ctx.token_ids, ctx, x)
         state = Residual(x)
         for entry, cache in zip(self.spec.order, caches, strict=True):
             self.blocks[entry.layer].forward(state, ctx, cache)
@@ -102,7 +101,7 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         rows = self.final_norm.forward(state, ctx, ctx.dtype, rows=logits_rows)
         state.pending = None
-        return self.head.forward(rows, ctx, "logits", whole=True)[0]
+        return self.head.forward(rows, ctx)
 
 
 def declared_weights(spec: ModelSpec) -> list[WeightSpec]:

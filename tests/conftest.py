@@ -17,6 +17,22 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 
 
+# Largest relative error that the replay comparisons of a run reached, by dtype; printed at the
+# end of the run so that the tolerances can be kept close to what the kernels really do.
+WORST_ERRORS: dict[str, float] = {}
+
+
+def note_error(kind: str, value: float) -> None:
+    WORST_ERRORS[kind] = max(WORST_ERRORS.get(kind, 0.0), value)
+
+
+def pytest_terminal_summary(terminalreporter):
+    if WORST_ERRORS:
+        terminalreporter.write_line(
+            "worst relative logit errors: " + ", ".join(f"{k}={v:.3g}" for k, v in sorted(WORST_ERRORS.items()))
+        )
+
+
 def pytest_collection_modifyitems(config, items):
     if torch.cuda.is_available():
         return
@@ -49,7 +65,7 @@ def peaked_model_folders(tmp_path_factory):
     """The same sizes with ten times wider matrices: logits are peaked, so an argmax cannot
     flip on rounding alone (the reference widens its test model's init for the same reason,
     tests/conftest.py:25-27 of YuvGev00/mini-engine)."""
-    return {name: make_model_folder(tmp_path_factory, name, seed=12, scale=10.0) for name in ("A", "B")}
+    return {name: make_model_folder(tmp_path_factory, name, seed=12, scale=10.0) for name in ("A", "B", "C", "D")}
 
 
 def load_plain(folder):

@@ -6,7 +6,7 @@ import random
 
 import pytest
 
-from mini_engine_b200.cache import NULL_PAGE, CacheManager, GroupSpec, hash_page
+from mini_engine_b200.cache import NULL_PAGE, CacheManager, GroupSpec, SlotGroupSpec, hash_page
 
 FULL = [GroupSpec("full")]
 
@@ -107,8 +107,61 @@ def test_prefix_caching_disabled_or_unsound():
     assert off.try_allocate(a, 4)
     computed(off, a, [1, 2, 3, 4], 4)
     assert off.match_prefix([1, 2, 3, 4, 5]) == [[]] and a.page_hashes == []
-    assert not CacheManager([GroupSpec("w", window=8)], 4, 2, 2).enable_prefix_caching
-    assert not CacheManager(FULL, 4, 2, 2, has_state=True).enable_prefix_caching
+    # a group says by itself that what it holds cannot be found again by content: a slot of state
+    # (no snapshots), or a page group that declares it; one such group and every request starts at 0
+    assert not CacheManager(FULL, 4, 2, 2, slot_groups=[SlotGroupSpec("state")]).enable_prefix_caching
+    assert not CacheManager([GroupSpec("full"), GroupSpec("odd", shareable=False)], 4, 2, 2).enable_prefix_caching
+    assert CacheManager(FULL, 4, 2, 2, slot_groups=[SlotGroupSpec("snapshotted", shareable=True)]).enable_prefix_caching
+    assert CacheManager([GroupSpec("w", window=8)], 4, 2, 2).enable_prefix_caching
+
+
+def test_prefix_hits_with_a_window_need_only_the_pages_the_window_reaches():
+    """A group with a window shares the pages that its window still reaches from the end of the
+    shared prefix; earlier ones may be long gone and stand as NULL_PAGE in the new table."""
+    groups = [GroupSpec("full"), GroupSpec("win", window=6)]
+    mgr = CacheManager(groups, num_blocks=12, block_size=4, max_num_seqs=3)
+    tokens = list(range(100, 120))
+    first = mgr.new_request()
+    assert mgr.try_allocate(first, 20)
+    computed(mgr, first, tokens, 20)
+    assert mgr.release_behind_window(first, 20) == 3  # next query at 20 reads keys > 14: pages 0..2 are passed
+    # a second request with the same 20 tokens and 5 more: 5 whole pages could be shared; the window at
+    # position 20 needs page 3 on (keys 15..19 lie in pages 3 and 4), which `first` still holds
+    hits = mgr.match_prefix(tokens + [1, 2, 3, 4, 5])
+    assert hits[0] == first.block_tables[0][:5]
+    assert hits[1][:3] == [NULL_PAGE] * 3 and hits[1][3:] == first.block_tables[1][3:5]
+    second = mgr.new_request()
+    assert mgr.try_allocate(second, 25, hits)
+    assert second.block_tables[1][:3] == [NULL_PAGE] * 3 and len(second.block_tables[1]) == 7
+    mgr.check_invariants([first, second])
+    # the passed pages of the window group went back hashed; once they are evicted nothing changes for a
+    # hit at this length, but a shorter prefix (12 tokens: window needs pages 1..2) cannot be served
+    # by the window group when those pages have been overwritten
+    taker = mgr.new_request()
+    assert mgr.try_allocate(taker, 12)  # takes three fresh pages in each group
+    short = mgr.match_prefix(tokens[:12] + [9])
+    served = len(short[0])
+    assert served in (0, 3)
+    if served:
+        assert NULL_PAGE not in short[1][mgr._first_needed_page(groups[1], 12) : 3]
+    mgr.free(first), mgr.free(second), mgr.free(taker)
+    mgr.check_invariants([])
+    assert mgr.pools[0].num_free == 12 and mgr.pools[1].num_free == 12
+
+
+def test_groups_have_pools_of_their_own_size():
+    groups = [GroupSpec("full"), GroupSpec("win", window=6, num_blocks=5)]
+    mgr = CacheManager(groups, num_blocks=16, block_size=4, max_num_seqs=2, enable_prefix_caching=False)
+    assert [p.num_pages for p in mgr.pools] == [16, 5] and mgr.smallest_pool == 16
+    req = mgr.new_request()
+    assert not mgr.try_allocate(req, 24) and req.holds_nothing()  # six pages at once: the window group has five
+    assert mgr.try_allocate(req, 16)
+    mgr.release_behind_window(req, 16)
+    assert mgr.try_allocate(req, 28)  # 7 pages of the full group; the window group holds pages 2..6 only
+    assert mgr.num_free_blocks == 0
+    mgr.check_invariants([req])
+    mgr.free(req)
+    mgr.check_invariants([])
 
 
 def test_window_group_gives_pages_back_while_the_request_runs():
@@ -128,7 +181,7 @@ def test_window_group_gives_pages_back_while_the_request_runs():
 
 
 def test_state_slots_run_out_and_come_back():
-    mgr = CacheManager(FULL, num_blocks=16, block_size=4, max_num_seqs=2, has_state=True)
+    mgr = CacheManager(FULL, num_blocks=16, block_size=4, max_num_seqs=2, slot_groups=[SlotGroupSpec("state")])
     reqs = [mgr.new_request() for _ in range(3)]
     assert mgr.try_allocate(reqs[0], 1) and mgr.try_allocate(reqs[1], 1)
     assert not mgr.try_allocate(reqs[2], 1) and reqs[2].holds_nothing()

@@ -267,7 +267,8 @@ def attention_reference(q, k, v, scale, window=None):
     return out
 
 
-def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None, stale=None, ramp=None):
+def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed, spike=None, stale=None, ramp=None,
+               window=None):
     """Sequences of the given lengths in scattered pages; the last ``new_counts[i]`` tokens of
     each are the batch's queries.  Returns kernel inputs and the expected output rows.  Slots that
     no sequence owns hold random numbers, or ``stale`` when given.  With ``ramp`` the scores of
@@ -304,7 +305,7 @@ def paged_case(lengths, new_counts, heads, kv_heads, head_dim, page, dtype, seed
         for p in range(n):
             k_pages[table[b, p // page], :, p % page] = k[p]
             v_pages[table[b, p // page], :, p % page] = v[p]
-        want = attention_reference(q.double(), k.double(), v.double(), head_dim**-0.5)
+        want = attention_reference(q.double(), k.double(), v.double(), head_dim**-0.5, window)
         q_rows.append(q[n - new :])
         want_rows.append(want[n - new :])
         entry_of += [b] * new
@@ -343,25 +344,13 @@ def test_paged_attention_generic(case, dtype):
 
 def test_paged_attention_generic_window():
     heads, kv_heads, head_dim, page, window = 4, 2, 16, 4, 10
-    data = paged_case([50, 9], [50, 3], heads, kv_heads, head_dim, page, torch.float32, seed=8)
+    data = paged_case([50, 9], [50, 3], heads, kv_heads, head_dim, page, torch.float32, seed=8, window=window)
     out = torch.empty_like(data["q"])
     ops().paged_attention_generic(
         data["q"], data["k_pages"], data["v_pages"], data["table"], data["entry_of"], data["positions"], out,
         heads, kv_heads, head_dim, head_dim**-0.5, window,
     )  # fmt: skip
-    # reference with the window: rebuild from the pages
-    wants = []
-    for b, (n, new) in enumerate(zip(data["lengths"], data["new_counts"])):
-        table = data["table"][b].cpu()
-        k = torch.stack([data["k_pages"][table[p // page], :, p % page].cpu() for p in range(n)]).double()
-        v = torch.stack([data["v_pages"][table[p // page], :, p % page].cpu() for p in range(n)]).double()
-        rows = data["entry_of"].cpu() == b
-        q_new = data["q"].cpu()[rows].view(new, heads, head_dim).double()
-        q = torch.zeros(n, heads, head_dim, dtype=torch.float64)
-        q[n - new :] = q_new
-        wants.append(attention_reference(q, k, v, head_dim**-0.5, window)[n - new :])
-    want = torch.cat(wants).reshape(-1, heads * head_dim)
-    assert rel_error(out.cpu(), want) < 2e-5
+    assert rel_error(out.cpu(), data["want"]) < 2e-5
 
 
 BF16_ATTENTION_CASES = [
@@ -384,12 +373,9 @@ BF16_ATTENTION_CASES = [
 ]
 
 
-@pytest.fixture(params=[0, 6, 8])
-def decode_warps(request, monkeypatch):
+@pytest.fixture(params=[None, 6, 8], ids=["by-rule", "six-warps", "eight-warps"])
+def decode_warps(request):
     """Warps of a CTA of the TMA decode kernel: by the engine's rule, six (tiles of 96 keys) or eight."""
-    from mini_engine_b200.csrc import attention_bf16
-
-    monkeypatch.setattr(attention_bf16, "FORCED_TMA_WARPS", request.param)
     return request.param
 
 
@@ -498,22 +484,52 @@ def test_paged_attention_tcgen05_growing_maximum(ramp):
 
 @pytest.mark.parametrize("news", [[1, 1], [90, 5]])
 def test_paged_attention_bf16_window(news, decode_warps):
+    """A window of 70 keys over contexts of 400 and 90, against attention in float64 with the
+    same window (a window edge inside a tile, a tile wholly behind the window)."""
     from mini_engine_b200.csrc import attention_bf16
 
     heads, kv_heads, head_dim, page, window = 4, 2, 64, 8, 70
     lengths = [400, 90]
-    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=12)
+    data = paged_case(lengths, news, heads, kv_heads, head_dim, page, torch.bfloat16, seed=12, window=window)
     out = torch.full_like(data["q"], float("nan"))
     attention_bf16.paged_attention(
         data["q"], data["k_pages"], data["v_pages"], data["table"], fake_context(data), out, heads, kv_heads,
         head_dim, head_dim**-0.5, window,
     )  # fmt: skip
-    generic = torch.empty_like(out)
-    ops().paged_attention_generic(
-        data["q"], data["k_pages"], data["v_pages"], data["table"], data["entry_of"], data["positions"], generic,
-        heads, kv_heads, head_dim, head_dim**-0.5, window,
-    )  # fmt: skip
-    assert rel_error(out, generic) < 1e-2
+    assert torch.isfinite(out).all()
+    assert rel_error(out.cpu(), data["want"]) < 1e-2
+    assert attention_bf16.take_error() == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
+    """Every barrier wait of the tensor-core kernels has a limit, after which the kernel records
+    an error word, gives its tensor memory back and returns.  The probe is a CTA with the product
+    kernels' warp roles whose copies are never issued, so its waits run out after a few thousand
+    polls: the error must reach the host, `raise_on_device_error` must raise exactly once, and
+    the next ordinary product must be right (tensor memory was freed, the context is intact)."""
+    from mini_engine_b200.csrc import ops as kernel_ops
+    from mini_engine_b200.csrc import tensor_core
+
+    kernel_ops.raise_on_device_error()  # nothing pending from earlier tests
+    assert tensor_core.wait_probe(polls=4096)  # it returned, past its dealloc
+    torch.cuda.synchronize()
+    with pytest.raises(kernel_ops.KernelError, match="limit of a wait"):
+        kernel_ops.raise_on_device_error()
+    kernel_ops.raise_on_device_error()  # taken: the word is clear again
+    # the code says which wait gave up first: the MMA warp's (40) or the epilogue's (41)
+    assert tensor_core.wait_probe(polls=2048)
+    assert tensor_core.take_error() >> 8 in (40, 41)
+    # many probes in a row leave tensor memory free: 512 columns per SM would be gone after 16 leaks
+    for _ in range(40):
+        assert tensor_core.wait_probe(polls=64)
+    assert tensor_core.take_error() != 0
+    torch.manual_seed(5)
+    x = torch.randn(40, 256, device="cuda").to(torch.bfloat16)
+    w = torch.randn(300, 256, device="cuda").to(torch.bfloat16)
+    out = torch.full((1, 40, 300), float("nan"), device="cuda")
+    tensor_core.gemm(tensor_core.GemmPlan(w), x, out, 1)
+    assert rel_error(out[0], x.double() @ w.double().T) < 1e-5
+    assert tensor_core.take_error() == 0
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -34,7 +34,7 @@ def make_runner(spec, dtype=torch.float32, page=4, pages=64, seed=0, scale=5.0):
     model.load(place_tensors(dict(host), specs, dtype, "cuda"))
     runner = ModelRunner(model, dtype=dtype, num_blocks=pages, block_size=page, max_num_seqs=4,
                          max_num_batched_tokens=256, max_model_len=pages * page)  # fmt: skip
-    manager = CacheManager(runner.layout.groups, pages, page, 4, False, has_state=runner.layout.has_state)
+    manager = CacheManager(runner.layout.groups, pages, page, 4, False, slot_groups=runner.layout.slot_groups)
     return model, runner, manager, host
 
 
@@ -279,6 +279,14 @@ def register_toy():
                 self.weight = tensors[self.name].float()
 
             def forward(self, h, ctx, cache):
+                if ctx.all_decode:
+                    # One token per entry: everything stays on the device (slots and fresh flags are
+                    # read there), so that a captured decode graph replays it for other requests.
+                    slots = ctx.state_slots.long()
+                    state = cache.state[slots] * (1.0 - ctx.fresh.float())[:, None]
+                    state = state * self.decay + h.float()
+                    cache.state.index_copy_(0, slots, state)
+                    return (state @ self.weight.T).unsqueeze(0)
                 out = torch.empty(1, h.shape[0], self.hidden, device=h.device)
                 row = 0
                 for count, start, slot in zip(ctx.host["counts"], ctx.host["starts"], ctx.host["state_slots"]):
@@ -373,6 +381,57 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
 
 
 # ------------------------------ a toy position encoding and a toy routed feed-forward
+
+
+def test_toy_mixer_with_state_runs_through_the_engine_without_steps_launched_ahead(tmp_path):
+    """A step that was launched ahead and then dropped is run again, which would advance a mixer's
+    own state twice; so for a model with such a mixer the scheduler plans no step ahead.  Requests
+    that end early on an end-of-sequence token (the case that drops steps) give the same tokens
+    with `overlap_steps` on and off, equal to the whole-sequence restatement of the toy model."""
+    from safetensors.torch import load_file
+
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.weights import write_random_model
+
+    ToyConfig = register_toy()
+    cfg = ToyConfig(vocab_size=40, hidden_size=24, intermediate_size=32, decay=0.7, eps=1e-5)
+    folder = write_random_model(tmp_path / "toy", cfg, seed=6, dtype=torch.float32, scale=8.0)
+    w = load_file(str(folder / "model.safetensors"))
+
+    def plain_next(tokens):
+        x = w["embed.weight"][torch.tensor(tokens)]
+        for _ in range(2):
+            normed = plain.rms_norm(x, w["layers.0.norm1.weight"], cfg.eps)
+            state, rows = torch.zeros(cfg.hidden_size), []
+            for row in normed:
+                state = state * cfg.decay + row
+                rows.append(state @ w["layers.0.toy.weight"].T)
+            x = x + torch.stack(rows)
+            x = x + plain.swiglu_mlp(plain.rms_norm(x, w["layers.0.norm2.weight"], cfg.eps), w, "layers.0.")
+        logits = plain.rms_norm(x, w["final.weight"], cfg.eps) @ w["embed.weight"].T
+        return int(logits[-1].argmax())
+
+    prompts = [[3, 1, 4, 1, 5], [9, 2, 6], [5, 3, 5, 8, 9, 7, 9]]
+    options = dict(block_size=16, num_blocks=16, max_model_len=64, max_num_seqs=4)
+    free_run = LLMEngine.from_pretrained(folder, EngineConfig(**options)).generate(prompts, SamplingParams(max_tokens=10))
+    for prompt, out in zip(prompts, free_run):
+        ids = list(prompt)
+        for token in out:
+            assert plain_next(ids) == token
+            ids.append(token)
+    eos = {free_run[0][3], free_run[2][6]}
+    runs = {}
+    for overlap in (False, True):
+        engine = LLMEngine.from_pretrained(folder, EngineConfig(overlap_steps=overlap, **options))
+        engine.scheduler.eos_token_ids = set(eos)
+        runs[overlap] = engine.generate(prompts, SamplingParams(max_tokens=10))
+        assert engine.stats.graph_steps > 0  # decode steps replay graphs, with the state slots in them
+        assert engine.stats.prepacked_steps == 0 and engine.stats.dropped_steps == 0
+        engine.block_manager.check_invariants([])
+    assert runs[True] == runs[False]
+    assert any(len(out) < 10 for out in runs[True])
+    for out, free in zip(runs[True], free_run):
+        assert out == free[: len(out)]
 
 
 def test_toy_position_encoding_is_registered_and_applied():
@@ -479,3 +538,103 @@ def test_toy_routed_feed_forward_is_registered_and_stepped():
     x = x + routed_out
     want = plain.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
     assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
+
+
+# ------------------------------------------- the model's two ends and blocks with more norms
+
+
+def test_embedding_multiplier_and_a_head_with_bias_scale_and_cap():
+    """An embedding multiplier, a head bias, a logit scale and a soft cap are options of the two
+    end parts: a spec switches them on, nothing else changes.  Whole == cut, and equal to the plain
+    model with the same four changes restated here."""
+    from mini_engine_b200.config.model_spec import PartSpec
+
+    base = one_layer_spec(**SIZES, layers=2)
+    spec = type(base)(**{
+        **base.__dict__,
+        "embedding": PartSpec("token_embedding", {"weight": "model.embed_tokens.weight", "multiplier": 48**0.5}),
+        "head": PartSpec("linear_head", {"weight": "lm_head.weight", "tied_to": "model.embed_tokens.weight",
+                                         "bias": "lm_head.bias", "logit_scale": 0.25, "soft_cap": 3.0}),
+    })  # fmt: skip
+    model, runner, manager, host = make_runner(spec, scale=2.0)
+    assert "lm_head.bias" in host and "lm_head.weight" not in host  # tied: one tensor; the bias is the head's own
+    tokens = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+    cfg = plain_cfg(**SIZES, layers=2)
+    x = host["model.embed_tokens.weight"][torch.tensor(tokens)] * 48**0.5
+    for index in range(2):
+        x = plain.decoder_layer(x, host, index, cfg, torch.arange(len(tokens)))
+    x = plain.rms_norm(x, host["model.norm.weight"], cfg["eps"])
+    logits = (x @ host["model.embed_tokens.weight"].T) * 0.25 + host["lm_head.bias"]
+    want = 3.0 * torch.tanh(logits / 3.0)
+    assert float(want.abs().max()) > 1.5  # the cap bends the largest logits
+    assert torch.allclose(whole, want, atol=3e-5, rtol=1e-4)
+
+
+def test_a_block_with_four_norms_is_registered_from_here():
+    """A post-norm arrangement (a norm in front of and behind both the mixer and the feed-forward,
+    four per layer) is a block class that names its norms; the layer's spec gives them by name.
+    Nothing of the framework changes.  The block adds the normed outputs into the stream itself."""
+    from mini_engine_b200.config.model_spec import LayerSpec, PartSpec
+    from mini_engine_b200.parts.base import BLOCKS, Block, Residual, register
+
+    if "toy_sandwich" not in BLOCKS:
+
+        @register("block", "toy_sandwich")
+        class SandwichBlock(Block):
+            """``h = x + post_m(mixer(pre_m(x)))``, ``y = h + post_f(ff(pre_f(h)))``."""
+
+            NORMS = ("mixer", "after_mixer", "feed_forward", "after_feed_forward")
+
+            def _after(self, name, out, state, ctx):
+                # normalise the part's output on its own (an all-zero stream plus the pending slices), then
+                # hand the normed rows to the residual stream as its next pending addend
+                normed = self.norms[name].forward(Residual(torch.zeros_like(state.x), out), ctx, torch.float32)
+                state.add(normed.clone())
+
+            def forward(self, state, ctx, cache):
+                h = self.norms["mixer"].forward(state, ctx, ctx.dtype)
+                self._after("after_mixer", self.mixer.forward(h, ctx, cache), state, ctx)
+                h = self.norms["feed_forward"].forward(state, ctx, ctx.dtype)
+                self._after("after_feed_forward", self.feed_forward.forward(h, ctx), state, ctx)
+
+    base = one_layer_spec(**SIZES, layers=2)
+    eps = 2e-5
+    layers = tuple(
+        LayerSpec(
+            prefix=layer.prefix, block="toy_sandwich", mixer=layer.mixer, feed_forward=layer.feed_forward,
+            norms={
+                "mixer": layer.mixer_norm,
+                "after_mixer": PartSpec("rmsnorm", {"name": "post_mixer_norm.weight", "eps": eps}),
+                "feed_forward": layer.feed_forward_norm,
+                "after_feed_forward": PartSpec("rmsnorm", {"name": "post_ff_norm.weight", "eps": eps}),
+            },
+        )
+        for layer in base.layers
+    )  # fmt: skip
+    spec = type(base)(**{**base.__dict__, "layers": layers})
+    model, runner, manager, host = make_runner(spec, scale=3.0)
+    assert "model.layers.1.post_ff_norm.weight" in host and len(model.blocks[0].norms) == 4
+    tokens = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+    cfg = plain_cfg(**SIZES, layers=2)
+    positions = torch.arange(len(tokens))
+    x = host["model.embed_tokens.weight"][torch.tensor(tokens)]
+    for index in range(2):
+        p = f"model.layers.{index}."
+        a = plain.attention_block(plain.rms_norm(x, host[p + "input_layernorm.weight"], eps), host, p + "self_attn.", cfg, positions)
+        x = x + plain.rms_norm(a, host[p + "post_mixer_norm.weight"], eps)
+        f = plain.swiglu_mlp(plain.rms_norm(x, host[p + "post_attention_layernorm.weight"], eps), host, p + "mlp.")
+        x = x + plain.rms_norm(f, host[p + "post_ff_norm.weight"], eps)
+    want = plain.rms_norm(x, host["model.norm.weight"], eps) @ host["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=3e-5, rtol=1e-4)
+    # a layer that names the wrong norms is refused when the model is built
+    wrong = type(base)(**{**base.__dict__, "layers": tuple(
+        LayerSpec(prefix=l.prefix, block="toy_sandwich", mixer=l.mixer, feed_forward=l.feed_forward,
+                  mixer_norm=l.mixer_norm, feed_forward_norm=l.feed_forward_norm) for l in base.layers)})  # fmt: skip
+    from mini_engine_b200.parts.model import DecoderModel
+
+    with pytest.raises(ValueError, match="wants the norms"):
+        DecoderModel(wrong)

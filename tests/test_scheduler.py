@@ -201,3 +201,107 @@ def test_random_workloads_finish_with_every_invariant_kept(seed):
     run_to_end(sched)
     assert all(s.is_finished and s.num_output_tokens == s.params.max_tokens for s in seqs)
     cache.check_invariants([])
+
+
+# ---------------------------------------------------------------- plans and the step after
+
+
+def test_a_plan_carries_the_entries_of_its_items():
+    sched, _ = make(budget=8, prefix=False)
+    long, short = request(13), request(2, base=100)
+    sched.add(long), sched.add(short)
+    plan = sched.plan()
+    assert [(e.start, list(e.token_ids), tuple(e.want)) for e in plan.entries] == [(0, list(range(8)), ())]
+    assert plan.entries[0].cache is long.cache and not plan.decode_only
+    sched.postprocess(plan.items, [None])
+    plan = sched.plan()
+    assert [(e.start, len(e.token_ids), tuple(e.want)) for e in plan.entries] == [(8, 5, (4,)), (0, 2, (1,))]
+    sched.postprocess(plan.items, [7, 7])
+    plan = sched.plan()  # both decode now
+    assert plan.decode_only and [(e.start, list(e.token_ids), tuple(e.want)) for e in plan.entries] == [(13, [7], (0,)), (2, [7], (0,))]
+
+
+def decoding(sched, seqs):
+    """Adds the requests and runs steps until every one of them decodes."""
+    for s in seqs:
+        sched.add(s)
+    while any(s.num_computed_tokens < s.num_prompt_tokens for s in seqs):
+        step(sched)
+
+
+def test_the_step_after_is_planned_when_it_is_certain():
+    sched, cache = make(num_blocks=16, block_size=4)
+    a, b = request(3, max_tokens=6), request(6, max_tokens=6, base=50)
+    decoding(sched, [a, b])
+    plan = sched.plan()
+    free_before = cache.num_free_blocks
+    ahead = sched.plan_ahead(plan)
+    assert ahead is not None and [row for row, _ in ahead.staying] == [0, 1]
+    # one position further than the step being run, a placeholder token each, logits wanted
+    assert [(e.start, list(e.token_ids), tuple(e.want)) for e in ahead.entries] == [
+        (a.num_computed_tokens + 1, [0], (0,)), (b.num_computed_tokens + 1, [0], (0,))]  # fmt: skip
+    # `a` holds 4 tokens after this step and its next token opens a second page, taken here already
+    assert len(a.cache.block_tables[0]) == 2 and cache.num_free_blocks == free_before - 1
+    sched.postprocess(plan.items, [1, 1])
+    following = sched.plan()
+    assert [(e.cache, e.start) for e in following.entries] == [(e.cache, e.start) for e in ahead.entries]
+    assert cache.num_free_blocks == free_before - 1  # the plan found its pages taken
+    cache.check_invariants([a.cache, b.cache])
+
+
+def test_requests_that_end_at_their_own_limit_are_left_out_of_the_step_after():
+    sched, _ = make()
+    ends, goes_on = request(3, max_tokens=2), request(5, max_tokens=9, base=50)
+    decoding(sched, [ends, goes_on])  # each has one generated token now
+    plan = sched.plan()
+    ahead = sched.plan_ahead(plan)
+    assert ahead is not None and [(row, item.seq) for row, item in ahead.staying] == [(1, goes_on)]
+    assert len(ahead.entries) == 1 and ahead.entries[0].cache is goes_on.cache
+    finished = sched.postprocess(plan.items, [1, 1])
+    assert finished == [ends]
+    assert [e.cache for e in sched.plan().entries] == [goes_on.cache]
+
+
+def test_no_step_is_planned_ahead_when_the_next_plan_is_open():
+    # a request waits and a place is free: the next step admits it
+    sched, _ = make(max_num_seqs=2)
+    first = request(3, max_tokens=8)
+    decoding(sched, [first])
+    plan = sched.plan()
+    sched.waiting.append(Sequence([1, 2, 3], SamplingParams(max_tokens=2)))  # arrives while the step runs
+    sched.waiting[-1].cache = sched.cache.new_request()
+    assert sched.plan_ahead(plan) is None
+    # ... unless every place stays taken
+    sched, _ = make(max_num_seqs=2)
+    pair = [request(3, max_tokens=8), request(4, max_tokens=8, base=30)]
+    decoding(sched, pair)
+    sched.add(request(2, max_tokens=2, base=60))
+    plan = sched.plan()
+    assert len(plan.items) == 2 and sched.plan_ahead(plan) is not None
+    # a step with a prompt portion in it is no decode step
+    sched, _ = make(budget=4)
+    sched.add(request(9))
+    assert sched.plan_ahead(sched.plan()) is None
+    # pages for one more token cannot be had without preempting
+    sched, cache = make(num_blocks=3, block_size=4, prefix=False, max_model_len=16)
+    two = [request(3, max_tokens=5), request(3, max_tokens=5, base=40)]
+    decoding(sched, two)  # 4 tokens each after the step planned now: a page each is full, one page is free
+    plan = sched.plan()
+    assert sched.plan_ahead(plan) is None
+    cache.check_invariants([s.cache for s in sched.running])
+    # the model's length limit ends a request with the token being drawn
+    sched, _ = make(max_model_len=8)
+    last = request(5, max_tokens=3)
+    decoding(sched, [last])
+    step(sched)
+    plan = sched.plan()  # computes token 7 of 8: nothing can follow
+    assert sched.plan_ahead(plan) is None
+
+
+def test_no_step_is_planned_ahead_for_a_model_whose_steps_cannot_be_rerun():
+    cache = CacheManager([GroupSpec("full")], 16, 4, 4, True)
+    sched = Scheduler(SchedulerConfig(4, 64, 64), cache, {EOS}, rerun_safe=False)
+    one = request(3, max_tokens=8)
+    decoding(sched, [one])
+    plan = sched.plan()
+    assert plan.decode_only and sched.plan_ahead(plan) is None
