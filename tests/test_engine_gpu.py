@@ -417,6 +417,33 @@ def test_a_replayed_graph_gives_the_bits_of_the_eager_step(name, model_folders):
     manager.check_invariants([])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_random_weights_in_memory_equal_those_of_a_written_folder(dtype, tmp_path):
+    """`LLMEngine.from_random(config, seed)` makes its weights on the device, `write_random_model`
+    on the host; both are the same function of (seed, tensor name, element index), so the two
+    engines give the same logits bit for bit."""
+    from tiny_configs import CONFIGS
+
+    from mini_engine_b200 import EngineConfig, LLMEngine
+    from mini_engine_b200.config import Qwen3Config
+    from mini_engine_b200.engine.runner import StepEntry
+    from mini_engine_b200.weights import write_random_model
+
+    cfg = Qwen3Config.from_dict(CONFIGS["C"])
+    options = EngineConfig(block_size=16, num_blocks=16, max_model_len=128, max_num_seqs=2, dtype=dtype, cuda_graphs=False)
+    in_memory = LLMEngine.from_random(cfg, seed=21, config=options)
+    folder = write_random_model(tmp_path / "m", cfg, seed=21, dtype=torch.bfloat16 if dtype == torch.bfloat16 else torch.float32)
+    from_folder = LLMEngine.from_pretrained(folder, options)
+    tokens = random_ids(2100, 70, cfg.vocab_size)
+    logits = []
+    for engine in (in_memory, from_folder):
+        cache = engine.block_manager.new_request()
+        assert engine.block_manager.try_allocate(cache, len(tokens))
+        logits.append(engine.runner.execute([StepEntry(cache, 0, tokens, tuple(range(len(tokens))))]).clone())
+    assert torch.equal(logits[0], logits[1])
+    assert float(logits[0].abs().max()) > 0
+
+
 def test_command_line(peaked_model_folders):
     import subprocess
     import sys

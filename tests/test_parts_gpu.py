@@ -250,6 +250,56 @@ def test_layers_with_and_without_a_window_get_groups_of_their_own():
     assert torch.allclose(whole, want, atol=1e-4, rtol=1e-4)
 
 
+def test_prefix_hits_with_a_windowed_layer_through_the_engine():
+    """A model whose second layer reads only the last 6 keys, through the scheduler with prefix
+    reuse on: requests that share a prompt prefix skip it (the window group supplies the pages its
+    window reaches, its table starts with pages that were never taken), the window group's own pool
+    is far smaller than the other's, and the tokens equal those of an engine without prefix reuse
+    and the plain implementation's."""
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.config.model_spec import PartSpec
+    from mini_engine_b200.parts.model import DecoderModel
+    from mini_engine_b200.weights.loader import place_tensors
+    from mini_engine_b200.weights.random_init import random_tensors
+
+    base = one_layer_spec(**SIZES, layers=2)
+    windowed = base.layers[1]
+    mixer = PartSpec(windowed.mixer.kind, {**windowed.mixer.params, "window": 6})
+    spec = type(base)(**{**base.__dict__, "layers": (base.layers[0], type(windowed)(**{**windowed.__dict__, "mixer": mixer}))})
+    model = DecoderModel(spec)
+    host = random_tensors(model.weight_specs(), 3, torch.float32, scale=5.0)
+    model.load(place_tensors(dict(host), model.weight_specs(), torch.float32, "cuda"))
+    shared = [7, 3, 9, 1, 4, 4, 8, 2, 6, 5, 11, 13, 12, 10, 15, 14, 17, 19, 21, 23]  # five pages of four
+    prompts = [shared + tail for tail in ([30, 31], [32], [33, 34, 35, 36, 37], [38, 39, 40])]
+    options = dict(block_size=4, num_blocks=48, max_model_len=64, max_num_seqs=2, max_num_batched_tokens=16)
+    runs = {}
+    for reuse in (False, True):
+        engine = LLMEngine(model, EngineConfig(enable_prefix_caching=reuse, **options), [])
+        groups = engine.runner.layout.groups
+        assert [g.window for g in groups] == [None, 6]
+        # window 6 + a step of 16 tokens: 6 pages and two for the edges, for each of two requests
+        assert groups[0].num_blocks == 48 and groups[1].num_blocks == 2 * (-(-(6 + 16) // 4) + 2)
+        runs[reuse] = [engine.generate([p], SamplingParams(max_tokens=6))[0] for p in prompts]
+        engine.block_manager.check_invariants([])
+        assert [pool.num_free for pool in engine.block_manager.pools] == [g.num_blocks for g in groups]
+        if reuse:
+            assert engine.scheduler.num_cached_tokens == 3 * 20  # every later request found the five shared pages
+        else:
+            assert engine.scheduler.num_cached_tokens == 0
+    assert runs[True] == runs[False]
+    cfg0, cfg1 = plain_cfg(**SIZES, layers=2), plain_cfg(**SIZES, layers=2, window=6)
+    for prompt, out in zip(prompts, runs[True]):
+        ids = list(prompt)
+        for token in out:
+            x = host["model.embed_tokens.weight"][torch.tensor(ids)]
+            x = plain.decoder_layer(x, host, 0, cfg0, torch.arange(len(ids)))
+            x = plain.decoder_layer(x, host, 1, cfg1, torch.arange(len(ids)))
+            logits = plain.rms_norm(x[-1:], host["model.norm.weight"], cfg0["eps"]) @ host["lm_head.weight"].T
+            top = torch.topk(logits[0], 2).values
+            assert int(logits[0].argmax()) == token or float(top[0] - logits[0][token]) < 1e-3
+            ids.append(token)
+
+
 # --------------------------------------------------- a toy mixer with state of its own
 
 
