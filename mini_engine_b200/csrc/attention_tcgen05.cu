@@ -354,6 +354,289 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 1) tcgen05_dealloc(tmem_s, TC_TMEM_COLUMNS);
 }
 
+// ------------------------------------------------ two query heads of one KV group per CTA
+//
+// The kernel above keeps the tensor pipe a third busy: a CTA's tile is one dependent chain (scores,
+// softmax, second product) and only the SM's other CTA fills the gaps.  Here one CTA carries two such
+// chains that never wait for each other and share everything they can: the 128 new tokens of TWO
+// query heads of the same KV group.  Both heads read the same keys and values, so one K tile and one
+// V tile in shared memory (two stages each) feed four products per tile, and both heads have the same
+// positions, hence the same masks and the same number of tiles.  Tensor memory holds S_a, S_b, O_a and
+// O_b (512 columns, the whole of it: one CTA per SM).  A softmax thread owns a whole row of one head
+// (128 scores in registers), so no two threads exchange anything: each of the two groups of 128
+// threads talks to the MMA warp through its own barriers only.  The MMA warp issues
+//     S_a(0), S_b(0);  then per tile j:  O_a += P_a V(j),  S_a(j+1),  O_b += P_b V(j),  S_b(j+1)
+// so that while group a turns S_a(j+1) into probabilities the pipe runs O_b(j) and S_b(j+1), and
+// the other way round.  Lazy rescaling, masking by position and page addressing as above.
+constexpr int DUO_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-5 rows of head a, warps 6-9 rows of head b
+constexpr int DUO_TMEM_COLUMNS = 512;
+constexpr int DUO_TILE_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 bfloat16 tile as two 64-column halves
+constexpr int DUO_SMEM_BYTES = 6 * DUO_TILE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(DUO_THREADS, 1)
+attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_tiles = tiles;                       // [2 heads][2 halves][128 rows][64 dims]
+    uint8_t* k_tiles = tiles + 2 * DUO_TILE_BYTES;  // [2 stages][2 halves][128 keys][64 dims]
+    uint8_t* v_tiles = tiles + 4 * DUO_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + 6 * DUO_TILE_BYTES);
+    uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
+             *s_full = bars + 9, *p_full = bars + 11, *o_full = bars + 13;  // o_full[2 heads][2 tile parities]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head0 = 2 * blockIdx.x, q_block = gridDim.y - 1 - blockIdx.y;  // the longest blocks start first
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + i, 1);
+            mbar_init(k_empty + i, 1);
+            mbar_init(v_full + i, 1);
+            mbar_init(v_empty + i, 1);
+            mbar_init(s_full + i, 1);
+            mbar_init(p_full + i, 128);
+        }
+        for (int i = 0; i < 4; ++i) mbar_init(o_full + i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tcgen05_alloc(tmem_holder, DUO_TMEM_COLUMNS);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_holder;  // S_a, S_b at columns 0 and 128 (P over the first 64 of each), O_a, O_b at 256 and 384
+
+    pdl_trigger();
+    pdl_wait();
+    const int entry = p.entry_ids ? p.entry_ids[blockIdx.z] : blockIdx.z;
+    const int token0 = p.cu_tokens[entry];
+    const int new_tokens = p.cu_tokens[entry + 1] - token0;
+    const bool has_work = q_block * TC_ROWS < new_tokens;  // uniform for the CTA
+    const int context = p.context_lens[entry];
+    const int rows_valid = min(TC_ROWS, new_tokens - q_block * TC_ROWS);
+    const int pos0 = context - new_tokens + q_block * TC_ROWS;  // position of row 0
+    const int tiles_count = has_work ? (pos0 + rows_valid - 1) / TC_KEYS + 1 : 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (has_work) {
+            const int kv_head = head0 / (p.heads / p.kv_heads);
+            const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+            const int pages_per_tile = TC_KEYS / p.page_size;
+            const int last_page_index = (context - 1) / p.page_size;
+            const int page_bytes = p.page_size * 128;  // one page of one 64-dimension half
+            if (lane == 0) {
+                mbar_expect_tx(q_full, 2 * DUO_TILE_BYTES);
+                for (int h = 0; h < 2; ++h)
+                    for (int half = 0; half < 2; ++half)
+                        tma_load_2d(q_tiles + h * DUO_TILE_BYTES + half * TC_HALF_BYTES, &map_q,
+                                    (head0 + h) * TC_DIM + half * 64, token0 + q_block * TC_ROWS, q_full);
+            }
+            const bool loads = lane < pages_per_tile;
+            int page = loads ? table[min(lane, last_page_index)] : 0;
+            bool ok = true;
+            for (int j = 0; j < tiles_count && ok; ++j) {
+                const int stage = j & 1;
+                const uint32_t parity = (j >> 1) & 1;
+                const int next_page = (loads && j + 1 < tiles_count) ? table[min((j + 1) * pages_per_tile + lane, last_page_index)] : 0;
+                const int row = (page * p.kv_heads + kv_head) * p.page_size;
+                for (int which = 0; which < 2 && ok; ++which) {  // keys, then values
+                    uint64_t* empty = (which ? v_empty : k_empty) + stage;
+                    uint64_t* full = (which ? v_full : k_full) + stage;
+                    uint8_t* tile = (which ? v_tiles : k_tiles) + stage * DUO_TILE_BYTES;
+                    const CUtensorMap* map = which ? &map_v : &map_k;
+                    if (lane == 0) {
+                        ok = mbar_wait(empty, parity ^ 1);
+                        if (ok) mbar_expect_tx(full, DUO_TILE_BYTES);
+                        else atomicCAS(&g_attention_error, 0, (11 << 8) | which);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (ok && loads) {
+                        tma_load_2d(tile + lane * page_bytes, map, 0, row, full);
+                        tma_load_2d(tile + TC_HALF_BYTES + lane * page_bytes, map, 64, row, full);
+                    }
+                }
+                page = next_page;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && has_work) {
+            constexpr uint32_t idesc_s = make_idesc(TC_KEYS);       // S[128 x 128] = Q K^T, K-major operands
+            constexpr uint32_t idesc_o = make_idesc(TC_DIM, true);  // O[128 x 128] += P V, V is MN-major
+            auto scores = [&](int h, int stage) {
+                const uint32_t q = smem_u32(q_tiles + h * DUO_TILE_BYTES), k = smem_u32(k_tiles + stage * DUO_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_DIM / 16; ++kk) {
+                    const uint32_t offset = (kk / 4) * TC_HALF_BYTES + (kk % 4) * 32;
+                    tcgen05_mma_bf16(tmem_base + h * 128, smem_desc_sw128(q + offset), smem_desc_sw128(k + offset), idesc_s,
+                                     kk > 0 ? 1u : 0u);
+                }
+                tcgen05_commit(s_full + h);
+            };
+            auto outputs = [&](int h, int stage, int j) {
+                const uint32_t v = smem_u32(v_tiles + stage * DUO_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_KEYS / 16; ++kk)
+                    tcgen05_mma_bf16_ts(tmem_base + 256 + h * 128, tmem_base + h * 128 + kk * 8,
+                                        smem_desc_sw128_mn(v + kk * 16 * 128, TC_HALF_BYTES), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                tcgen05_commit(o_full + h * 2 + (j & 1));
+            };
+            bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
+            if (!ok) atomicCAS(&g_attention_error, 0, 12 << 8);
+            if (ok) {
+                tcgen05_fence_after();
+                scores(0, 0);
+                scores(1, 0);
+                tcgen05_commit(k_empty);
+            }
+            for (int j = 0; j < tiles_count && ok; ++j) {
+                const int stage = j & 1, next = stage ^ 1;
+                const uint32_t tile_parity = j & 1, stage_parity = (j >> 1) & 1, next_parity = ((j + 1) >> 1) & 1;
+                const bool more = j + 1 < tiles_count;
+                // head a: its probabilities of tile j are ready; then its scores of tile j + 1.  The
+                // MMAs of a CTA run in the order of their issue, so the scores cannot overwrite the
+                // probabilities that the product before them still reads.
+                ok = mbar_wait(v_full + stage, stage_parity) && mbar_wait(p_full, tile_parity);
+                if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 1); break; }
+                tcgen05_fence_after();
+                outputs(0, stage, j);
+                if (more) {
+                    ok = mbar_wait(k_full + next, next_parity);
+                    if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 2); break; }
+                    tcgen05_fence_after();
+                    scores(0, next);
+                }
+                // head b likewise; after its products the stages of V(j) and K(j + 1) are free
+                ok = mbar_wait(p_full + 1, tile_parity);
+                if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 3); break; }
+                tcgen05_fence_after();
+                outputs(1, stage, j);
+                tcgen05_commit(v_empty + stage);
+                if (more) {
+                    scores(1, next);
+                    tcgen05_commit(k_empty + next);
+                }
+            }
+        }
+    } else if (has_work) {
+        // ------------------------------------------------------------------ softmax rows
+        const int h = (warp - 2) >> 2;  // which of the two heads
+        const int quarter = warp & 3;   // this warp's tensor-memory lanes are [32 * quarter, +32)
+        const int row = quarter * 32 + lane;
+        const int row_pos = pos0 + row;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + h * 128 + lane_base, tmem_o = tmem_base + 256 + h * 128 + lane_base;
+        uint64_t* my_o_full = o_full + h * 2;
+        float row_max = -INFINITY, row_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < tiles_count; ++j) {
+            ok = __all_sync(0xffffffffu, mbar_wait(s_full + h, j & 1));
+            if (!ok) break;
+            tcgen05_fence_after();
+            const int first_key = j * TC_KEYS;
+            const bool masked_tile = first_key + TC_KEYS - 1 > pos0;  // some row must not see some key of the tile
+            uint32_t raw[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tcgen05_ld32_nowait(tmem_s + c * 32, raw + c * 32);
+            tcgen05_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tcgen05_pin32(raw + c * 32);
+            float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (masked_tile) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (first_key + i <= row_pos) best[i & 3] = fmaxf(best[i & 3], __uint_as_float(raw[i]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 128; i += 2)
+                    best[(i >> 1) & 3] = fmax3(best[(i >> 1) & 3], __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+            }
+            const float tile_max = fmaxf(fmaxf(best[0], best[1]), fmaxf(best[2], best[3])) * p.scale_log2;  // the scale is positive
+            // The reference value of the row follows its maximum lazily, as in the kernel above.
+            const float new_max = fmaxf(row_max, tile_max);
+            if (j == 0) {
+                row_max = new_max;
+            } else if (__any_sync(0xffffffffu, new_max - row_max > 8.0f)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(my_o_full + ((j - 1) & 1), ((j - 1) >> 1) & 1));  // the MMAs run in order: all of O is complete
+                if (!ok) break;
+                tcgen05_fence_after();
+                const float rescale = exp2f(row_max - new_max);
+                row_sum *= rescale;
+                row_max = new_max;
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    float o[16];
+                    tcgen05_ld16(tmem_o + c * 16, o);
+                    uint32_t scaled[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) scaled[i] = __float_as_uint(o[i] * rescale);
+                    tcgen05_st16(tmem_o + c * 16, scaled);
+                }
+            }
+            const float base = row_max == -INFINITY ? 0.0f : row_max;
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(-base, -base);
+            float2 partial[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t packed[16];
+                if (masked_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = first_key + c * 32 + i;
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
+                        const float2 pr = make_float2(key <= row_pos ? fast_exp2(x.x) : 0.0f, key + 1 <= row_pos ? fast_exp2(x.y) : 0.0f);
+                        partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
+                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
+                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                    }
+                }
+                // P columns [16 c, +16) hold keys [32 c, +32); this thread has read its whole row of S
+                tcgen05_st16(tmem_s + c * 16, packed);
+            }
+            row_sum += (partial[0].x + partial[0].y) + (partial[1].x + partial[1].y);
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(p_full + h);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(my_o_full + ((tiles_count - 1) & 1), ((tiles_count - 1) >> 1) & 1));
+        if (!ok && lane == 0) atomicCAS(&g_attention_error, 0, 13 << 8);
+        if (ok) {
+            tcgen05_fence_after();
+            const float inv = 1.0f / row_sum;
+            __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head0 + h) * TC_DIM;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float o[32];
+                tcgen05_ld32(tmem_o + c * 32, o);  // collective: every lane takes part
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 chunk;
+                        chunk.x = pack_bf16x2(o[i] * inv, o[i + 1] * inv);
+                        chunk.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
+                        chunk.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
+                        chunk.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = chunk;
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem_base, DUO_TMEM_COLUMNS);
+}
+
 // -------------------------------------------------------------------------------- host
 
 // q, k and v are described by TMA maps made with me_make_tensor_map (gemm_tcgen05.cu): q as
@@ -372,11 +655,17 @@ ME_EXPORT int me_attention_tcgen05(const void* map_q, const void* map_k, const v
     memcpy(&v, map_v, sizeof(v));
     TcAttnParams p{block_table, cu_tokens, context_lens, entry_ids, static_cast<__nv_bfloat16*>(out), scale * TC_LOG2E,
                    heads, kv_heads, page_size, table_width};
+    const int blocks = (max_new_tokens + TC_ROWS - 1) / TC_ROWS;
+    if ((heads / kv_heads) % 2 == 0) {  // two query heads of a KV group per CTA
+        static SharedMemoryOptIn duo_opt_in;
+        if (const int e = duo_opt_in(attention_tcgen05_duo_kernel, DUO_SMEM_BYTES)) return e;
+        return launch_kernel(attention_tcgen05_duo_kernel, dim3(heads / 2, blocks, entries), DUO_THREADS, DUO_SMEM_BYTES,
+                             stream, q, k, v, p);
+    }
     constexpr int SMEM = 6 * TC_HALF_BYTES + 1024 + 256 + 2 * 2 * 128 * 4;
     static SharedMemoryOptIn opt_in;
     if (const int e = opt_in(attention_tcgen05_kernel, SMEM)) return e;
-    dim3 grid(heads, (max_new_tokens + TC_ROWS - 1) / TC_ROWS, entries);
-    return launch_kernel(attention_tcgen05_kernel, grid, TC_THREADS, SMEM, stream, q, k, v, p);
+    return launch_kernel(attention_tcgen05_kernel, dim3(heads, blocks, entries), TC_THREADS, SMEM, stream, q, k, v, p);
 }
 
 ME_EXPORT int me_attention_take_error(int* code) {

@@ -444,6 +444,11 @@ TENSOR_MEMORY_CASES = [
     ([1000, 3, 257], [256, 3, 257], 4, 4, 32),  # the last 256 tokens of 1000; a tiny entry in the same launch
     ([500, 90, 300, 64, 17], [1, 90, 1, 64, 1], 8, 2, 16),  # decoded tokens of some beside portions of others
     ([2048], [2048], 2, 1, 128),  # pages as large as a tile
+    # groups of an odd number of query heads (and of one) take the kernel with one head per CTA,
+    # even groups the one that carries two heads of a KV group per CTA
+    ([300, 129], [300, 64], 6, 2, 16),
+    ([640], [640], 3, 3, 64),
+    ([1500, 200], [1500, 130], 8, 1, 16),  # a group of eight: four CTAs share each block's keys
 ]
 
 
