@@ -83,6 +83,39 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
+// The high halves of two float32 values side by side: both cut to bfloat16 (toward zero) by one
+// byte permutation on the integer pipe.  The conversion instruction rounds to nearest but runs on
+// the special-function unit, which the exponentials already fill.
+__device__ __forceinline__ uint32_t cut_bf16x2(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+}
+
+// Cutting loses half a bfloat16 step on average, 2^-8 / m of a value with mantissa m; over
+// mantissas spread evenly in the exponent (what exponentials of spread-out scores give) that is
+// 0.7213 * 2^-8 = 0.28 %.  The probabilities are therefore formed CUT_GAIN too large, so that what
+// is left after the cut is right on average, and the row sums, which add the uncut values, are
+// divided by the same factor at the end.
+constexpr float CUT_GAIN = 1.0f + 0.7213475f / 256.0f;
+constexpr float CUT_GAIN_LOG2 = 0.0040598f;  // log2(CUT_GAIN)
+
+// 2^x for two values on the multiply-add pipe alone: x = n + r with n the nearest integer (the add
+// of 1.5 * 2^23 leaves n in the low mantissa bits) and r in [-0.5, 0.5]; 2^r by a cubic whose
+// relative error is below 8e-5 (the result is cut to bfloat16, step 4e-3); n goes into the
+// exponent field by one shift-and-add.  Values below 2^-126 come out as 2^-126.
+__device__ __forceinline__ float2 poly_exp2_pair(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 magic = make_float2(12582912.0f, 12582912.0f), minus_magic = make_float2(-12582912.0f, -12582912.0f);
+    const float2 t = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(t, minus_magic);
+    const float2 r = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(make_float2(0.05517098f, 0.05517098f), r, make_float2(0.24260943f, 0.24260943f));
+    p = __ffma2_rn(p, r, make_float2(0.69326097f, 0.69326097f));
+    p = __ffma2_rn(p, r, make_float2(0.99992818f, 0.99992818f));
+    return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t packed;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
@@ -368,10 +401,27 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 //     S_a(0), S_b(0);  then per tile j:  O_a += P_a V(j),  S_a(j+1),  O_b += P_b V(j),  S_b(j+1)
 // so that while group a turns S_a(j+1) into probabilities the pipe runs O_b(j) and S_b(j+1), and
 // the other way round.  Lazy rescaling, masking by position and page addressing as above.
+//
+// What bounds it (clock stamps of one CTA, 2,048 to 8,192 tokens): a tile of 128 keys of both heads
+// takes 3,700-3,900 cycles; its four products 2,580; each head's rows 35 for the load of the scores,
+// 315 for the maximum and 1,600 for the exponentials.  The special-function unit takes four lanes a
+// cycle per scheduler, so the 128 exponentials of a row are 1,024 cycles of its warp whatever else
+// is done (measured alone: 9.1 cycles per score with the sum and the packing); both heads' rows
+// share the four schedulers, which makes the softmax of a tile about 3,100 cycles of scheduler time
+// against 2,580 of the tensor pipe.  Tried from here and dropped: 2^x by a cubic on the multiply-add pipe
+// costs 10.5 cycles per score there (the two-wide float32 instructions issue at half rate), so
+// more than a quarter of the exponentials moved over is a loss (503 us at 8,192 tokens with a quarter,
+// 514 with none, 513 with half, 559 with three quarters); two threads per row halve a warp's
+// exponentials but not the unit's (514 us); steps of 64 keys with two score buffers per head, so
+// that rows never wait for a product, lost because a product of 64 keys takes the pipe as long as
+// one of 128 (648 us).
 constexpr int DUO_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-5 rows of head a, warps 6-9 rows of head b
 constexpr int DUO_TMEM_COLUMNS = 512;
 constexpr int DUO_TILE_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 bfloat16 tile as two 64-column halves
 constexpr int DUO_SMEM_BYTES = 6 * DUO_TILE_BYTES + 1024 + 256;
+#ifndef DUO_POLY
+#define DUO_POLY 1  // of every four pairs of exponentials, how many the multiply-add pipe computes
+#endif
 
 __global__ void __launch_bounds__(DUO_THREADS, 1)
 attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -577,7 +627,10 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
             }
             const float base = row_max == -INFINITY ? 0.0f : row_max;
-            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(-base, -base);
+            // exp2(score * scale - base) * CUT_GAIN.  DUO_POLY of every four pairs of exponentials go
+            // through the multiply-add pipe instead of the special-function unit, and the
+            // probabilities are cut to bfloat16 on the integer pipe.
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), base2 = make_float2(CUT_GAIN_LOG2 - base, CUT_GAIN_LOG2 - base);
             float2 partial[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -589,15 +642,15 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
                         const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
                         const float2 pr = make_float2(key <= row_pos ? fast_exp2(x.x) : 0.0f, key + 1 <= row_pos ? fast_exp2(x.y) : 0.0f);
                         partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
-                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                        packed[i / 2] = cut_bf16x2(pr.x, pr.y);
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw[c * 32 + i]), __uint_as_float(raw[c * 32 + i + 1])), scale2, base2);
-                        const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                        const float2 pr = ((i >> 1) % 4) < DUO_POLY ? poly_exp2_pair(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
                         partial[(i >> 1) & 1] = __fadd2_rn(partial[(i >> 1) & 1], pr);
-                        packed[i / 2] = pack_bf16x2(pr.x, pr.y);
+                        packed[i / 2] = cut_bf16x2(pr.x, pr.y);
                     }
                 }
                 // P columns [16 c, +16) hold keys [32 c, +32); this thread has read its whole row of S
@@ -612,7 +665,7 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (!ok && lane == 0) atomicCAS(&g_attention_error, 0, 13 << 8);
         if (ok) {
             tcgen05_fence_after();
-            const float inv = 1.0f / row_sum;
+            const float inv = CUT_GAIN / row_sum;
             __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + q_block * TC_ROWS + row) * p.heads + head0 + h) * TC_DIM;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
