@@ -10,7 +10,9 @@ prints ONE JSON line: ``value`` is decoded tokens per second on the device; ``e2
 same through ``LLMEngine.step`` (host token ids in, sampled ids out, scheduler and copies
 included); ``prefill`` times one 2,048-token prompt; ``roofline`` is the bytes a decode step
 must read (every weight once plus the live requests' cache) over its time, against the
-measured copy bandwidth; ``points`` adds decode at batch 1 and 64.
+measured copy bandwidth; ``points`` adds decode at batch 1 and 64; ``workloads`` the reference's
+own two end-to-end workloads at Qwen3-0.6B layer sizes (output tokens per second, wall time).
+``--impl reference`` measures all of it through the unmodified reference engine instead.
 
 Every step reads about 15 GB of weights, far more than the 126 MB L2, so no flush is needed
 between timed iterations (``config.l2`` says so).
@@ -36,6 +38,14 @@ QWEN3_8B = dict(
     num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
     max_position_embeddings=40960, tie_word_embeddings=False,
 )  # fmt: skip
+# BASELINE.json configs[3]: Qwen3-0.6B layer sizes, for the reference's own two end-to-end workloads.
+QWEN3_0P6B = dict(
+    vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+    num_attention_heads=16, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
+    max_position_embeddings=40960, tie_word_embeddings=True,
+)  # fmt: skip
+# Engine settings of those workloads (benchmarks/bench.py:113-123 of YuvGev00/mini-engine).
+WORKLOAD_ENGINE = dict(block_size=16, num_blocks=2048, max_num_seqs=64, max_num_batched_tokens=8192, max_model_len=2048)
 CONTEXT = 2048  # tokens each request holds when decode is timed
 REPEATS = 3  # the timed decode region is run this often; the median counts, the spread is printed
 PREFILL_TOKENS = 2048
@@ -110,6 +120,45 @@ class ClockSampler:
             "reasons": reasons,
             "samples": len(clocks),
         }
+
+
+def workload_prompts(vocab: int) -> tuple[list[list[int]], list[list[int]]]:
+    """Seeded synthetic prompts in the shapes of the reference's two workloads
+    (benchmarks/bench.py:52-62): 64 x 256 tokens; 64 x (512 shared + 32 own)."""
+    import random
+
+    rng = random.Random(0)
+
+    def ids(n: int) -> list[int]:
+        return [rng.randrange(100, vocab) for _ in range(n)]
+
+    shared = ids(512)
+    return [ids(256) for _ in range(64)], [shared + ids(32) for _ in range(64)]
+
+
+def run_workloads(make_engine, generate, synchronize) -> dict:
+    """Output tokens per second of the two workloads, wall time with prompts and scheduling
+    included, as the reference counts them (benchmarks/bench.py:18,267-277): 64 requests of 256 in
+    and 128 out; 64 requests of 512 shared + 32 in and 64 out, one first and then the other 63,
+    with the prefix cache on.  ``make_engine()`` builds a fresh engine, ``generate(engine, prompts,
+    max_tokens)`` returns the generated ids."""
+    throughput, prefix = workload_prompts(QWEN3_0P6B["vocab_size"])
+    generate(make_engine(), throughput[:4], 4)  # warm-up: kernels built, graphs captured once
+    out = {}
+    engine = make_engine()
+    synchronize()
+    began = time.perf_counter()
+    tokens = sum(len(o) for o in generate(engine, throughput, 128))
+    synchronize()
+    out["qwen3_0.6b_64x(256in,128out)_tok_s"] = round(tokens / (time.perf_counter() - began), 1)
+    engine = make_engine()
+    synchronize()
+    began = time.perf_counter()
+    tokens = sum(len(o) for o in generate(engine, prefix[:1], 64) + generate(engine, prefix[1:], 64))
+    synchronize()
+    out["qwen3_0.6b_64x(512shared+32in,64out)_tok_s"] = round(tokens / (time.perf_counter() - began), 1)
+    out["published_on_L4_tok_s"] = [1982.4, 1691.0]  # the reference's own numbers for these two, another GPU
+    return out
 
 
 def decode_bytes(cfg, layers: int, batch: int, context: int) -> float:
@@ -265,10 +314,22 @@ def run_ours(args) -> dict:
     if args.fp32_check:
         fp32_check = check_against_fp32(engine, cfg, random_prompt(args.fp32_check))
 
+    workloads = None
+    if not args.skip_workloads:
+        del engine, runner, graphs
+        torch.cuda.empty_cache()
+        small = Qwen3Config(**QWEN3_0P6B)
+        workloads = run_workloads(
+            lambda: LLMEngine.from_random(small, 0, EngineConfig(dtype=torch.bfloat16, **WORKLOAD_ENGINE)),
+            lambda engine, prompts, n: engine.generate(prompts, SamplingParams(max_tokens=n, ignore_eos=True)),
+            torch.cuda.synchronize,
+        )
+        device_error = device_error or tensor_core.take_error()
     return result_line(
         "ours", cfg, layers, full_layers, args, peaks, regions, e2e_value, h2d_bytes, d2h_bytes, prefill_ms, points,
         clock_summary, "captured CUDA graph per step + sampling kernel",
         gpu_launches=launches, device_error=device_error, **({"fp32_check": fp32_check} if fp32_check else {}),
+        **({"workloads": workloads} if workloads else {}),
     )  # fmt: skip
 
 
@@ -535,9 +596,36 @@ def run_reference(args) -> dict:
                 points[f"decode_b{batch}_error"] = str(error).splitlines()[0][:200]
                 torch.cuda.empty_cache()
 
+    workloads = None
+    if not args.skip_workloads:
+        del model
+        torch.cuda.empty_cache()
+        small = types.SimpleNamespace(**QWEN3_0P6B)
+        with torch.device("cuda"):
+            small_model = Qwen3ForCausalLM(ModelConfig(
+                vocab_size=small.vocab_size, hidden_size=small.hidden_size, intermediate_size=small.intermediate_size,
+                num_layers=small.num_hidden_layers, num_heads=small.num_attention_heads,
+                num_kv_heads=small.num_key_value_heads, head_dim=small.head_dim, rms_norm_eps=small.rms_norm_eps,
+                rope_theta=small.rope_theta, max_position_embeddings=small.max_position_embeddings,
+                tie_word_embeddings=small.tie_word_embeddings,
+            ))  # fmt: skip
+        with torch.no_grad():
+            for parameter in small_model.parameters():
+                if parameter.dim() == 2:
+                    parameter.normal_(0.0, 0.02)
+        small_model = small_model.to(dtype=torch.bfloat16)
+        try:
+            workloads = run_workloads(
+                lambda: LLMEngine(small_model, EngineConfig(device="cuda", dtype=torch.bfloat16, enable_prefix_caching=True,
+                                                            seed=0, cuda_graphs=True, **WORKLOAD_ENGINE)),
+                lambda engine, prompts, n: engine.generate(prompts, SamplingParams(max_tokens=n, ignore_eos=True)),
+                torch.cuda.synchronize,
+            )  # fmt: skip
+        except (RuntimeError, AssertionError) as error:
+            workloads = {"error": str(error).splitlines()[0][:200]}
     return result_line(
         "reference", cfg, layers, full_layers, args, peaks, regions, e2e_value, h2d_bytes, d2h_bytes, prefill_ms,
-        points, clock_summary, decode_path,
+        points, clock_summary, decode_path, **({"workloads": workloads} if workloads else {}),
     )  # fmt: skip
 
 
@@ -550,6 +638,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0: all)")
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--skip-points", action="store_true", help="do not time batch 1 and 64")
+    parser.add_argument("--skip-workloads", action="store_true", help="do not run the two Qwen3-0.6B end-to-end workloads")
     parser.add_argument("--fp32-check", type=int, default=0, metavar="TOKENS",
                         help="also run a prompt of this many tokens through the float32 path and compare logits")
     args = parser.parse_args()
