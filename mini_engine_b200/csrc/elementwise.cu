@@ -306,7 +306,7 @@ struct QkvArgs {
     const float* q_weight;  // [head_dim] or null: no norm
     const float* k_weight;
     float eps;
-    const float2* cos_sin;  // [tokens][head_dim / 2] (cos, sin) of each token's angles, or null: no rotation
+    const float2* cos_sin;  // [tokens][rotary_dim / 2] (cos, sin) of each token's angles, or null: no rotation
     const int* positions;
     const int* slot_mapping;  // null: dense outputs
     void* q_out;
@@ -315,6 +315,7 @@ struct QkvArgs {
     void* k_dense;
     void* v_dense;
     int tokens, heads, kv_heads, head_dim, page_size;
+    int rotary_dim;  // the first rotary_dim elements of a head are rotated (in halves of rotary_dim / 2), the rest pass through
 };
 
 constexpr int QKV_WARPS = 4;
@@ -329,7 +330,7 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     if (item >= static_cast<long long>(a.tokens) * heads_total) return;
     const int token = static_cast<int>(item / heads_total);
     const int column_head = static_cast<int>(item % heads_total);
-    const int d = a.head_dim, half = d / 2;
+    const int d = a.head_dim, half = a.rotary_dim / 2;
     float* vec = staged + warp * d;
     pdl_trigger();
     pdl_wait();
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     const float2* angles = a.cos_sin + static_cast<size_t>(token) * half;
     for (int i = lane; i < d; i += 32) {
         float value = weight ? weight[i] * (vec[i] * inv) : vec[i];
-        if (rotate) {
+        if (rotate && i < a.rotary_dim) {
             // rotate-half: out[i] = x[i] cos - x[i + half] sin (i < half); x[i] cos + x[i - half] sin.
             const int j = i < half ? i + half : i - half;
             const float other = weight ? weight[j] * (vec[j] * inv) : vec[j];
@@ -490,16 +491,18 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
                                     const float* k_weight, float eps, const float* cos_sin,
                                     const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
                                     void* v_pages, void* k_dense, void* v_dense, int out_type, int tokens,
-                                    int heads, int kv_heads, int head_dim, int page_size, cudaStream_t stream) {
+                                    int heads, int kv_heads, int head_dim, int page_size, int rotary_dim,
+                                    cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim > MAX_HEAD_DIM || head_dim % 2) return ME_ERR_UNSUPPORTED;
+    if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
     QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin), positions, slot_mapping,
-              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size};
+              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size, rotary_dim};
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
     const size_t smem = static_cast<size_t>(QKV_WARPS) * head_dim * sizeof(float);
     // The choice depends on the model's sizes and the engine's buffers only, never on the batch.
-    const bool vec = head_dim == 128 && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
+    const bool vec = head_dim == 128 && rotary_dim == head_dim && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
                      aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin);
     if (vec) {

@@ -253,26 +253,30 @@ def qk_norm_rope_store(
             raise KernelError("pages must be given in the dtype of q_out")
         if k_pages.shape[1:] != (kv_heads, page_size, head_dim):
             raise KernelError(f"pages {tuple(k_pages.shape)} do not fit kv_heads/page_size/head_dim")
-    if cos_sin is not None and tuple(cos_sin.shape) != (tokens, head_dim // 2, 2):
-        raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, head_dim / 2, 2]")
+    rotary_dim = head_dim
+    if cos_sin is not None:
+        # a rotation of the first rotary_dim <= head_dim elements of every head; the rest pass through
+        rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
+        if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= head_dim:
+            raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= head_dim")
     for w in (q_weight, k_weight, cos_sin):
         if w is not None:
             _need(w, torch.float32, "weight/table")
     fn = _fn(
         "elementwise",
         "me_qk_norm_rope_store",
-        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 6 + [c_void_p],
+        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 7 + [c_void_p],
     )
     code = fn(
         _ptr(qkv), splits, qkv.stride(0), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos_sin), _ptr(positions),
         _ptr(slot_mapping if kv_heads else None), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(k_dense),
-        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, _stream(),
+        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, rotary_dim, _stream(),
     )  # fmt: skip
     _check(code, "qk_norm_rope_store")
 
 
 def rope_table(inv_freq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t, i] = (cos, sin)(positions[t] * inv_freq[i])`` in float32, ``[T, head_dim / 2, 2]``."""
+    """``out[t, i] = (cos, sin)(positions[t] * inv_freq[i])`` in float32, ``[T, rotary_dim / 2, 2]``."""
     _need(inv_freq, torch.float32, "inv_freq"), _need(positions, torch.int32, "positions"), _need(out, torch.float32, "out")
     tokens, half = positions.shape[0], inv_freq.shape[0]
     if tuple(out.shape) != (tokens, half, 2):

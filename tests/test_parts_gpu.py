@@ -133,6 +133,48 @@ def test_attention_mixer_alone(window):
         start += n
 
 
+@pytest.mark.parametrize("head_dim,rotary_dim", [(16, 8), (128, 64), (48, 48)])
+def test_attention_mixer_with_a_partial_rotation(head_dim, rotary_dim):
+    """`rope` with `rotary_dim` < head_dim rotates the first rotary_dim elements of every head (in two
+    halves of rotary_dim / 2) and passes the rest through, inside the same fused kernel (norm,
+    rotation, cache write); a spec switches it on.  Whole == cut bitwise, equal to a plain restatement."""
+    from mini_engine_b200.config.model_spec import LayerSpec, PartSpec
+
+    sizes = dict(hidden=48, heads=4, kv_heads=2, head_dim=head_dim, inter=72)
+    base = one_layer_spec(**sizes)
+    layer = base.layers[0]
+    rope = PartSpec("rope", {"head_dim": head_dim, "theta": 777.0, "rotary_dim": rotary_dim})
+    mixer = PartSpec(layer.mixer.kind, {**layer.mixer.params, "position_encoding": rope})
+    spec = type(base)(**{**base.__dict__, "layers": (type(layer)(**{**layer.__dict__, "mixer": mixer}),)})
+    model, runner, manager, host = make_runner(spec)
+    tokens = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+
+    cfg = plain_cfg(**sizes)
+    t, eps = len(tokens), cfg["eps"]
+    positions = torch.arange(t)
+    p = "model.layers.0."
+    x = host["model.embed_tokens.weight"][torch.tensor(tokens)]
+    h = plain.rms_norm(x, host[p + "input_layernorm.weight"], eps)
+    q = plain.rms_norm((h @ host[p + "self_attn.q_proj.weight"].T).view(t, 4, head_dim), host[p + "self_attn.q_norm.weight"], eps)
+    k = plain.rms_norm((h @ host[p + "self_attn.k_proj.weight"].T).view(t, 2, head_dim), host[p + "self_attn.k_norm.weight"], eps)
+    v = (h @ host[p + "self_attn.v_proj.weight"].T).view(t, 2, head_dim)
+    cos, sin = plain.rope_angles(positions, rotary_dim, 777.0, torch.float32)
+
+    def partly_rotated(z):
+        return torch.cat((plain.apply_rope(z[..., :rotary_dim], cos, sin), z[..., rotary_dim:]), dim=-1)
+
+    attended = plain.causal_attention(partly_rotated(q), partly_rotated(k), v)
+    x = x + attended.reshape(t, -1) @ host[p + "self_attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, host[p + "post_attention_layernorm.weight"], eps), host, p + "mlp.")
+    want = plain.rms_norm(x, host["model.norm.weight"], eps) @ host["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=3e-5, rtol=1e-4)
+    if rotary_dim < head_dim:  # and the rotation of only a part is not the rotation of the whole
+        full = plain.rope_angles(positions, head_dim, 777.0, torch.float32)
+        assert not torch.allclose(partly_rotated(q), plain.apply_rope(q, *full), atol=1e-3)
+
+
 def test_feed_forward_alone():
     model, runner, manager, host = make_runner(one_layer_spec(**SIZES))
     ctx = context_for(runner, manager, [9])
