@@ -1,6 +1,6 @@
 """The reference's end-to-end workloads with seeded synthetic tokens and random weights.
 
-    python -m mini_engine_b200.cli.workloads [--size 0.6b|32b] [--layers N]
+    python -m mini_engine_b200.cli.workloads [--size 0.6b|8b|32b] [--layers N]
 
 Shapes follow benchmarks/bench.py:56-62,113-123 of YuvGev00/mini-engine (Qwen3-0.6B layer sizes;
 ``block_size 16, num_blocks 2048, max_num_seqs 64, max_num_batched_tokens 8192, max_model_len
@@ -16,6 +16,10 @@ workload instead: steps of 8 prompt portions of 512 tokens beside 32 single deco
 4,096-token contexts, device-timed through the step function (the decoding requests' pages hold
 random keys and values rather than computed ones); and the same mix through the scheduler with a
 page pool too small for all requests, so that it has to preempt.
+
+With ``--size 8b`` (Qwen3-8B layer sizes) it sweeps what ``bench.py`` measures at one point: one
+prompt of 128 to 16,384 tokens through the step function (eager launches, host included), and
+decode steps of a batch of 8 as captured graphs at contexts of 512 to 32,768 tokens.
 
 Token ids are uniform random from a fixed seed (the reference draws its prompts the same way,
 benchmarks/bench.py:52-53).
@@ -124,14 +128,76 @@ def mixed_32b(layers: int) -> int:
     return 0
 
 
+def sweep_8b(layers: int) -> int:
+    """Prompt lengths and decode context lengths at Qwen3-8B layer sizes."""
+    from mini_engine_b200 import EngineConfig, LLMEngine
+    from mini_engine_b200.config import Qwen3Config
+    from mini_engine_b200.engine.runner import StepEntry
+
+    cfg = Qwen3Config(
+        vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers,
+        num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
+        max_position_embeddings=40960, tie_word_embeddings=False,
+    )  # fmt: skip
+    batch, longest = 8, 32768
+    engine = LLMEngine.from_random(
+        cfg, 0,
+        EngineConfig(block_size=16, num_blocks=batch * (longest // 16 + 8) + 8, max_num_seqs=batch,
+                     max_num_batched_tokens=16384, max_model_len=longest + 64, enable_prefix_caching=False,
+                     dtype=torch.bfloat16),
+    )  # fmt: skip
+    runner, manager, graphs = engine.runner, engine.block_manager, engine.decode_graphs
+    rng = random.Random(0)
+
+    def ids(n: int) -> list[int]:
+        return [rng.randrange(100, cfg.vocab_size) for _ in range(n)]
+
+    def timed(function, repeats: int) -> float:
+        function()
+        torch.cuda.synchronize()
+        began = time.perf_counter()
+        for _ in range(repeats):
+            function()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - began) / repeats * 1e3
+
+    for tokens in (128, 512, 2048, 8192, 16384):
+        cache = manager.new_request()
+        assert manager.try_allocate(cache, tokens)
+        entry = StepEntry(cache, 0, ids(tokens), (tokens - 1,))
+        ms = timed(lambda: runner.execute([entry]), 3)
+        manager.free(cache)
+        print(json.dumps({"prompt_tokens": tokens, "ms": round(ms, 2), "tokens_per_second": round(tokens / ms * 1e3)}), flush=True)
+    weights = layers * (6144 * 4096 + 4096 * 4096 + 3 * 4096 * 12288) * 2 + cfg.vocab_size * 4096 * 2
+    for array in runner.layout.arrays:
+        array.normal_()  # contexts of random keys and values: only the time of a decode step is looked at
+    caches = [manager.new_request() for _ in range(batch)]
+    for context in (512, 2048, 8192, 32768):
+        for cache in caches:
+            assert manager.try_allocate(cache, context + 40)
+        position = [context]
+
+        def step() -> None:
+            graphs.run([StepEntry(c, position[0], [7], (0,)) for c in caches])
+            position[0] += 1
+
+        ms = timed(step, 20)
+        read = weights + batch * context * 2 * layers * 8 * 128 * 2
+        print(json.dumps({"decode_batch": batch, "context": context, "ms_per_step": round(ms, 3),
+                          "tokens_per_second": round(batch / ms * 1e3), "terabytes_per_second": round(read / ms / 1e9, 2)}), flush=True)  # fmt: skip
+    return 0
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--size", choices=["0.6b", "32b"], default="0.6b")
+    parser.add_argument("--size", choices=["0.6b", "8b", "32b"], default="0.6b")
     parser.add_argument("--layers", type=int, default=0, help="0: all layers of the size (28 or 64)")
     parser.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
     args = parser.parse_args(argv)
     if args.size == "32b":
         return mixed_32b(args.layers or 64)
+    if args.size == "8b":
+        return sweep_8b(args.layers or 36)
     args.layers = args.layers or 28
 
     from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams

@@ -20,8 +20,14 @@ from mini_engine_b200.engine.runner import ModelRunner, StepEntry
 
 
 def batch_buckets(max_batch: int) -> list[int]:
-    small = [b for b in (1, 2, 4, 8) if b < max_batch]
-    return small + list(range(16, max_batch, 16)) + [max_batch]
+    """Batch sizes that get a graph of their own: 1, 2, 4, 8, the multiples of 16, and the cap
+    itself, so that no batch is padded by more than its own size or 15 rows."""
+    sizes = {max_batch}
+    size = 1
+    while size < max_batch:
+        sizes.add(size)
+        size = size * 2 if size < 16 else size + 16
+    return sorted(sizes)
 
 
 class DecodeGraphs:
