@@ -12,7 +12,8 @@ included); ``prefill`` times one 2,048-token prompt; ``roofline`` is the bytes a
 must read (every weight once plus the live requests' cache) over its time, against the
 measured copy bandwidth; ``points`` adds decode at batch 1 and 64; ``workloads`` the reference's
 own two end-to-end workloads at Qwen3-0.6B layer sizes (output tokens per second, wall time).
-``--impl reference`` measures all of it through the unmodified reference engine instead.
+``fp32_check`` compares the bfloat16 logits of a 256-token prompt with the true 32-bit path of the
+same full-size model.  ``--impl reference`` measures through the unmodified reference engine instead.
 
 Every step reads about 15 GB of weights, far more than the 126 MB L2, so no flush is needed
 between timed iterations (``config.l2`` says so).
@@ -639,8 +640,9 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--skip-points", action="store_true", help="do not time batch 1 and 64")
     parser.add_argument("--skip-workloads", action="store_true", help="do not run the two Qwen3-0.6B end-to-end workloads")
-    parser.add_argument("--fp32-check", type=int, default=0, metavar="TOKENS",
-                        help="also run a prompt of this many tokens through the float32 path and compare logits")
+    parser.add_argument("--fp32-check", type=int, default=256, metavar="TOKENS",
+                        help="also run a prompt of this many tokens through the true 32-bit path of the same model and "
+                             "compare the bfloat16 logits with it (0: skip; needs 33 GB more device memory for a second)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
