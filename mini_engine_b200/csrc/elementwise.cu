@@ -316,6 +316,7 @@ struct QkvArgs {
     void* v_dense;
     int tokens, heads, kv_heads, head_dim, page_size;
     int rotary_dim;  // the first rotary_dim elements of a head are rotated (in halves of rotary_dim / 2), the rest pass through
+    const float* bias;  // [(heads + 2 kv_heads) * head_dim] added to the projections' sums, or null
 };
 
 constexpr int QKV_WARPS = 4;
@@ -341,6 +342,7 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_kernel(QkvA
     for (int i = lane; i < d; i += 32) {
         float v = 0.0f;
         for (int s = 0; s < a.splits; ++s) v += src[s * a.split_stride + i];
+        if (a.bias) v += a.bias[static_cast<size_t>(column_head) * d + i];
         vec[i] = v;
         sum_sq = fmaf(v, v, sum_sq);
     }
@@ -427,6 +429,10 @@ __global__ void __launch_bounds__(QKV_WARPS * 32) qk_norm_rope_store_128_kernel(
 #pragma unroll
         for (int s = 0; s < MAX_SPLITS; ++s)
             if (s < a.splits) { v.x += part[u][s].x; v.y += part[u][s].y; v.z += part[u][s].z; v.w += part[u][s].w; }
+        if (a.bias) {
+            const float4 b = *reinterpret_cast<const float4*>(a.bias + static_cast<size_t>(column_head) * D + lane * 4);
+            v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+        }
         const bool is_q = column_head < a.heads;
         const bool is_k = !is_q && column_head < a.heads + a.kv_heads;
         const float* weight = is_q ? a.q_weight : (is_k ? a.k_weight : nullptr);
@@ -492,19 +498,19 @@ ME_EXPORT int me_qk_norm_rope_store(const float* qkv, int splits, long long spli
                                     const int* positions, const int* slot_mapping, void* q_out, void* k_pages,
                                     void* v_pages, void* k_dense, void* v_dense, int out_type, int tokens,
                                     int heads, int kv_heads, int head_dim, int page_size, int rotary_dim,
-                                    cudaStream_t stream) {
+                                    const float* bias, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (head_dim > MAX_HEAD_DIM || head_dim % 2) return ME_ERR_UNSUPPORTED;
     if (rotary_dim < 0 || rotary_dim > head_dim || rotary_dim % 2) return ME_ERR_ARGUMENT;
     QkvArgs a{qkv, splits, (size_t)split_stride, q_weight, k_weight, eps, reinterpret_cast<const float2*>(cos_sin), positions, slot_mapping,
-              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size, rotary_dim};
+              q_out, k_pages, v_pages, k_dense, v_dense, tokens, heads, kv_heads, head_dim, page_size, rotary_dim, bias};
     const long long items = static_cast<long long>(tokens) * (heads + 2 * kv_heads);
     const int blocks = static_cast<int>((items + QKV_WARPS - 1) / QKV_WARPS);
     const size_t smem = static_cast<size_t>(QKV_WARPS) * head_dim * sizeof(float);
     // The choice depends on the model's sizes and the engine's buffers only, never on the batch.
     const bool vec = head_dim == 128 && rotary_dim == head_dim && splits <= MAX_UNROLLED_SPLITS && split_stride % 4 == 0 && aligned16(qkv) &&
                      aligned16(q_out) && aligned16(k_pages) && aligned16(v_pages) && aligned16(k_dense) &&
-                     aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin);
+                     aligned16(v_dense) && aligned16(q_weight) && aligned16(k_weight) && aligned16(cos_sin) && aligned16(bias);
     if (vec) {
         // The number of heads per warp depends on the number of partial sums and on the model's
         // head counts only, never on the batch.

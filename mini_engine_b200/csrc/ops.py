@@ -237,10 +237,12 @@ def qk_norm_rope_store(
     v_pages: torch.Tensor | None = None,
     k_dense: torch.Tensor | None = None,
     v_dense: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
 ) -> None:
     """Per-head RMSNorm of q and k, rotation, and the write of k and v to their cache slots
     (or to dense ``[T, kv_heads * head_dim]`` buffers when ``slot_mapping`` is ``None``).
-    ``qkv`` is ``[S, T, (heads + 2 * kv_heads) * head_dim]`` float32 partial sums."""
+    ``qkv`` is ``[S, T, (heads + 2 * kv_heads) * head_dim]`` float32 partial sums; ``bias`` (float32,
+    one value per column of ``qkv``) is added to their sum before anything else."""
     _need(qkv, torch.float32, "qkv"), _need(q_out, None, "q_out"), _need(positions, torch.int32, "positions")
     splits, tokens, width = qkv.shape
     if width != (heads + 2 * kv_heads) * head_dim:
@@ -259,18 +261,20 @@ def qk_norm_rope_store(
         rotary_dim = 2 * cos_sin.shape[1] if cos_sin.dim() == 3 else -1
         if cos_sin.dim() != 3 or cos_sin.shape[0] != tokens or cos_sin.shape[2] != 2 or not 2 <= rotary_dim <= head_dim:
             raise KernelError(f"cos_sin {tuple(cos_sin.shape)} is not [tokens, rotary_dim / 2, 2] with rotary_dim <= head_dim")
-    for w in (q_weight, k_weight, cos_sin):
+    for w in (q_weight, k_weight, cos_sin, bias):
         if w is not None:
             _need(w, torch.float32, "weight/table")
+    if bias is not None and bias.shape != (width,):
+        raise KernelError(f"bias {tuple(bias.shape)} does not fit the {width} columns of qkv")
     fn = _fn(
         "elementwise",
         "me_qk_norm_rope_store",
-        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 7 + [c_void_p],
+        [c_void_p, c_int, c_longlong] + [c_void_p] * 2 + [c_float] + [c_void_p] * 8 + [c_int] * 7 + [c_void_p, c_void_p],
     )
     code = fn(
         _ptr(qkv), splits, qkv.stride(0), _ptr(q_weight), _ptr(k_weight), eps, _ptr(cos_sin), _ptr(positions),
         _ptr(slot_mapping if kv_heads else None), _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _ptr(k_dense),
-        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, rotary_dim, _stream(),
+        _ptr(v_dense), _type_code(q_out.dtype), tokens, heads, kv_heads, head_dim, page_size, rotary_dim, _ptr(bias), _stream(),
     )  # fmt: skip
     _check(code, "qk_norm_rope_store")
 

@@ -48,6 +48,7 @@ class GroupedQueryAttention(Mixer):
         window: int | None = None,
         scale: float | None = None,
         reads_shared_cache: bool = False,
+        qkv_bias: bool = False,
         names: Mapping[str, str] | None = None,
     ):
         if num_heads % kv_heads:
@@ -58,6 +59,7 @@ class GroupedQueryAttention(Mixer):
         self.window = window
         self.scale = float(scale) if scale is not None else head_dim**-0.5
         self.reads_shared_cache = reads_shared_cache
+        self.qkv_bias = qkv_bias  # the reference's projections have none (src/mini_engine/model.py:97-100)
         defaults = {
             "q": "q_proj.weight",
             "k": "k_proj.weight",
@@ -65,6 +67,9 @@ class GroupedQueryAttention(Mixer):
             "o": "o_proj.weight",
             "q_norm": "q_norm.weight",
             "k_norm": "k_norm.weight",
+            "q_bias": "q_proj.bias",
+            "k_bias": "k_proj.bias",
+            "v_bias": "v_proj.bias",
         }
         self.names = {key: prefix + (names or {}).get(key, value) for key, value in defaults.items()}
         self.position = build_part("position_encoding", position_encoding, prefix, hidden_size)
@@ -72,6 +77,7 @@ class GroupedQueryAttention(Mixer):
         self.out: Linear | None = None
         self.q_norm: torch.Tensor | None = None
         self.k_norm: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ declarations
 
@@ -91,6 +97,11 @@ class GroupedQueryAttention(Mixer):
             specs.append(WeightSpec(n["q_norm"], (d,), role="vector", init="ones_normal"))
             if not self.reads_shared_cache:
                 specs.append(WeightSpec(n["k_norm"], (d,), role="vector", init="ones_normal"))
+        if self.qkv_bias:
+            specs.append(WeightSpec(n["q_bias"], (self.heads * d,), role="vector"))
+            if not self.reads_shared_cache:
+                specs.append(WeightSpec(n["k_bias"], (self.kv_heads * d,), role="vector"))
+                specs.append(WeightSpec(n["v_bias"], (self.kv_heads * d,), role="vector"))
         return specs + self.position.weight_specs()
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -103,6 +114,11 @@ class GroupedQueryAttention(Mixer):
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[n["q_norm"]]
             self.k_norm = None if self.reads_shared_cache else tensors[n["k_norm"]]
+        if self.qkv_bias:
+            parts = [tensors[n["q_bias"]]]
+            if not self.reads_shared_cache:
+                parts += [tensors[n["k_bias"]], tensors[n["v_bias"]]]
+            self.bias = torch.cat(parts).contiguous()
         self.position.load(tensors)
 
     # ------------------------------------------------------------------------ step
@@ -117,7 +133,7 @@ class GroupedQueryAttention(Mixer):
         args: dict[str, Any] = dict(
             qkv=qkv, heads=self.heads, kv_heads=kv_in, head_dim=d, q_weight=self.q_norm,
             k_weight=self.k_norm, eps=self.qk_norm_eps or 0.0, positions=ctx.positions, q_out=q,
-            page_size=ctx.page_size,
+            page_size=ctx.page_size, bias=self.bias,
         )  # fmt: skip
         if kv_in and not cache.writes:
             # This execution reads another entry's cache: its own keys and values are not kept.

@@ -64,7 +64,7 @@ class LinearHead(Head):
     def weight_specs(self) -> list[WeightSpec]:
         specs = [WeightSpec(self.weight_name, (self.vocab, self.hidden), alias_of=self.tied_to)]
         if self.bias_name:
-            specs.append(WeightSpec(self.bias_name, (self.vocab,), role="vector", init="ones_normal"))
+            specs.append(WeightSpec(self.bias_name, (self.vocab,), role="vector"))
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:

@@ -175,6 +175,48 @@ def test_attention_mixer_with_a_partial_rotation(head_dim, rotary_dim):
         assert not torch.allclose(partly_rotated(q), plain.apply_rope(q, *full), atol=1e-3)
 
 
+@pytest.mark.parametrize("head_dim,qk_norm", [(16, False), (128, False), (128, True)])
+def test_attention_mixer_with_projection_biases(head_dim, qk_norm):
+    """`qkv_bias` adds a bias to the q, k and v projections (and `qk_norm_eps=None` drops the per-head
+    norms): the attention of models that have biases instead of q/k norms, by spec alone.  The bias
+    is added inside the fused kernel, to the sum of the product's partial sums."""
+    from mini_engine_b200.config.model_spec import PartSpec
+
+    sizes = dict(hidden=48, heads=4, kv_heads=2, head_dim=head_dim, inter=72)
+    base = one_layer_spec(**sizes)
+    layer = base.layers[0]
+    names = {**layer.mixer.params["names"], "q_bias": "self_attn.q_proj.bias", "k_bias": "self_attn.k_proj.bias",
+             "v_bias": "self_attn.v_proj.bias"}  # fmt: skip
+    params = {**layer.mixer.params, "qkv_bias": True, "names": names}
+    if not qk_norm:
+        params["qk_norm_eps"] = None
+    spec = type(base)(**{**base.__dict__, "layers": (type(layer)(**{**layer.__dict__, "mixer": PartSpec(layer.mixer.kind, params)}),)})
+    model, runner, manager, host = make_runner(spec)
+    p = "model.layers.0."
+    assert (p + "self_attn.q_norm.weight" in host) == qk_norm and host[p + "self_attn.k_proj.bias"].shape == (2 * head_dim,)
+    tokens = [3, 14, 15, 9, 2, 6, 5, 35, 8, 9, 7, 9, 3]
+    whole, cut = run_whole_and_cut(runner, manager, tokens)
+    assert torch.equal(whole, cut)
+
+    cfg = plain_cfg(**sizes)
+    t, eps = len(tokens), cfg["eps"]
+    x = host["model.embed_tokens.weight"][torch.tensor(tokens)]
+    h = plain.rms_norm(x, host[p + "input_layernorm.weight"], eps)
+    q = (h @ host[p + "self_attn.q_proj.weight"].T + host[p + "self_attn.q_proj.bias"]).view(t, 4, head_dim)
+    k = (h @ host[p + "self_attn.k_proj.weight"].T + host[p + "self_attn.k_proj.bias"]).view(t, 2, head_dim)
+    v = (h @ host[p + "self_attn.v_proj.weight"].T + host[p + "self_attn.v_proj.bias"]).view(t, 2, head_dim)
+    if qk_norm:
+        q = plain.rms_norm(q, host[p + "self_attn.q_norm.weight"], eps)
+        k = plain.rms_norm(k, host[p + "self_attn.k_norm.weight"], eps)
+    cos, sin = plain.rope_angles(torch.arange(t), head_dim, 777.0, torch.float32)
+    attended = plain.causal_attention(plain.apply_rope(q, cos, sin), plain.apply_rope(k, cos, sin), v)
+    x = x + attended.reshape(t, -1) @ host[p + "self_attn.o_proj.weight"].T
+    x = x + plain.swiglu_mlp(plain.rms_norm(x, host[p + "post_attention_layernorm.weight"], eps), host, p + "mlp.")
+    want = plain.rms_norm(x, host["model.norm.weight"], eps) @ host["lm_head.weight"].T
+    assert torch.allclose(whole, want, atol=3e-5, rtol=1e-4)
+    assert float(host[p + "self_attn.v_proj.bias"].abs().max()) > 0.01  # the biases are not negligible
+
+
 def test_feed_forward_alone():
     model, runner, manager, host = make_runner(one_layer_spec(**SIZES))
     ctx = context_for(runner, manager, [9])
@@ -646,7 +688,7 @@ def test_embedding_multiplier_and_a_head_with_bias_scale_and_cap():
         **base.__dict__,
         "embedding": PartSpec("token_embedding", {"weight": "model.embed_tokens.weight", "multiplier": 48**0.5}),
         "head": PartSpec("linear_head", {"weight": "lm_head.weight", "tied_to": "model.embed_tokens.weight",
-                                         "bias": "lm_head.bias", "logit_scale": 0.25, "soft_cap": 3.0}),
+                                         "bias": "lm_head.bias", "logit_scale": 1.5, "soft_cap": 3.0}),
     })  # fmt: skip
     model, runner, manager, host = make_runner(spec, scale=2.0)
     assert "lm_head.bias" in host and "lm_head.weight" not in host  # tied: one tensor; the bias is the head's own
@@ -658,9 +700,9 @@ def test_embedding_multiplier_and_a_head_with_bias_scale_and_cap():
     for index in range(2):
         x = plain.decoder_layer(x, host, index, cfg, torch.arange(len(tokens)))
     x = plain.rms_norm(x, host["model.norm.weight"], cfg["eps"])
-    logits = (x @ host["model.embed_tokens.weight"].T) * 0.25 + host["lm_head.bias"]
+    logits = (x @ host["model.embed_tokens.weight"].T) * 1.5 + host["lm_head.bias"]
     want = 3.0 * torch.tanh(logits / 3.0)
-    assert float(want.abs().max()) > 1.5  # the cap bends the largest logits
+    assert float(logits.abs().max()) > 2.5 and float((logits - want).abs().max()) > 0.3  # the cap bends the largest logits
     assert torch.allclose(whole, want, atol=3e-5, rtol=1e-4)
 
 
