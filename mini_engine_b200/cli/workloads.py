@@ -161,13 +161,18 @@ def sweep_8b(layers: int) -> int:
         torch.cuda.synchronize()
         return (time.perf_counter() - began) / repeats * 1e3
 
-    for tokens in (128, 512, 2048, 8192, 16384):
+    for tokens in (32, 60, 100, 127, 128, 512, 2048, 8192, 16384):
         cache = manager.new_request()
         assert manager.try_allocate(cache, tokens)
         entry = StepEntry(cache, 0, ids(tokens), (tokens - 1,))
         ms = timed(lambda: runner.execute([entry]), 3)
+        row = {"prompt_tokens": tokens, "ms": round(ms, 2), "tokens_per_second": round(tokens / ms * 1e3)}
+        if engine.prompt_graphs is not None and engine.prompt_graphs.bucket_for(tokens):
+            # what LLMEngine.step does with a prompt that is alone in its step: the graph of its bucket
+            row["ms_as_captured_graph"] = round(timed(lambda: engine.prompt_graphs.run(entry), 5), 2)
+            row["bucket"] = engine.prompt_graphs.bucket_for(tokens)
         manager.free(cache)
-        print(json.dumps({"prompt_tokens": tokens, "ms": round(ms, 2), "tokens_per_second": round(tokens / ms * 1e3)}), flush=True)
+        print(json.dumps(row), flush=True)
     weights = layers * (6144 * 4096 + 4096 * 4096 + 3 * 4096 * 12288) * 2 + cfg.vocab_size * 4096 * 2
     for array in runner.layout.arrays:
         array.normal_()  # contexts of random keys and values: only the time of a decode step is looked at

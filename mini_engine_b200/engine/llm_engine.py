@@ -19,7 +19,7 @@ from mini_engine_b200.cache.manager import CacheManager
 from mini_engine_b200.cache.storage import blocks_for_budget
 from mini_engine_b200.config.engine_config import EngineConfig
 from mini_engine_b200.csrc import ops
-from mini_engine_b200.engine.graphs import DecodeGraphs
+from mini_engine_b200.engine.graphs import PROMPT_BUCKETS, DecodeGraphs, PromptGraphs
 from mini_engine_b200.engine.loading import load_model, random_model
 from mini_engine_b200.engine.runner import ModelRunner, Prepacked
 from mini_engine_b200.engine.scheduler import ScheduledSeq, Scheduler, SchedulerConfig
@@ -38,7 +38,8 @@ class EngineStats:
     prompt_tokens: int = 0  # hits of the prefix cache are counted in scheduler.num_cached_tokens
     computed_tokens: int = 0  # tokens actually run through the model
     generated_tokens: int = 0
-    graph_steps: int = 0  # steps that replayed a captured graph
+    graph_steps: int = 0  # decode steps that replayed a captured graph
+    prompt_graph_steps: int = 0  # steps of one short prompt that replayed a captured graph
     prepacked_steps: int = 0  # of those, steps that were launched while the step before ran
     dropped_steps: int = 0  # steps launched ahead that turned out not to be the next step
     step_batch_sizes: list[int] = field(default_factory=list)
@@ -68,14 +69,19 @@ class LLMEngine:
             config = dataclasses.replace(config, num_blocks=blocks)
         self.config = config
         self.model = model
+        capacity = config.max_num_batched_tokens
+        if config.cuda_graphs and model.capturable:
+            # room for the bucket that a portion as long as the token budget replays (one token more at least)
+            capacity = max(capacity, min((b for b in PROMPT_BUCKETS if b > capacity), default=capacity))
         self.runner = ModelRunner(
             model,
             dtype=config.dtype,
             num_blocks=config.num_blocks,
             block_size=config.block_size,
             max_num_seqs=config.max_num_seqs,
-            max_num_batched_tokens=config.max_num_batched_tokens,
+            max_num_batched_tokens=capacity,
             max_model_len=config.max_model_len,
+            max_request_tokens=config.max_num_batched_tokens,
         )
         self.block_manager = CacheManager(
             self.runner.layout.groups,
@@ -99,8 +105,11 @@ class LLMEngine:
         self._rows_host = torch.empty((2, max(config.max_num_seqs, 1)), dtype=torch.int32).pin_memory()
         self._rows = torch.empty(max(config.max_num_seqs, 1), dtype=torch.int32, device="cuda")
         self.decode_graphs: DecodeGraphs | None = None
+        self.prompt_graphs: PromptGraphs | None = None
         if config.cuda_graphs:
             self.decode_graphs = DecodeGraphs(self.runner, config.max_num_seqs)
+            if model.capturable:  # steps of one short prompt replay a graph too (captured at first use)
+                self.prompt_graphs = PromptGraphs(self.runner)
 
     # ----------------------------------------------------------------- loading
 
@@ -163,7 +172,10 @@ class LLMEngine:
             self.stats.prepacked_steps += 1
         else:
             graph_step = self._graph_fits(batch)
-            logits = self.decode_graphs.run(entries) if graph_step else self.runner.execute(entries)
+            if graph_step:
+                logits = self.decode_graphs.run(entries)
+            else:
+                logits = self._run_prompt_step(batch, entries)
             draw = self._draw(batch, logits, 0)
         if graph_step:
             self.stats.graph_steps += 1
@@ -200,6 +212,16 @@ class LLMEngine:
             [seq.seq_id for seq in sampling],
             [seq.num_output_tokens + ahead for seq in sampling],
         )
+
+    def _run_prompt_step(self, batch: list[ScheduledSeq], entries) -> torch.Tensor:
+        """A step that is no pure decode step: eagerly, or, when it is one short prompt or portion
+        alone, through the captured graph of its token-count bucket."""
+        if self.prompt_graphs is not None and len(entries) == 1:
+            logits = self.prompt_graphs.run(entries[0])
+            if logits is not None:
+                self.stats.prompt_graph_steps += 1
+                return logits if batch[0].samples else logits[:0]
+        return self.runner.execute(entries)
 
     def _graph_fits(self, batch: list[ScheduledSeq]) -> bool:
         graphs = self.decode_graphs

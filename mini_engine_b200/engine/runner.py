@@ -62,7 +62,10 @@ class ModelRunner:
         max_num_batched_tokens: int,
         max_model_len: int,
         device: str = "cuda",
+        max_request_tokens: int | None = None,
     ):
+        """``max_request_tokens``: the most tokens that ONE request brings to a step (the scheduler's
+        budget), where that is less than the step's capacity; it sizes the pools of groups with a window."""
         if not torch.cuda.is_available():
             raise RuntimeError("mini_engine_b200 runs on a CUDA device only; none is available")
         self.model = model
@@ -76,7 +79,7 @@ class ModelRunner:
         self.vocab_size = model.spec.vocab_size
         self.layout: CacheLayout = allocate_cache(
             model.cache_needs(), num_blocks, block_size, max_num_seqs, dtype, self.device,
-            max_step_tokens=max_num_batched_tokens,
+            max_step_tokens=max_request_tokens or max_num_batched_tokens,
         )  # fmt: skip
         self.num_groups = len(self.layout.groups)
         self.workspace = Workspace(max_num_batched_tokens, self.device)

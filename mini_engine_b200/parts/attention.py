@@ -35,6 +35,8 @@ from mini_engine_b200.weights.loader import WeightSpec
 
 @register("mixer", "gqa_attention")
 class GroupedQueryAttention(Mixer):
+    capturable = True
+
     def __init__(
         self,
         prefix: str,

@@ -135,6 +135,11 @@ class StepContext:
 class Part:
     """Common to all parts: declared weights and their arrival."""
 
+    # Whether the part's launches depend on the batch through device arrays and the token count
+    # alone, so that a step of a fixed token count can be captured in a CUDA graph and replayed for
+    # other requests (a part whose Python reads ``ctx.host`` or branches on values must say False).
+    capturable = False
+
     def weight_specs(self) -> list[WeightSpec]:
         return []
 

@@ -12,6 +12,8 @@ class PreNormBlock(Block):
     the norms that follow them (the last one inside the next layer's first norm or the
     model's final norm), in 32-bit."""
 
+    capturable = True
+
     def forward(self, state: Residual, ctx: StepContext, cache: LayerCache) -> None:
         h = self.mixer_norm.forward(state, ctx, ctx.dtype)
         state.add(self.mixer.forward(h, ctx, cache))

@@ -23,6 +23,8 @@ from mini_engine_b200.weights.loader import WeightSpec
 
 @register("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
+    capturable = True
+
     def __init__(self, vocab_size: int, hidden_size: int, *, weight: str, multiplier: float | None = None):
         self.vocab, self.hidden = vocab_size, hidden_size
         self.weight_name = weight
@@ -41,6 +43,8 @@ class TokenEmbedding(Embedding):
 
 @register("head", "linear_head")
 class LinearHead(Head):
+    capturable = True
+
     def __init__(
         self,
         vocab_size: int,

@@ -19,6 +19,8 @@ from mini_engine_b200.weights.loader import WeightSpec
 
 @register("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
+    capturable = True
+
     def __init__(
         self,
         prefix: str,

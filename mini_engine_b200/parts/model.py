@@ -64,6 +64,18 @@ class DecoderModel:
         specs += self.head.weight_specs()
         return specs
 
+    @property
+    def capturable(self) -> bool:
+        """Whether every part of the model says that a step of a fixed token count may be captured
+        in a CUDA graph (see ``Part.capturable``)."""
+        parts = [self.embedding, self.final_norm, self.head]
+        for blk in self.blocks:
+            parts += [blk, *blk.parts()]
+            position = getattr(blk.mixer, "position", None)
+            if position is not None:
+                parts.append(position)
+        return all(getattr(part, "capturable", False) for part in parts)
+
     def cache_needs(self) -> list[tuple[PagedCacheSpec | None, StateSpec | None, int | None]]:
         """For every entry of the execution order: its per-token need, its per-request
         need, and the earlier entry whose cache it reads instead (or ``None``)."""

@@ -20,6 +20,8 @@ from mini_engine_b200.weights.loader import WeightSpec
 
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, prefix: str, hidden_size: int, *, name: str, eps: float, dim: int | None = None):
         self.weight_name = prefix + name
         self.dim = dim or hidden_size

@@ -18,6 +18,8 @@ from mini_engine_b200.parts.base import PositionEncoding, register
 
 @register("position_encoding", "rope")
 class RotaryEncoding(PositionEncoding):
+    capturable = True
+
     def __init__(self, prefix: str, hidden_size: int, *, head_dim: int, theta: float, rotary_dim: int | None = None):
         """``rotary_dim`` (default: all of ``head_dim``) is how many leading elements of a head are
         rotated, in two halves of ``rotary_dim / 2``; the rest of the head passes through.  The
@@ -52,6 +54,8 @@ class RotaryEncoding(PositionEncoding):
 @register("position_encoding", "none")
 class NoEncoding(PositionEncoding):
     """Queries and keys are used as projected (and normalised)."""
+
+    capturable = True
 
     def __init__(self, prefix: str, hidden_size: int):
         pass

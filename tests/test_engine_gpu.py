@@ -448,6 +448,59 @@ def test_random_weights_in_memory_equal_those_of_a_written_folder(dtype, tmp_pat
     assert float(logits[0].abs().max()) > 0
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_a_short_prompt_alone_replays_a_graph_with_the_eager_bits(name, model_folders):
+    """A step that holds one short prompt (or one portion of a longer one) replays a graph of its
+    token-count bucket, padded with a dummy entry on the spare page.  In float32 its logits are
+    bit for bit those of the eager step, whatever the length, the position it starts at and what
+    the graph's buffers held before; a prompt too long for the buckets runs eagerly."""
+    from mini_engine_b200.engine.runner import StepEntry
+
+    folder = model_folders[name]
+    _, cfg = load_plain(folder)
+    engine = engine_for(folder, name, max_model_len=512, num_blocks=96, max_num_batched_tokens=512)
+    manager, runner, graphs = engine.block_manager, engine.runner, engine.prompt_graphs
+    assert graphs is not None and graphs.buckets == [32, 64, 96, 128]
+    assert graphs.bucket_for(1) is None and graphs.bucket_for(31) == 32 and graphs.bucket_for(32) == 64
+    assert graphs.bucket_for(100) == 128 and graphs.bucket_for(127) == 128 and graphs.bucket_for(128) is None
+    for i, (start, count) in enumerate([(0, 100), (0, 2), (0, 31), (0, 32), (40, 90), (0, 127), (7, 5), (100, 64)]):
+        tokens = random_ids(1900 + i, start + count, cfg["vocab"])
+        cache = manager.new_request()
+        assert manager.try_allocate(cache, start + count)
+        if start:
+            runner.execute([StepEntry(cache, 0, tokens[:start], ())])
+        entry = StepEntry(cache, start, tokens[start:], (count - 1,))
+        eager = runner.execute([entry]).clone()
+        replayed = graphs.run(entry).clone()  # writes the same keys and values again
+        assert torch.equal(eager, replayed), f"start {start}, {count} tokens: the graph's logits differ from the eager step's"
+        manager.free(cache)
+    assert sorted(graphs.graphs) == [32, 64, 96, 128]
+    manager.check_invariants([])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["float32", "bfloat16"])
+def test_short_prompts_through_the_engine_use_their_graphs(dtype, peaked_model_folders):
+    """Requests that arrive one at a time: each prompt is a step of its own and replays a graph;
+    portions under a small budget do too; the tokens follow the plain implementation."""
+    from mini_engine_b200 import SamplingParams
+
+    folder = peaked_model_folders["D"]
+    _, cfg = load_plain(folder)
+    prompts = [random_ids(2000 + i, n, cfg["vocab"]) for i, n in enumerate((17, 90, 2, 140, 33))]
+    params = SamplingParams(max_tokens=6)
+    engine = engine_for(folder, "D", dtype=dtype, num_blocks=64)
+    outputs = [engine.generate([p], params)[0] for p in prompts]
+    assert engine.stats.prompt_graph_steps == len(prompts) - 1  # the prompt of 140 tokens runs eagerly
+    assert_follows_plain(folder, dtype, prompts, outputs)
+    cut = engine_for(folder, "D", dtype=dtype, num_blocks=64, max_num_batched_tokens=48, enable_prefix_caching=False)
+    outputs = [cut.generate([p], params)[0] for p in prompts]
+    # portions of 48 tokens replay the graph of 64: 17 and 2 whole, 90 as 48 + 42, 140 as 48 + 48 + 44, 33 whole
+    assert cut.stats.prompt_graph_steps == 1 + 2 + 1 + 3 + 1
+    assert_follows_plain(folder, dtype, prompts, outputs)
+    without = engine_for(folder, "D", dtype=dtype, num_blocks=64, cuda_graphs=False)
+    assert without.prompt_graphs is None and without.generate([prompts[1]], params)[0] == outputs[1]
+
+
 def test_command_line(peaked_model_folders):
     import subprocess
     import sys
