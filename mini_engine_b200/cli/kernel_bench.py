@@ -62,7 +62,7 @@ def bench_gemm(args, gated: bool) -> None:
         tc.GemmPlan(torch.randn(rows, inner, device="cuda").to(torch.bfloat16), dual_rows=outs if gated else None)
         for _ in range(copies)
     ]
-    splits = 1 if gated else tc.choose_splits(tokens, outs, inner)
+    splits = 1 if gated else (args.gemm_splits or tc.choose_splits(tokens, outs, inner))
     out = (
         torch.empty(tokens, outs, device="cuda", dtype=torch.bfloat16)
         if gated
@@ -139,6 +139,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--splits", type=int, default=0, help="decode-attention: CTAs per (request, KV head); 0: the engine's rule")
     parser.add_argument("--warps", type=int, default=0, choices=[0, 6, 8], help="decode-attention: warps of a CTA; 0: the engine's rule")
+    parser.add_argument("--gemm-splits", type=int, default=0, help="gemm: ranges of the reduction axis; 0: the engine's rule")
     parser.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph")
     args = parser.parse_args(argv)
     global GRAPH

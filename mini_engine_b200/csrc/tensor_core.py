@@ -83,7 +83,7 @@ def choose_splits(tokens: int, outs: int, inner: int, max_splits: int = 8) -> in
     tile = token_tile(tokens)
     tiles = -(-outs // BLOCK_N) * -(-tokens // tile)
     k_blocks = -(-inner // BLOCK_K)
-    slots = NUM_SMS * (3 if tile <= 32 else 2 if tile <= 64 else 1)  # CTAs of this tile size that are resident at once
+    slots = NUM_SMS * (3 if tile <= 16 else 2 if tile <= 64 else 1)  # CTAs of this tile size that fit an SM at once (72, 80, 96, 192 KB of shared memory)
     wanted = min(max_splits, max(1, slots // tiles), max(1, k_blocks // MIN_K_BLOCKS_PER_SPLIT))
     per_split = -(-k_blocks // wanted)
     return -(-k_blocks // per_split)
