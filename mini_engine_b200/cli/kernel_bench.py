@@ -16,12 +16,14 @@ from __future__ import annotations
 
 import argparse
 import sys
+import time
 from types import SimpleNamespace
 
 import torch
 
 
 GRAPH = False  # set by --graph: launches are captured into one CUDA graph and replayed
+WARM_MS = 0.0  # set by --warm-ms
 
 
 def timed(run, iters: int, warmup: int = 3) -> float:
@@ -30,6 +32,13 @@ def timed(run, iters: int, warmup: int = 3) -> float:
     for i in range(warmup):
         run(i)
     torch.cuda.synchronize()
+    # A GPU that was idle runs its first milliseconds below its boost clock (1.5 of 1.9 GHz seen
+    # in kernels of 50 us): --warm-ms keeps it busy that long before the timed calls.
+    deadline = time.perf_counter() + WARM_MS / 1e3
+    while time.perf_counter() < deadline:
+        for i in range(8):
+            run(i)
+        torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if GRAPH:
         graph = torch.cuda.CUDAGraph()
@@ -140,10 +149,12 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--splits", type=int, default=0, help="decode-attention: CTAs per (request, KV head); 0: the engine's rule")
     parser.add_argument("--warps", type=int, default=0, choices=[0, 6, 8], help="decode-attention: warps of a CTA; 0: the engine's rule")
     parser.add_argument("--gemm-splits", type=int, default=0, help="gemm: ranges of the reduction axis; 0: the engine's rule")
+    parser.add_argument("--warm-ms", type=float, default=0.0, help="keep the GPU busy this long before the timed calls")
     parser.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph")
     args = parser.parse_args(argv)
-    global GRAPH
+    global GRAPH, WARM_MS
     GRAPH = args.graph
+    WARM_MS = args.warm_ms
     if args.kernel in ("gemm", "swiglu-gemm"):
         bench_gemm(args, gated=args.kernel == "swiglu-gemm")
     else:

@@ -414,7 +414,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // 514 with none, 513 with half, 559 with three quarters); two threads per row halve a warp's
 // exponentials but not the unit's (514 us); steps of 64 keys with two score buffers per head, so
 // that rows never wait for a product, lost because a product of 64 keys takes the pipe as long as
-// one of 128 (648 us).
+// one of 128 (648 us); one CTA per SM that walks a list of items (longest first, to and fro over the
+// CTAs) with the barriers' phases running on from item to item, so that an item's queries, first keys
+// and first scores come while the item before is normalised and stored: 2 to 3 % at 4,096 and 8,192
+// tokens, nothing at 2,048, and entries of unequal length would leave such a fixed list unbalanced
+// where the hardware hands this kernel's CTAs out as SMs come free.  Clock stamps of all CTAs at
+// 2,048 tokens: 60,000 to 77,000 cycles a CTA in 43 to 52 us, that is 1.48 GHz of 1.965 (the SMs
+// run this kernel under the power limit), and the MMA warp needs 750 cycles to issue the eight
+// instructions of one 128 x 128 x 128 product (the pipe takes them at 94 cycles each, two thirds of
+// its nominal rate), 3,080 of a tile's 3,600 cycles.
 constexpr int DUO_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-5 rows of head a, warps 6-9 rows of head b
 constexpr int DUO_TMEM_COLUMNS = 512;
 constexpr int DUO_TILE_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 bfloat16 tile as two 64-column halves
