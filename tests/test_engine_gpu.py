@@ -555,3 +555,60 @@ def test_engine_profiler_reports_phases(capsys):
     assert running["kernel_launches_per_step"] > 100  # 28 layers of eight kernels and more
     assert "wait for the token ids" in running["phases_us_per_step"]
     assert "lay out + H2D + graph launch" in isolated["phases_us_per_step"]
+
+
+def test_requests_arriving_over_time_on_a_layer_of_real_sizes(tmp_path_factory):
+    """One layer of Qwen3-8B's own sizes through the whole engine in bfloat16: requests arrive while
+    others run, some share a prefix, some are short enough to replay a prompt graph when they are
+    alone in a step, the longest are cut by the token budget into portions of several hundred
+    tokens (the CTA-pair products and the tensor-core attention), and the pool is so small that
+    requests are preempted.  Every generated token is checked teacher-forced against the plain
+    implementation."""
+    import random
+
+    from conftest import make_model_folder
+    from tiny_configs import LAYER_OF_8B
+
+    from mini_engine_b200 import EngineConfig, LLMEngine, SamplingParams
+    from mini_engine_b200.csrc import ops
+
+    folder = make_model_folder(tmp_path_factory, "8B_engine", seed=17, dtype=torch.bfloat16, raw=LAYER_OF_8B)
+    vocab = LAYER_OF_8B["vocab_size"]
+    rng = random.Random(5)
+    shared = random_ids(40, 200, vocab)
+    prompts, limits = [], []
+    for i in range(14):
+        kind = i % 3
+        if i == 0:
+            prompt = random_ids(50, 50, vocab)  # alone in the first step: a prompt graph
+        elif kind == 0:
+            prompt = shared[: rng.choice([64, 160])] + random_ids(50 + i, rng.randrange(1, 30), vocab)
+        elif kind == 1:
+            prompt = random_ids(70 + i, rng.randrange(2, 100), vocab)
+        else:
+            prompt = random_ids(90 + i, rng.randrange(300, 420), vocab)
+        prompts.append(prompt)
+        limits.append(rng.randrange(1, 24))
+    engine = LLMEngine.from_pretrained(
+        folder,
+        EngineConfig(block_size=16, num_blocks=40, max_num_seqs=6, max_num_batched_tokens=384, max_model_len=512, dtype=torch.bfloat16),
+    )  # fmt: skip
+    pending = list(zip(prompts, limits))
+    seqs = [engine.add_request(pending[0][0], SamplingParams(max_tokens=pending[0][1], ignore_eos=True))]
+    pending.pop(0)
+    engine.step()
+    assert engine.stats.prompt_graph_steps == 1
+    while pending or engine.scheduler.has_unfinished():
+        if not engine.scheduler.has_unfinished() or rng.random() < 0.3:
+            for _ in range(rng.randrange(1, 4)):
+                if pending:
+                    prompt, limit = pending.pop(0)
+                    seqs.append(engine.add_request(prompt, SamplingParams(max_tokens=limit, ignore_eos=True)))
+        engine.step()
+    ops.raise_on_device_error()
+    engine.block_manager.check_invariants([])
+    outputs = [s.output_token_ids for s in seqs]
+    assert [len(o) for o in outputs] == limits
+    assert engine.scheduler.num_preemptions > 0 and engine.scheduler.num_cached_tokens > 0
+    assert engine.stats.prompt_graph_steps > 0 and engine.stats.prepacked_steps > 0 and engine.stats.graph_steps > 0
+    assert_follows_plain(folder, torch.bfloat16, prompts, outputs)
