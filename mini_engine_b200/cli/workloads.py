@@ -129,7 +129,7 @@ def mixed_32b(layers: int) -> int:
 
 
 def sweep_8b(layers: int) -> int:
-    """Prompt lengths and decode context lengths at Qwen3-8B layer sizes."""
+    """Prompt lengths, decode context lengths and decode batch sizes at Qwen3-8B layer sizes."""
     from mini_engine_b200 import EngineConfig, LLMEngine
     from mini_engine_b200.config import Qwen3Config
     from mini_engine_b200.engine.runner import StepEntry
@@ -139,10 +139,10 @@ def sweep_8b(layers: int) -> int:
         num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
         max_position_embeddings=40960, tie_word_embeddings=False,
     )  # fmt: skip
-    batch, longest = 8, 32768
+    batch, longest, most = 8, 32768, 128  # decode: 8 contexts of up to 32,768 tokens, up to 128 of 2,048
     engine = LLMEngine.from_random(
         cfg, 0,
-        EngineConfig(block_size=16, num_blocks=batch * (longest // 16 + 8) + 8, max_num_seqs=batch,
+        EngineConfig(block_size=16, num_blocks=max(batch * (longest // 16 + 8), most * (2048 // 16 + 4)) + 8, max_num_seqs=most,
                      max_num_batched_tokens=16384, max_model_len=longest + 64, enable_prefix_caching=False,
                      dtype=torch.bfloat16),
     )  # fmt: skip
@@ -176,20 +176,23 @@ def sweep_8b(layers: int) -> int:
     weights = layers * (6144 * 4096 + 4096 * 4096 + 3 * 4096 * 12288) * 2 + cfg.vocab_size * 4096 * 2
     for array in runner.layout.arrays:
         array.normal_()  # contexts of random keys and values: only the time of a decode step is looked at
-    caches = [manager.new_request() for _ in range(batch)]
-    for context in (512, 2048, 8192, 32768):
+    caches = [manager.new_request() for _ in range(most)]
+    shapes = [(batch, context) for context in (512, 2048, 8192, 32768)] + [(b, 2048) for b in (1, 2, 4, 16, 32, 64, 128)]
+    for entries, context in shapes:
         for cache in caches:
+            manager.free(cache)
+        for cache in caches[:entries]:
             assert manager.try_allocate(cache, context + 40)
         position = [context]
 
         def step() -> None:
-            graphs.run([StepEntry(c, position[0], [7], (0,)) for c in caches])
+            graphs.run([StepEntry(c, position[0], [7], (0,)) for c in caches[:entries]])
             position[0] += 1
 
         ms = timed(step, 20)
-        read = weights + batch * context * 2 * layers * 8 * 128 * 2
-        print(json.dumps({"decode_batch": batch, "context": context, "ms_per_step": round(ms, 3),
-                          "tokens_per_second": round(batch / ms * 1e3), "terabytes_per_second": round(read / ms / 1e9, 2)}), flush=True)  # fmt: skip
+        read = weights + entries * context * 2 * layers * 8 * 128 * 2
+        print(json.dumps({"decode_batch": entries, "context": context, "ms_per_step": round(ms, 3),
+                          "tokens_per_second": round(entries / ms * 1e3), "terabytes_per_second": round(read / ms / 1e9, 2)}), flush=True)  # fmt: skip
     return 0
 
 
