@@ -51,11 +51,12 @@ def main(argv: list[str] | None = None) -> int:
         vocab_size=151936, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6,
         max_position_embeddings=40960, **sizes,
     )  # fmt: skip
-    pages = -(-(args.context + 8 * args.steps) // 16)
+    room = args.context + args.steps + 8  # every class starts again at the same position
+    pages = -(-room // 16)
     engine = LLMEngine.from_random(
         cfg, 0,
         EngineConfig(block_size=16, num_blocks=args.batch * pages + 8, max_num_seqs=args.batch,
-                     max_num_batched_tokens=max(args.batch, 64), max_model_len=args.context + 8 * args.steps + 16,
+                     max_num_batched_tokens=max(args.batch, 64), max_model_len=pages * 16,
                      dtype=torch.bfloat16, enable_prefix_caching=False, cuda_graphs=False),
     )  # fmt: skip
     runner, manager = engine.runner, engine.block_manager
@@ -63,7 +64,7 @@ def main(argv: list[str] | None = None) -> int:
         array.normal_()  # contexts of random keys and values: only the step's time is looked at
     caches = [manager.new_request() for _ in range(args.batch)]
     for cache in caches:
-        assert manager.try_allocate(cache, args.context + 8 * args.steps)
+        assert manager.try_allocate(cache, room)
 
     real = {name: getattr(ops, name) for names in CLASSES.values() for name in names}
     left_out: set[str] = set()
@@ -82,6 +83,7 @@ def main(argv: list[str] | None = None) -> int:
         for label, names in [("whole step", ())] + list(CLASSES.items()):
             left_out.clear()
             left_out.update(names)
+            position[0] = args.context
             graphs = DecodeGraphs(runner, args.batch)  # captured with these launches left out
 
             def step() -> None:

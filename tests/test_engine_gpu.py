@@ -612,3 +612,20 @@ def test_requests_arriving_over_time_on_a_layer_of_real_sizes(tmp_path_factory):
     assert engine.scheduler.num_preemptions > 0 and engine.scheduler.num_cached_tokens > 0
     assert engine.stats.prompt_graph_steps > 0 and engine.stats.prepacked_steps > 0 and engine.stats.graph_steps > 0
     assert_follows_plain(folder, torch.bfloat16, prompts, outputs)
+
+
+def test_step_costs_reports_every_class(capsys):
+    """The in-place cost tool captures the decode step with each class of launches left out and
+    puts the kernels back when it is done."""
+    import json
+
+    from mini_engine_b200.cli import step_costs
+    from mini_engine_b200.csrc import ops
+
+    before = (ops.add_rmsnorm, ops.qk_norm_rope_store, ops.paged_attention)
+    assert step_costs.main(["--size", "0.6b", "--layers", "2", "--batch", "3", "--context", "64", "--steps", "3"]) == 0
+    assert (ops.add_rmsnorm, ops.qk_norm_rope_store, ops.paged_attention) == before
+    rows = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    assert [r["left_out"] for r in rows] == [None, "norms", "norm_rotation_cache_write", "decode_attention", "all_but_products"]
+    whole = rows[0]["launches"]
+    assert [whole - r["launches"] for r in rows] == [0, 5, 2, 2, 9]  # two layers: 2 x 2 + 1 norms, 2 rotations, 2 attentions
