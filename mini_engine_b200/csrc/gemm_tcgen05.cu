@@ -229,21 +229,39 @@ constexpr int STACK_ROWS = 64;
 
 // All of a product's CTAs (192 for 12,288 features) are resident at once, two per SM where they
 // do not go round, so the stages of each are what keeps loads in flight.
-template <int BLOCK_T>
+//
+// KSPLIT == 2 (up to 16 tokens): the 192 CTAs above keep 20 MB on their way, and the weights come at
+// 5.9 TB/s; twice as many CTAs of half the reduction each, three to an SM, stream them at 6.5 TB/s
+// (measured with the plain split product; this kernel: 6.25 TB/s at 8 tokens, 32.2 us against
+// 34.5 us for 12,288 gated features of 4,096).  With tiles of 32 and 64 tokens (three stages to fit
+// three CTAs to an SM) the halves gain nothing (35.8 against 36.0 us, 39.9 against 39.4 us).  The two halves of a reduction are the two CTAs of a
+// cluster: the second writes its sums into the first one's shared memory (st.shared::cluster),
+// which adds them to its own before the activation, so there are still no partial sums in global
+// memory and no second kernel.  grid (2 x token tiles, ceil(outs / 64)), clusters of 2 along x.
+template <int BLOCK_T, int KSPLIT>
 struct StackedConfig {
     static constexpr int A_BYTES = BLOCK_N * BLOCK_K * 2;  // 64 gate rows on 64 up rows
     static constexpr int B_BYTES = BLOCK_T * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (100 * 1024) / STAGE_BYTES + (BLOCK_T == 16 ? 1 : 0);  // 6, 5, 4
+    // one half of a split reduction: 72 KB, three CTAs to an SM; else 6, 5, 4 stages, two to an SM
+    static constexpr int STAGES = KSPLIT == 2 ? 4 : (100 * 1024) / STAGE_BYTES + (BLOCK_T == 16 ? 1 : 0);
     static constexpr int TMEM_COLUMNS = BLOCK_T < 32 ? 32 : BLOCK_T;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
-template <int BLOCK_T>
+__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float value) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(value) : "memory");
+}
+
+template <int BLOCK_T, int KSPLIT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
-    using C = StackedConfig<BLOCK_T>;
-    static_assert(BLOCK_T <= 64 && STACK_ROWS * BLOCK_T * 4 <= C::STAGES * C::STAGE_BYTES, "the exchange buffer reuses the stages");
+    using C = StackedConfig<BLOCK_T, KSPLIT>;
+    static_assert(BLOCK_T <= 64 && (STACK_ROWS + (KSPLIT == 2 ? BLOCK_N : 0)) * BLOCK_T * 4 <= C::STAGES * C::STAGE_BYTES,
+                  "the exchange buffers reuse the stages");
+    static_assert(KSPLIT == 1 || KSPLIT == 2, "one CTA or a cluster of two per reduction");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
@@ -252,8 +270,11 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.y * STACK_ROWS, t0 = blockIdx.x * BLOCK_T;
-    const int iterations = p.k_blocks;
+    const uint32_t rank = KSPLIT == 2 ? cluster_ctarank() : 0;  // which half of the reduction
+    const int n0 = blockIdx.y * STACK_ROWS, t0 = (blockIdx.x / KSPLIT) * BLOCK_T;
+    const int per_rank = (p.k_blocks + KSPLIT - 1) / KSPLIT;
+    const int kb0 = static_cast<int>(rank) * per_rank;  // first k block of this CTA
+    const int iterations = max(min(per_rank, p.k_blocks - kb0), 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -266,6 +287,7 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_holder;
     constexpr int HALF_A = STACK_ROWS * BLOCK_K * 2;  // bytes of 64 rows of a k block
+    bool ok = true;  // of the epilogue warps: the sums are there
 
     if (warp == 0) {
         if (lane == 0) {
@@ -274,21 +296,21 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
             for (int i = 0; i < early; ++i) {
                 uint8_t* a_tile = tiles + i * C::STAGE_BYTES;
                 mbar_expect_tx(&full[i], C::STAGE_BYTES);
-                tma_load_2d(a_tile, &map_w, i * BLOCK_K, n0, &full[i]);
-                tma_load_2d(a_tile + HALF_A, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[i]);
+                tma_load_2d(a_tile, &map_w, (kb0 + i) * BLOCK_K, n0, &full[i]);
+                tma_load_2d(a_tile + HALF_A, &map_w, (kb0 + i) * BLOCK_K, p.dual_row_offset + n0, &full[i]);
             }
             pdl_wait();
             for (int i = 0; i < early; ++i)
-                tma_load_2d(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, i * BLOCK_K, t0, &full[i]);
+                tma_load_2d(tiles + i * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb0 + i) * BLOCK_K, t0, &full[i]);
             int issued = early;
             for (int i = early; i < iterations; ++i, ++issued) {
                 const int stage = i % C::STAGES;
                 if (!mbar_wait(&empty[stage], ((i / C::STAGES) & 1) ^ 1)) { atomicCAS(&g_gemm_error, 0, (30 << 8) | stage); break; }
                 uint8_t* a_tile = tiles + stage * C::STAGE_BYTES;
                 mbar_expect_tx(&full[stage], C::STAGE_BYTES);
-                tma_load_2d(a_tile, &map_w, i * BLOCK_K, n0, &full[stage]);
-                tma_load_2d(a_tile + HALF_A, &map_w, i * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
-                tma_load_2d(a_tile + C::A_BYTES, &map_x, i * BLOCK_K, t0, &full[stage]);
+                tma_load_2d(a_tile, &map_w, (kb0 + i) * BLOCK_K, n0, &full[stage]);
+                tma_load_2d(a_tile + HALF_A, &map_w, (kb0 + i) * BLOCK_K, p.dual_row_offset + n0, &full[stage]);
+                tma_load_2d(a_tile + C::A_BYTES, &map_x, (kb0 + i) * BLOCK_K, t0, &full[stage]);
             }
             if (issued < iterations || g_gemm_error != 0) {
                 for (int i = max(issued - C::STAGES, 0); i < issued; ++i)
@@ -315,16 +337,37 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
             tcgen05_commit(accum);
         }
     } else {
-        const int quarter = warp & 3;  // a warp may read TMEM lanes [32 * (warp % 4), +32): 0, 1 gate rows; 2, 3 up rows
         pdl_wait();
-        bool ok = mbar_wait(accum, 0);
+        ok = iterations == 0 || mbar_wait(accum, 0);
         if (!ok && lane == 0) atomicCAS(&g_gemm_error, 0, (32 << 8));
         ok = __all_sync(0xffffffffu, ok) && g_gemm_error == 0;
         tcgen05_fence_after();
-        // All copies have landed and all MMAs have read them: the stages now carry the up sums,
-        // [token of the tile][feature of the 64].
-        float* exchange = reinterpret_cast<float*>(tiles);
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    }
+    // All copies of this CTA have landed and all its MMAs have read them: the stages now carry the
+    // sums on their way, first the other half's [token of the tile][row of the 128], then the up
+    // sums [token of the tile][feature of the 64].
+    float* other_half = reinterpret_cast<float*>(tiles);
+    float* exchange = other_half + (KSPLIT == 2 ? BLOCK_N * BLOCK_T : 0);
+    const int quarter = warp & 3;  // a warp may read TMEM lanes [32 * (warp % 4), +32): 0, 1 gate rows; 2, 3 up rows
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    if (KSPLIT == 2) {
+        // Every thread of both CTAs takes part in the cluster's barriers, also after a wait that ran out.
+        __syncthreads();
+        cluster_sync();  // the first CTA's stages are free
+        if (rank == 1 && warp >= 2 && ok && iterations > 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BLOCK_T; c0 += 16) {
+                if (t0 + c0 >= p.tokens) break;
+                float sums[16];
+                tcgen05_ld16(lane_base + c0, sums);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) st_cluster_f32(other_half + (c0 + c) * BLOCK_N + quarter * 32 + lane, 0, sums[c]);
+            }
+        }
+        cluster_sync();  // the second CTA's sums are in the first one's shared memory
+    }
+    if (warp >= 2 && rank == 0) {
+        const bool add = KSPLIT == 2 && p.k_blocks > per_rank;  // the other half had k blocks of its own
         const int feature = (quarter & 1) * 32 + lane;
         if (ok && quarter >= 2) {
 #pragma unroll 1
@@ -333,7 +376,8 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
                 float up[16];
                 tcgen05_ld16(lane_base + c0, up);
 #pragma unroll
-                for (int c = 0; c < 16; ++c) exchange[(c0 + c) * STACK_ROWS + feature] = up[c];
+                for (int c = 0; c < 16; ++c)
+                    exchange[(c0 + c) * STACK_ROWS + feature] = up[c] + (add ? other_half[(c0 + c) * BLOCK_N + quarter * 32 + lane] : 0.0f);
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
@@ -350,7 +394,8 @@ gemm_tcgen05_stacked_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, co
                     for (int c = 0; c < 16; ++c) {
                         const int t = t0 + c0 + c;
                         if (t < p.tokens) {
-                            const float activated = __fdividef(gate[c], 1.0f + __expf(-gate[c]));
+                            const float g = gate[c] + (add ? other_half[(c0 + c) * BLOCK_N + quarter * 32 + lane] : 0.0f);
+                            const float activated = __fdividef(g, 1.0f + __expf(-g));
                             out[static_cast<size_t>(t) * p.outs + n] = __float2bfloat16_rn(activated * exchange[(c0 + c) * STACK_ROWS + feature]);
                         }
                     }
@@ -938,23 +983,50 @@ ME_EXPORT int me_gemm_tcgen05_swiglu(const void* map_w, const void* map_x, void*
 
 template <int BLOCK_T>
 static int launch_stacked(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
-    using C = StackedConfig<BLOCK_T>;
-    auto kernel = gemm_tcgen05_stacked_swiglu_kernel<BLOCK_T>;
+    using C = StackedConfig<BLOCK_T, 1>;
+    auto kernel = gemm_tcgen05_stacked_swiglu_kernel<BLOCK_T, 1>;
     static SharedMemoryOptIn opt_in;
     if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
     dim3 grid((p.tokens + BLOCK_T - 1) / BLOCK_T, (p.outs + STACK_ROWS - 1) / STACK_ROWS, 1);
     return launch_kernel(kernel, grid, GEMM_THREADS, C::SMEM_BYTES, stream, map_w, map_x, p);
 }
 
+// The same with the reduction cut in two halves, one per CTA of a cluster of two.
+template <int BLOCK_T>
+static int launch_stacked_halves(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+    using C = StackedConfig<BLOCK_T, 2>;
+    auto kernel = gemm_tcgen05_stacked_swiglu_kernel<BLOCK_T, 2>;
+    static SharedMemoryOptIn opt_in;
+    if (const int e = opt_in(kernel, C::SMEM_BYTES)) return e;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * ((p.tokens + BLOCK_T - 1) / BLOCK_T), (p.outs + STACK_ROWS - 1) / STACK_ROWS, 1);
+    config.blockDim = dim3(GEMM_THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = 2;
+    return static_cast<int>(cudaLaunchKernelEx(&config, kernel, map_w, map_x, p));
+}
+
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for few tokens (block_t 16,
-// 32 or 64), the reduction unsplit.  The weight map has boxes of 64 rows.
+// 32 or 64), the reduction in one CTA or (`halves` 2, block_t 16) in the two CTAs of a cluster.
+// The weight map has boxes of 64 rows.
 ME_EXPORT int me_gemm_tcgen05_stacked_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
-                                             int inner, int dual_row_offset, int block_t, cudaStream_t stream) {
+                                             int inner, int dual_row_offset, int block_t, int halves, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
     GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0};
+    if (halves == 2) return block_t == 16 ? launch_stacked_halves<16>(w, x, p, stream) : ME_ERR_ARGUMENT;
+    if (halves != 1) return ME_ERR_ARGUMENT;
     switch (block_t) {
         case 16: return launch_stacked<16>(w, x, p, stream);
         case 32: return launch_stacked<32>(w, x, p, stream);

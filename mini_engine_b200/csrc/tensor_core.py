@@ -27,6 +27,10 @@ PAIR_MIN_TOKENS = 128  # longer products run on CTA pairs (256 x 256 tiles), uns
 # 33.1 -> 31.3 us, 512 tokens 48.9 -> 44.2 us); with 16 to 32 k blocks per split the lone CTAs are as
 # fast or 2 % faster.
 PAIR_SPLIT_MIN_K_BLOCKS = 48
+# Up to this many tokens the stacked gated product cuts its reduction in two halves, one per CTA of a
+# cluster of two: 384 CTAs of 72 KB, three to an SM, stream the weights at 6.5 TB/s where 192 CTAs
+# with the whole reduction reach 5.9 (8 tokens, 12,288 gated features of 4,096: 34.3 us unsplit).
+STACKED_HALVES_MAX_TOKENS = 16
 STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
 
 
@@ -53,7 +57,7 @@ def _library():
         lib.me_gemm_tcgen05_persistent.restype = c_int
         lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
-        lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
         lib.me_gemm_wait_probe.argtypes = [c_int, c_void_p, c_void_p]
         lib.me_gemm_wait_probe.restype = c_int
@@ -160,9 +164,10 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
         raise RuntimeError(f"tensor-core product failed to launch (code {code})")
 
 
-def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
+def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int | None = None) -> None:
     """``act = silu(x @ gate^T) * (x @ up^T)`` in bfloat16, gate/up being the halves of the
-    plan's weight."""
+    plan's weight.  ``halves`` (1 or 2) pins how many CTAs share a reduction of the few-token kernel
+    instead of the rule's choice: the kernel tests run both forms, the kernel bench times them."""
     _check_x(plan, x)
     tokens = x.shape[0]
     if plan.dual_rows is None:
@@ -172,9 +177,11 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor) -> None:
     stream = _ops_stream()
     if tokens <= STACKED_MAX_TOKENS:
         tile = token_tile(tokens)
+        if halves is None:
+            halves = 2 if tokens <= STACKED_HALVES_MAX_TOKENS and plan.inner >= 2 * BLOCK_K else 1
         code = _library().me_gemm_tcgen05_stacked_swiglu(
             plan.map_half, _activation_map(x, tile), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
-            tile, stream,
+            tile, halves, stream,
         )  # fmt: skip
     elif tokens > PAIR_MIN_TOKENS:
         code = _library().me_gemm_tcgen05_persistent_swiglu(

@@ -27,15 +27,16 @@ from mini_engine_b200.parts.base import StepContext
 MAX_SPLITS = 8
 DECODE_TOKENS = 64
 # The tensor-core gated product runs as one kernel with the activation in its epilogue from this
-# many tokens on (5 to 64 tokens: gate rows stacked on up rows, the reduction unsplit; more: CTA
-# pairs).  Below, all of a step's time is the weight stream and 384 short CTAs of a split product
-# followed by the activation kernel stream it a little faster than 192 long ones (measured at
-# batch 1: 3.24 against 3.31 ms a step; at batch 8: 3.61 against 3.58).
-GATED_FUSED_MIN_TOKENS = 5
-# The stacked kernel (5 to 64 tokens) has one CTA per 64 gated features and does not split the
-# reduction: with few features it leaves most SMs idle, and the split product with the activation
-# kernel behind it is faster (intermediate size 3,072, 48 CTAs: a decode step of 28 layers at batch
-# 32 takes 1.13 ms that way against 1.20 ms; at 12,288, 192 CTAs, the stacked kernel wins).
+# many tokens on (4 to 64 tokens: gate rows stacked on up rows, up to 16 tokens with the reduction
+# in the two CTAs of a cluster; more: CTA pairs).  Below, all of a step's time is the weight stream
+# and 384 short CTAs of a split product followed by the activation kernel stream it as fast or a
+# little faster (a decode step of Qwen3-8B sizes, split product against one kernel: batch 1 3.21
+# against 3.23 ms, batch 2 3.26 against 3.27, batch 3 3.28 against 3.28, batch 4 3.33 against 3.30).
+GATED_FUSED_MIN_TOKENS = 4
+# The stacked kernel (4 to 64 tokens) has one CTA (up to 16 tokens: two) per 64 gated features: with
+# few features it leaves most SMs idle, and the split product with the activation kernel behind it
+# is faster (intermediate size 3,072: a decode step of 28 layers takes 1.11 ms that way against
+# 1.15 ms at batch 8, 2.07 against 2.13 ms at batch 32; at 12,288 features the stacked kernel wins).
 GATED_STACKED_MIN_FEATURES = 128 * 64
 
 

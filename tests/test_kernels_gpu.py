@@ -122,6 +122,34 @@ def test_gemm_tensor_core_swiglu(tokens, inter, inner):
     assert rel_error(act, want) < 6e-3  # one rounding to bfloat16
 
 
+@pytest.mark.parametrize(
+    "tokens,inter,inner",
+    [(1, 64, 128), (8, 200, 136), (16, 130, 200), (5, 12288, 4096), (3, 72, 64), (9, 64, 1096), (16, 100, 72), (12, 3072, 1024)],
+)  # fmt: skip
+def test_gemm_tensor_core_swiglu_with_the_reduction_in_two_ctas(tokens, inter, inner):
+    """Up to 16 tokens the reduction of the stacked gated product may be cut in two halves that
+    the two CTAs of a cluster compute, the second adding its sums into the first one's shared
+    memory: both forms against float64, over an odd number of k blocks, a last k block that is
+    partly empty and a single k block (the second CTA then has nothing to add).  A value that
+    stands out in the second half of the reduction must arrive."""
+    from mini_engine_b200.csrc import tensor_core
+
+    torch.manual_seed(5)
+    x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * inter, inner, device="cuda") * 0.2).to(torch.bfloat16)
+    x[tokens - 1, inner - 1], w[inter - 1, inner - 1], w[2 * inter - 1, inner - 1] = 16.0, 8.0, 8.0
+    both = x.double() @ w.double().T
+    gate, up = both[:, :inter], both[:, inter:]
+    want = gate * torch.sigmoid(gate) * up
+    plan = tensor_core.GemmPlan(w, dual_rows=inter)
+    for halves in (2, 1, None):
+        act = torch.full((tokens, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+        tensor_core.gemm_swiglu(plan, x, act, halves)
+        assert tensor_core.take_error() == 0
+        assert rel_error(act, want) < 6e-3, halves
+        assert int(act.float().abs().argmax()) == (tokens - 1) * inter + inter - 1
+
+
 # -------------------------------------------------------------------------- elementwise
 
 
