@@ -80,9 +80,9 @@ def bench_gemm(args, gated: bool) -> None:
 
     def run(i: int) -> None:
         if gated:
-            tc.gemm_swiglu(plans[i % copies], x, out, args.halves or None)
+            tc.gemm_swiglu(plans[i % copies], x, out, args.halves or None, None if args.group < 0 else args.group)
         else:
-            tc.gemm(plans[i % copies], x, out, splits)
+            tc.gemm(plans[i % copies], x, out, splits, None if args.group < 0 else args.group)
 
     ms = timed(run, args.iters)
     flops = 2.0 * tokens * rows * inner
@@ -150,6 +150,7 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--warps", type=int, default=0, choices=[0, 6, 8], help="decode-attention: warps of a CTA; 0: the engine's rule")
     parser.add_argument("--gemm-splits", type=int, default=0, help="gemm: ranges of the reduction axis; 0: the engine's rule")
     parser.add_argument("--halves", type=int, default=0, choices=[0, 1, 2], help="swiglu-gemm of up to 16 tokens: CTAs per reduction; 0: the engine's rule")
+    parser.add_argument("--group", type=int, default=-1, help="products of more than 128 tokens: token tiles of a group of the tile list (0: one group); -1: the engine's rule")
     parser.add_argument("--warm-ms", type=float, default=0.0, help="keep the GPU busy this long before the timed calls")
     parser.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph")
     args = parser.parse_args(argv)

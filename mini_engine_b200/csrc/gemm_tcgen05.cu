@@ -64,6 +64,7 @@ struct GemmParams {
     int dual_row_offset;  // row of W where the second (up) half starts
     int token_tiles, full_tiles, tail_parts;  // pair kernels: tiles along the tokens; whole ones; cuts of the rest
     int items;  // persistent pair kernel: whole tiles + parts of cut tiles
+    int feature_tiles, group;  // persistent pair kernel: tiles along the features; token tiles of a group (see pair_item)
 };
 
 template <int BLOCK_T, bool DUAL>
@@ -618,8 +619,15 @@ __device__ __forceinline__ void pair_item(const GemmParams& p, int item, int& t0
         width = (base + (part < extra ? 1 : 0)) * 16;
         token_offset = (part * base + min(part, extra)) * 16;
     }
-    t0 = (tile % p.token_tiles) * TILE_T + token_offset;
-    feature_tile = tile / p.token_tiles;
+    // Tiles are numbered group by group: a group is `group` token tiles wide and all feature tiles
+    // tall, and inside it the token tile runs fastest.  The pairs that work at the same time then
+    // cover a block of about as many feature tiles as token tiles, so they ask for the fewest
+    // different operand tiles, and the group's tokens are read once for all features.
+    const int per_group = p.group * p.feature_tiles;
+    const int g = tile / per_group, rest = tile % per_group;
+    const int wide = min(p.group, p.token_tiles - g * p.group);
+    t0 = (g * p.group + rest % wide) * TILE_T + token_offset;
+    feature_tile = rest / wide;
 }
 
 template <bool DUAL>
@@ -906,7 +914,7 @@ ME_EXPORT int me_gemm_tcgen05_pair_split(const void* map_w, const void* map_x, f
 }
 
 template <bool DUAL>
-static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, cudaStream_t stream) {
+static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmParams& p, int group, cudaStream_t stream) {
     using C = PersistentConfig<DUAL>;
     auto kernel = gemm_tcgen05_persistent_kernel<DUAL>;
     static SharedMemoryOptIn opt_in;
@@ -916,7 +924,9 @@ static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x,
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     GemmParams q = p;
     q.token_tiles = (p.tokens + C::TILE_T - 1) / C::TILE_T;
-    const int tiles = q.token_tiles * ((p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N));
+    q.feature_tiles = (p.outs + 2 * BLOCK_N - 1) / (2 * BLOCK_N);
+    q.group = group > 0 ? group : q.token_tiles;
+    const int tiles = q.token_tiles * q.feature_tiles;
     const int pairs = sms / 2 > 0 ? sms / 2 : 1;
     // The tiles of a last round that is less than half full are cut in 2 or 4 narrower ones that
     // run side by side (see the pair kernel's launcher for what was measured).
@@ -946,25 +956,25 @@ static int launch_persistent(const CUtensorMap& map_w, const CUtensorMap& map_x,
 // out[t][n] (float32) = x[t] . w[n] by persistent CTA pairs.  Weight and activation maps have
 // boxes of 128 rows.
 ME_EXPORT int me_gemm_tcgen05_persistent(const void* map_w, const void* map_x, float* out, int tokens, int outs,
-                                         int inner, cudaStream_t stream) {
+                                         int inner, int group, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1, 0};
-    return launch_persistent<false>(w, x, p, stream);
+    GemmParams p{out, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, 0, 0, 0, 1, 0, 0, 0};
+    return launch_persistent<false>(w, x, p, group, stream);
 }
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) by persistent CTA pairs.
 // Weight and activation maps have boxes of 128 rows.
 ME_EXPORT int me_gemm_tcgen05_persistent_swiglu(const void* map_w, const void* map_x, void* act, int tokens, int outs,
-                                                int inner, int dual_row_offset, cudaStream_t stream) {
+                                                int inner, int dual_row_offset, int group, cudaStream_t stream) {
     if (tokens <= 0 || outs <= 0) return 0;
     alignas(64) CUtensorMap w, x;
     memcpy(&w, map_w, sizeof(w));
     memcpy(&x, map_x, sizeof(x));
-    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0};
-    return launch_persistent<true>(w, x, p, stream);
+    GemmParams p{act, tokens, outs, (inner + BLOCK_K - 1) / BLOCK_K, 0, dual_row_offset, 0, 0, 1, 0, 0, 0};
+    return launch_persistent<true>(w, x, p, group, stream);
 }
 
 // act[t][n] (bfloat16) = silu(x . w[n]) * (x . w[dual_row_offset + n]) for n < outs.

@@ -31,6 +31,15 @@ PAIR_SPLIT_MIN_K_BLOCKS = 48
 # cluster of two: 384 CTAs of 72 KB, three to an SM, stream the weights at 6.5 TB/s where 192 CTAs
 # with the whole reduction reach 5.9 (8 tokens, 12,288 gated features of 4,096: 34.3 us unsplit).
 STACKED_HALVES_MAX_TOKENS = 16
+# The persistent pair kernel numbers its tiles in groups of this many token tiles (all feature tiles
+# of a group before the next group): the pairs that run together then share a block of tiles about
+# as tall as it is wide, and a group's activations are read once for all features.  0: one group (the
+# token tile fastest over the whole product).  Measured at Qwen3-8B's shapes: nothing changes up to
+# 4,096 tokens; 8,192 tokens: q/k/v 317 -> 295 us, o 211 -> 193, down 606 -> 563, gate and up with
+# SwiGLU 1,159 -> 1,119 (its groups 16 wide: with 8, 1,130); 16,384 tokens: 697 -> 574, 464 -> 384,
+# 1,349 -> 1,125, 2,462 -> 2,247 us (1.43 to 1.47 PFLOP/s).
+PAIR_GROUP_TOKEN_TILES = 8
+PAIR_GROUP_TOKEN_TILES_GATED = 16
 STACKED_MAX_TOKENS = 64  # gated products of up to this many tokens stack gate rows on up rows in one operand
 
 
@@ -53,9 +62,9 @@ def _library():
         lib.me_gemm_tcgen05_swiglu.restype = c_int
         lib.me_gemm_tcgen05_pair_split.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_pair_split.restype = c_int
-        lib.me_gemm_tcgen05_persistent.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_persistent.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent.restype = c_int
-        lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.me_gemm_tcgen05_persistent_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_persistent_swiglu.restype = c_int
         lib.me_gemm_tcgen05_stacked_swiglu.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         lib.me_gemm_tcgen05_stacked_swiglu.restype = c_int
@@ -138,9 +147,10 @@ def _check_x(plan: GemmPlan, x: torch.Tensor) -> None:
         raise RuntimeError("activation must be 16-byte aligned for TMA")
 
 
-def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
+def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int, group: int | None = None) -> None:
     """``out[s] = x @ weight^T`` restricted to the k range of split ``s``; float32
-    ``[splits, T, rows]``."""
+    ``[splits, T, rows]``.  ``group`` pins the width of the persistent kernel's tile groups (the
+    kernel tests run several; the kernel bench times them)."""
     _check_x(plan, x)
     tokens = x.shape[0]
     if out.dtype != torch.float32 or tuple(out.shape) != (splits, tokens, plan.rows) or not out.is_contiguous():
@@ -149,8 +159,9 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
     stream = _ops_stream()
     if tokens > PAIR_MIN_TOKENS and splits == 1:
         code = _library().me_gemm_tcgen05_persistent(
-            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, stream
-        )
+            plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner,
+            PAIR_GROUP_TOKEN_TILES if group is None else group, stream,
+        )  # fmt: skip
     elif tokens > PAIR_MIN_TOKENS and -(-plan.inner // BLOCK_K) >= PAIR_SPLIT_MIN_K_BLOCKS * splits:
         code = _library().me_gemm_tcgen05_pair_split(
             plan.map, _activation_map(x, 128), out.data_ptr(), tokens, plan.rows, plan.inner, splits, stream
@@ -164,7 +175,7 @@ def gemm(plan: GemmPlan, x: torch.Tensor, out: torch.Tensor, splits: int) -> Non
         raise RuntimeError(f"tensor-core product failed to launch (code {code})")
 
 
-def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int | None = None) -> None:
+def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int | None = None, group: int | None = None) -> None:
     """``act = silu(x @ gate^T) * (x @ up^T)`` in bfloat16, gate/up being the halves of the
     plan's weight.  ``halves`` (1 or 2) pins how many CTAs share a reduction of the few-token kernel
     instead of the rule's choice: the kernel tests run both forms, the kernel bench times them."""
@@ -185,8 +196,9 @@ def gemm_swiglu(plan: GemmPlan, x: torch.Tensor, act: torch.Tensor, halves: int 
         )  # fmt: skip
     elif tokens > PAIR_MIN_TOKENS:
         code = _library().me_gemm_tcgen05_persistent_swiglu(
-            plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows, stream
-        )
+            plan.map, _activation_map(x, 128), act.data_ptr(), tokens, plan.dual_rows, plan.inner, plan.dual_rows,
+            PAIR_GROUP_TOKEN_TILES_GATED if group is None else group, stream,
+        )  # fmt: skip
     else:
         tile = 128  # 65 to 128 tokens: lone CTAs with gate and up sums side by side in tensor memory
         code = _library().me_gemm_tcgen05_swiglu(

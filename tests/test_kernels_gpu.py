@@ -83,6 +83,33 @@ def test_gemm_tensor_core(tokens, outs, inner):
         assert rel_error(out.sum(0), want) < 1e-5 * max(1.0, math.sqrt(inner / 4096)), f"splits={splits}"
 
 
+@pytest.mark.parametrize("group", [None, 0, 1, 3, 8])
+def test_gemm_tensor_core_tile_groups(group):
+    """The persistent pair kernel numbers its tiles group by group (so many token tiles wide, all
+    feature tiles tall).  Ten token tiles and nine feature tiles, the last group narrower than the
+    others and the tiles of the last round cut in four: every width of group gives the product,
+    plain and gated (18 token tiles in groups of 16 by the rule)."""
+    from mini_engine_b200.csrc import tensor_core
+
+    torch.manual_seed(11)
+    tokens, outs, inner = 2321, 2100, 72
+    x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
+    w = torch.randn(outs, inner, device="cuda").to(torch.bfloat16)
+    out = torch.full((1, tokens, outs), float("nan"), device="cuda")
+    tensor_core.gemm(tensor_core.GemmPlan(w), x, out, 1, group)
+    assert tensor_core.take_error() == 0
+    assert rel_error(out[0], x.double() @ w.double().T) < 1e-5
+    tokens, inter = 4400, 1300
+    x = torch.randn(tokens, inner, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(2 * inter, inner, device="cuda") * 0.2).to(torch.bfloat16)
+    act = torch.full((tokens, inter), float("nan"), device="cuda", dtype=torch.bfloat16)
+    tensor_core.gemm_swiglu(tensor_core.GemmPlan(w, dual_rows=inter), x, act, None, group)
+    assert tensor_core.take_error() == 0
+    both = x.double() @ w.double().T
+    gate, up = both[:, :inter], both[:, inter:]
+    assert rel_error(act, gate * torch.sigmoid(gate) * up) < 6e-3
+
+
 def test_gemm_tensor_core_finds_one_large_product():
     """A single large x[t][k] * w[n][k] among small terms must land in exactly out[t][n]:
     a wrong swizzle, k step or lane mapping would put it elsewhere or drop it."""
