@@ -5,6 +5,7 @@
     python -m mini_engine_b200.cli.kernel_bench swiglu-gemm --tokens 2048 --outs 12288 --inner 4096
     python -m mini_engine_b200.cli.kernel_bench decode-attention --batch 64 --context 2048
     python -m mini_engine_b200.cli.kernel_bench prefill-attention --tokens 2048
+    python -m mini_engine_b200.cli.kernel_bench mma-rate     # the tensor pipe alone: cycles per MMA
 
 It is what the profiles under ``profiles/`` were captured with (small cases, a few launches).
 Weights are rotated between launches so that every launch reads more than the 126 MB L2 holds.
@@ -93,6 +94,47 @@ def bench_gemm(args, gated: bool) -> None:
     assert tc.take_error() == 0
 
 
+MMA_RATE_CASES = [
+    # (label, pair, a_in_tensor_memory, b_mn_major, n)
+    ("one CTA, both operands in shared memory, N = 64", 0, 0, 0, 64),
+    ("one CTA, both operands in shared memory, N = 128", 0, 0, 0, 128),
+    ("one CTA, both operands in shared memory, N = 256", 0, 0, 0, 256),
+    ("one CTA, A in tensor memory, B MN-major, N = 128", 0, 1, 1, 128),
+    ("CTA pair, both operands in shared memory, N = 64", 1, 0, 0, 64),
+    ("CTA pair, both operands in shared memory, N = 128", 1, 0, 0, 128),
+    ("CTA pair, both operands in shared memory, N = 256", 1, 0, 0, 256),
+    ("CTA pair, A in tensor memory, B MN-major, N = 128", 1, 1, 1, 128),
+]
+
+
+def mma_rate(pair: int, a_in_tensor_memory: int, b_mn_major: int, n: int, ctas: int = 148, iters: int = 2000) -> float:
+    """Cycles per MMA of K = 16 when nothing but MMAs runs (csrc/mma_rate.cu)."""
+    import ctypes
+
+    from mini_engine_b200.csrc.build import load_library
+
+    lib = load_library("mma_rate")
+    lib.me_mma_rate.argtypes = [ctypes.c_void_p] + [ctypes.c_int] * 6 + [ctypes.c_void_p]
+    lib.me_mma_rate.restype = ctypes.c_int
+    cycles = torch.zeros(1, dtype=torch.int64, device="cuda")
+    for _ in range(2):
+        code = lib.me_mma_rate(cycles.data_ptr(), pair, a_in_tensor_memory, b_mn_major, n, ctas, iters, None)
+        if code != 0:
+            raise RuntimeError(f"me_mma_rate failed to launch (code {code})")
+        torch.cuda.synchronize()
+    total = int(cycles.item())
+    if total < 0:
+        raise RuntimeError("the MMAs' bounded wait ran out")
+    return total / (4 * iters)
+
+
+def bench_mma_rate(args) -> None:
+    for label, pair, in_tmem, mn_major, n in MMA_RATE_CASES:
+        cycles = mma_rate(pair, in_tmem, mn_major, n)
+        m = 256 if pair else 128
+        print(f"{label}: {cycles:.1f} cycles per MMA of {m} x {n} x 16, {2 * 128 * n * 16 / cycles:.0f} flop per cycle and SM")
+
+
 def attention_context(entries: int, new_tokens: int, context: int):
     from mini_engine_b200.engine.workspace import Workspace
 
@@ -135,7 +177,7 @@ def bench_attention(args, decode: bool) -> None:
 
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=["gemm", "swiglu-gemm", "decode-attention", "prefill-attention"])
+    parser.add_argument("kernel", choices=["gemm", "swiglu-gemm", "decode-attention", "prefill-attention", "mma-rate"])
     parser.add_argument("--tokens", type=int, default=2048)
     parser.add_argument("--outs", type=int, default=4096)
     parser.add_argument("--inner", type=int, default=4096)
@@ -157,7 +199,9 @@ def main(argv: list[str] | None = None) -> int:
     global GRAPH, WARM_MS
     GRAPH = args.graph
     WARM_MS = args.warm_ms
-    if args.kernel in ("gemm", "swiglu-gemm"):
+    if args.kernel == "mma-rate":
+        bench_mma_rate(args)
+    elif args.kernel in ("gemm", "swiglu-gemm"):
         bench_gemm(args, gated=args.kernel == "swiglu-gemm")
     else:
         bench_attention(args, decode=args.kernel == "decode-attention")

@@ -36,6 +36,7 @@ LIBRARIES = {
     "attention_bf16": "attention_bf16.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
     "sampling": "sampling.cu",
+    "mma_rate": "mma_rate.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -110,6 +110,16 @@ def test_gemm_tensor_core_tile_groups(group):
     assert rel_error(act, gate * torch.sigmoid(gate) * up) < 6e-3
 
 
+def test_the_tensor_pipe_alone_runs_at_its_nominal_rate():
+    """The measuring kernel of `kernel_bench mma-rate`: a CTA, or a CTA pair, that only issues MMAs
+    needs 64 cycles for 128 x 128 x 16 and twice that for N = 256 (8,192 flop a cycle and SM)."""
+    from mini_engine_b200.cli.kernel_bench import mma_rate
+
+    assert 60 <= mma_rate(0, 0, 0, 128, ctas=4, iters=500) <= 72
+    assert 120 <= mma_rate(1, 0, 0, 256, ctas=4, iters=500) <= 144
+    assert 60 <= mma_rate(1, 1, 1, 128, ctas=4, iters=500) <= 72
+
+
 def test_gemm_tensor_core_finds_one_large_product():
     """A single large x[t][k] * w[n][k] among small terms must land in exactly out[t][n]:
     a wrong swizzle, k step or lane mapping would put it elsewhere or drop it."""
