@@ -400,7 +400,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // threads talks to the MMA warp through its own barriers only.  The MMA warp issues
 //     S_a(0), S_b(0);  then per tile j:  O_a += P_a V(j),  S_a(j+1),  O_b += P_b V(j),  S_b(j+1)
 // so that while group a turns S_a(j+1) into probabilities the pipe runs O_b(j) and S_b(j+1), and
-// the other way round.  Lazy rescaling, masking by position and page addressing as above.
+// the other way round.  A head's rows hand their probabilities over a quarter of the tile's keys at
+// a time (barriers p_part[head][quarter]), and the two MMAs of a quarter are issued as soon as it
+// is there: three quarters of O += P V run under the row's own exponentials instead of after them
+// (8,192 tokens: 497 -> 475 us).  Lazy rescaling, masking by position and page addressing as above.
 //
 // What bounds it (clock stamps of one CTA, 2,048 to 8,192 tokens): a tile of 128 keys of both heads
 // takes 3,700-3,900 cycles; its four products 2,580; each head's rows 35 for the load of the scores,
@@ -441,8 +444,9 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint8_t* v_tiles = tiles + 4 * DUO_TILE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + 6 * DUO_TILE_BYTES);
     uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-             *s_full = bars + 9, *p_full = bars + 11, *o_full = bars + 13;  // o_full[2 heads][2 tile parities]
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+             *s_full = bars + 9, *o_full = bars + 11,  // o_full[2 heads][2 tile parities]
+             *p_part = bars + 15;                      // p_part[2 heads][4 quarters of a tile's keys]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 23);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head0 = 2 * blockIdx.x, q_block = gridDim.y - 1 - blockIdx.y;  // the longest blocks start first
@@ -455,8 +459,8 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
             mbar_init(v_full + i, 1);
             mbar_init(v_empty + i, 1);
             mbar_init(s_full + i, 1);
-            mbar_init(p_full + i, 128);
         }
+        for (int i = 0; i < 8; ++i) mbar_init(p_part + i, 128);
         for (int i = 0; i < 4; ++i) mbar_init(o_full + i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -524,23 +528,41 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (lane == 0 && has_work) {
             constexpr uint32_t idesc_s = make_idesc(TC_KEYS);       // S[128 x 128] = Q K^T, K-major operands
             constexpr uint32_t idesc_o = make_idesc(TC_DIM, true);  // O[128 x 128] += P V, V is MN-major
+            // An MMA instruction holds the thread that issues it for 54 cycles whatever its size, and
+            // the pipe needs 64 for 128 x 128 x 16: what the thread does besides must stay under ten
+            // cycles an MMA or the pipe waits for it.  So the operands' descriptors are made once (their
+            // address field is additive: a k step further is a constant more) and the first MMA of a
+            // product, which overwrites, is its own instruction instead of a predicate computed each time.
+            constexpr uint64_t NEXT_TILE = DUO_TILE_BYTES >> 4;  // the second head's queries, the second stage
+            const uint64_t q_desc = smem_desc_sw128(smem_u32(q_tiles)), k_desc = smem_desc_sw128(smem_u32(k_tiles));
+            const uint64_t v_desc = smem_desc_sw128_mn(smem_u32(v_tiles), TC_HALF_BYTES);
             auto scores = [&](int h, int stage) {
-                const uint32_t q = smem_u32(q_tiles + h * DUO_TILE_BYTES), k = smem_u32(k_tiles + stage * DUO_TILE_BYTES);
+                const uint64_t q = q_desc + h * NEXT_TILE, k = k_desc + stage * NEXT_TILE;
+                const uint32_t d = tmem_base + h * 128;
 #pragma unroll
                 for (int kk = 0; kk < TC_DIM / 16; ++kk) {
-                    const uint32_t offset = (kk / 4) * TC_HALF_BYTES + (kk % 4) * 32;
-                    tcgen05_mma_bf16(tmem_base + h * 128, smem_desc_sw128(q + offset), smem_desc_sw128(k + offset), idesc_s,
-                                     kk > 0 ? 1u : 0u);
+                    constexpr uint32_t HALF_STEP = TC_HALF_BYTES >> 4;
+                    const uint64_t offset = (kk / 4) * HALF_STEP + (kk % 4) * 2;  // in units of 16 bytes
+                    if (kk == 0) tcgen05_mma_bf16_overwrite(d, q + offset, k + offset, idesc_s);
+                    else tcgen05_mma_bf16_add(d, q + offset, k + offset, idesc_s);
                 }
                 tcgen05_commit(s_full + h);
             };
-            auto outputs = [&](int h, int stage, int j) {
-                const uint32_t v = smem_u32(v_tiles + stage * DUO_TILE_BYTES);
+            // O_h (+)= P_h V: the rows hand their probabilities over a quarter of the keys at a time, and
+            // the two MMAs of a quarter are issued as soon as it is there, under the exponentials of the next.
+            auto outputs = [&](int h, int stage, int j) -> bool {
+                const uint64_t v = v_desc + stage * NEXT_TILE;
+                const uint32_t d = tmem_base + 256 + h * 128, a = tmem_base + h * 128;
 #pragma unroll
-                for (int kk = 0; kk < TC_KEYS / 16; ++kk)
-                    tcgen05_mma_bf16_ts(tmem_base + 256 + h * 128, tmem_base + h * 128 + kk * 8,
-                                        smem_desc_sw128_mn(v + kk * 16 * 128, TC_HALF_BYTES), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                for (int c = 0; c < 4; ++c) {
+                    if (!mbar_wait(p_part + h * 4 + c, j & 1)) return false;
+                    tcgen05_fence_after();
+                    if (c == 0 && j == 0) tcgen05_mma_bf16_ts_overwrite(d, a, v, idesc_o);
+                    else tcgen05_mma_bf16_ts_add(d, a + (2 * c) * 8, v + (2 * c) * (16 * 128 >> 4), idesc_o);
+                    tcgen05_mma_bf16_ts_add(d, a + (2 * c + 1) * 8, v + (2 * c + 1) * (16 * 128 >> 4), idesc_o);
+                }
                 tcgen05_commit(o_full + h * 2 + (j & 1));
+                return true;
             };
             bool ok = mbar_wait(q_full, 0) && mbar_wait(k_full, 0);
             if (!ok) atomicCAS(&g_attention_error, 0, 12 << 8);
@@ -552,15 +574,13 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
             }
             for (int j = 0; j < tiles_count && ok; ++j) {
                 const int stage = j & 1, next = stage ^ 1;
-                const uint32_t tile_parity = j & 1, stage_parity = (j >> 1) & 1, next_parity = ((j + 1) >> 1) & 1;
+                const uint32_t stage_parity = (j >> 1) & 1, next_parity = ((j + 1) >> 1) & 1;
                 const bool more = j + 1 < tiles_count;
                 // head a: its probabilities of tile j are ready; then its scores of tile j + 1.  The
                 // MMAs of a CTA run in the order of their issue, so the scores cannot overwrite the
                 // probabilities that the product before them still reads.
-                ok = mbar_wait(v_full + stage, stage_parity) && mbar_wait(p_full, tile_parity);
+                ok = mbar_wait(v_full + stage, stage_parity) && outputs(0, stage, j);
                 if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 1); break; }
-                tcgen05_fence_after();
-                outputs(0, stage, j);
                 if (more) {
                     ok = mbar_wait(k_full + next, next_parity);
                     if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 2); break; }
@@ -568,10 +588,8 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     scores(0, next);
                 }
                 // head b likewise; after its products the stages of V(j) and K(j + 1) are free
-                ok = mbar_wait(p_full + 1, tile_parity);
+                ok = outputs(1, stage, j);
                 if (!ok) { atomicCAS(&g_attention_error, 0, (12 << 8) | 3); break; }
-                tcgen05_fence_after();
-                outputs(1, stage, j);
                 tcgen05_commit(v_empty + stage);
                 if (more) {
                     scores(1, next);
@@ -661,13 +679,19 @@ attention_tcgen05_duo_kernel(const __grid_constant__ CUtensorMap map_q, const __
                         packed[i / 2] = cut_bf16x2(pr.x, pr.y);
                     }
                 }
-                // P columns [16 c, +16) hold keys [32 c, +32); this thread has read its whole row of S
+                // P columns [16 c, +16) hold keys [32 c, +32); this thread has read its whole row of S.
+                // The quarter before has had this quarter's exponentials to land in tensor memory.
+                if (c > 0) {
+                    tcgen05_wait_st();
+                    tcgen05_fence_before();
+                    mbar_arrive(p_part + h * 4 + c - 1);
+                }
                 tcgen05_st16(tmem_s + c * 16, packed);
             }
             row_sum += (partial[0].x + partial[0].y) + (partial[1].x + partial[1].y);
             tcgen05_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(p_full + h);
+            mbar_arrive(p_part + h * 4 + 3);
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(my_o_full + ((tiles_count - 1) & 1), ((tiles_count - 1) >> 1) & 1));
         if (!ok && lane == 0) atomicCAS(&g_attention_error, 0, 13 << 8);
