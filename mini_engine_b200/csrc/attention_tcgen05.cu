@@ -405,27 +405,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // is there: three quarters of O += P V run under the row's own exponentials instead of after them
 // (8,192 tokens: 497 -> 475 us).  Lazy rescaling, masking by position and page addressing as above.
 //
-// What bounds it (clock stamps of one CTA, 2,048 to 8,192 tokens): a tile of 128 keys of both heads
-// takes 3,700-3,900 cycles; its four products 2,580; each head's rows 35 for the load of the scores,
-// 315 for the maximum and 1,600 for the exponentials.  The special-function unit takes four lanes a
-// cycle per scheduler, so the 128 exponentials of a row are 1,024 cycles of its warp whatever else
-// is done (measured alone: 9.1 cycles per score with the sum and the packing); both heads' rows
-// share the four schedulers, which makes the softmax of a tile about 3,100 cycles of scheduler time
-// against 2,580 of the tensor pipe.  Tried from here and dropped: 2^x by a cubic on the multiply-add pipe
-// costs 10.5 cycles per score there (the two-wide float32 instructions issue at half rate), so
-// more than a quarter of the exponentials moved over is a loss (503 us at 8,192 tokens with a quarter,
-// 514 with none, 513 with half, 559 with three quarters); two threads per row halve a warp's
-// exponentials but not the unit's (514 us); steps of 64 keys with two score buffers per head, so
-// that rows never wait for a product, lost because a product of 64 keys takes the pipe as long as
-// one of 128 (648 us); one CTA per SM that walks a list of items (longest first, to and fro over the
-// CTAs) with the barriers' phases running on from item to item, so that an item's queries, first keys
-// and first scores come while the item before is normalised and stored: 2 to 3 % at 4,096 and 8,192
-// tokens, nothing at 2,048, and entries of unequal length would leave such a fixed list unbalanced
-// where the hardware hands this kernel's CTAs out as SMs come free.  Clock stamps of all CTAs at
-// 2,048 tokens: 60,000 to 77,000 cycles a CTA in 43 to 52 us, that is 1.48 GHz of 1.965 (the SMs
-// run this kernel under the power limit), and the MMA warp needs 750 cycles to issue the eight
-// instructions of one 128 x 128 x 128 product (the pipe takes them at 94 cycles each, two thirds of
-// its nominal rate), 3,080 of a tile's 3,600 cycles.
+// What bounds it (clock stamps of one CTA, 2,048 to 8,192 tokens, before the hand-over in quarters): a
+// tile of 128 keys of both heads takes 3,600 cycles; its 32 MMAs need 2,048 of the pipe (64 each, which
+// is what a CTA that only issues MMAs gets, also beside warps that read and write tensor memory and
+// compute exponentials: csrc/mma_rate.cu); each head's rows take 35 for the load of the scores, 250 to
+// 315 for the maximum and 1,430 to 1,600 for the exponentials, and wait 1,650 for their next scores.
+// So a head's tile is the chain scores -> maximum -> exponentials -> O += P V -> the next tile's
+// scores (queued behind the other head's products) -> barrier -> scores, and the two heads' chains
+// fill each other's gaps only in part.  The special-function unit takes four lanes a cycle per
+// scheduler, so the 128 exponentials of a row are 1,024 cycles of its warp whatever else is done
+// (measured alone: 9.1 cycles per score with the sum and the packing).  Tried from here and dropped:
+// 2^x by a cubic on the multiply-add pipe costs 10.5 cycles per score there (the two-wide float32
+// instructions issue at half rate), so more than a quarter of the exponentials moved over is a loss
+// (503 us at 8,192 tokens with a quarter, 514 with none, 513 with half, 559 with three quarters); two
+// threads per row halve a warp's exponentials but not the unit's (514 us); steps of 64 keys with two
+// score buffers per head, so that rows never wait for a product, lost because an MMA of 64 keys
+// holds its issuer as long as one of 128 (648 us); one CTA per SM that walks a list of items (longest
+// first, to and fro over the CTAs) with the barriers' phases running on from item to item, so that an
+// item's queries, first keys and first scores come while the item before is normalised and stored: 2
+// to 3 % at 4,096 and 8,192 tokens, nothing at 2,048, and entries of unequal length would leave such a
+// fixed list unbalanced where the hardware hands this kernel's CTAs out as SMs come free.  Clock
+// stamps of all CTAs at 2,048 tokens: 60,000 to 77,000 cycles a CTA in 43 to 52 us, that is 1.48 GHz
+// of 1.965 (the SMs run this kernel under the power limit).
 constexpr int DUO_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-5 rows of head a, warps 6-9 rows of head b
 constexpr int DUO_TMEM_COLUMNS = 512;
 constexpr int DUO_TILE_BYTES = 2 * TC_HALF_BYTES;  // a 128 x 128 bfloat16 tile as two 64-column halves
