@@ -424,8 +424,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 // first, to and fro over the CTAs) with the barriers' phases running on from item to item, so that an
 // item's queries, first keys and first scores come while the item before is normalised and stored: 2
 // to 3 % at 4,096 and 8,192 tokens, nothing at 2,048, and entries of unequal length would leave such a
-// fixed list unbalanced where the hardware hands this kernel's CTAs out as SMs come free.  Clock
-// stamps of all CTAs at 2,048 tokens: 60,000 to 77,000 cycles a CTA in 43 to 52 us, that is 1.48 GHz
+// fixed list unbalanced where the hardware hands this kernel's CTAs out as SMs come free; an MMA warp
+// that issues whatever is ready, head by head, instead of the fixed order a, b, a, b: 3,197 us against
+// 1,818 us at 16,384 tokens, because the fixed order is what keeps the two heads half a tile apart, and
+// heads in step compute their exponentials at the same time on the same units and leave the pipe idle
+// meanwhile.  Clock stamps of all CTAs at 2,048 tokens: 60,000 to 77,000 cycles a CTA in 43 to 52 us, that is 1.48 GHz
 // of 1.965 (the SMs run this kernel under the power limit).
 constexpr int DUO_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2-5 rows of head a, warps 6-9 rows of head b
 constexpr int DUO_TMEM_COLUMNS = 512;
